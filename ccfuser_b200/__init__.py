@@ -1,0 +1,11 @@
+"""B200-native fused expert-parallel MoE layer library."""
+from .config import MoEConfig
+from .errors import MoECommError, MoECommTimeout, MoEOverflow
+from .experts import Experts, ExpertLinear, scan_expert_params
+from .gates import BaseGate, NaiveGate, zipf_router_bias
+from .layers import MoELayer, MixMOE, MixMOETransformerMLP
+
+__version__ = "0.1.0"
+__all__ = ["MoEConfig", "MoELayer", "MixMOE", "MixMOETransformerMLP", "NaiveGate", "BaseGate", "Experts",
+           "ExpertLinear", "scan_expert_params", "zipf_router_bias", "MoECommError", "MoECommTimeout",
+           "MoEOverflow"]

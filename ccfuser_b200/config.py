@@ -1,0 +1,100 @@
+"""Configuration of one expert-parallel MoE FFN layer.
+
+The reference hard-codes most of these knobs (block size 64 at
+mix_moe/mix_moe/layers.py:66, top-2 buffer factor at mix_moe/csrc/mix_moe.h:77,
+fp16 only at mix_moe/csrc/mix_moe.h:242-245, GELU at mix_moe/mix_moe/transformer.py:445);
+here they are one frozen dataclass that every backend reads.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+import os
+from typing import Optional
+
+import torch
+
+ACTIVATIONS = ("gelu", "relu", "swiglu")
+BACKENDS = ("auto", "fused", "nccl", "cpu")
+
+
+@dataclasses.dataclass(frozen=True)
+class MoEConfig:
+    """Static description of an MoE FFN layer.
+
+    d_model / d_ffn      feature sizes of the expert FFN (d_model -> d_ffn -> d_model)
+    num_experts          total number of experts over the expert-parallel group
+    top_k                experts chosen per token
+    capacity_factor      >0: each (source rank, expert) pair keeps at most
+                         ceil(capacity_factor * tokens * top_k / num_experts) routed rows,
+                         later rows (in token-major slot order) are dropped;
+                         0 or None: nothing is dropped
+    activation           'gelu' | 'relu' | 'swiglu' (swiglu adds a second up projection)
+    bias                 expert linear layers carry a bias (the reference always does)
+    dtype                parameter / compute dtype
+    ep_size              expert-parallel world size (experts are split evenly)
+    backend              'fused' (sm_100a kernels), 'nccl' (all_to_all_single + library GEMM
+                         baseline), 'cpu' (same code path over gloo), 'auto'
+    max_tokens           upper bound of tokens per rank per call; sizes the symmetric buffers
+    recv_factor          without a capacity factor the receive buffer of a rank is sized
+                         recv_factor x the balanced load (overflow is reported, not silent)
+    """
+
+    d_model: int
+    d_ffn: int
+    num_experts: int
+    top_k: int = 2
+    capacity_factor: Optional[float] = None
+    activation: str = "gelu"
+    bias: bool = True
+    dtype: torch.dtype = torch.bfloat16
+    ep_size: int = 1
+    backend: str = "auto"
+    max_tokens: int = 4096
+    recv_factor: float = 2.0
+    router_bias: bool = True
+
+    def __post_init__(self):
+        if self.activation not in ACTIVATIONS:
+            raise ValueError(f"activation must be one of {ACTIVATIONS}, got {self.activation!r}")
+        if self.backend not in BACKENDS:
+            raise ValueError(f"backend must be one of {BACKENDS}, got {self.backend!r}")
+        if self.num_experts % self.ep_size != 0:
+            raise ValueError("num_experts must be divisible by ep_size")
+        if not (1 <= self.top_k <= self.num_experts):
+            raise ValueError("top_k must be in [1, num_experts]")
+
+    @property
+    def experts_per_rank(self) -> int:
+        return self.num_experts // self.ep_size
+
+    def capacity(self, tokens: int) -> int:
+        """Rows one source rank may send to one expert for a call with `tokens` tokens."""
+        slots = tokens * self.top_k
+        if not self.capacity_factor or self.capacity_factor <= 0:
+            return slots
+        return min(slots, int(math.ceil(self.capacity_factor * slots / self.num_experts)))
+
+    def max_recv_rows(self, tokens: Optional[int] = None, tile: int = 128) -> int:
+        """Upper bound of rows (tile padded, per expert) a rank must be able to receive."""
+        tokens = self.max_tokens if tokens is None else tokens
+        e_loc = self.experts_per_rank
+        if self.capacity_factor and self.capacity_factor > 0:
+            per_expert = self.ep_size * self.capacity(tokens)
+            per_expert = (per_expert + tile - 1) // tile * tile
+            return e_loc * per_expert
+        balanced = tokens * self.top_k  # == ep_size * tokens * top_k / ep_size
+        rows = int(math.ceil(self.recv_factor * balanced)) + e_loc * tile
+        rows = min(rows, self.ep_size * tokens * self.top_k + e_loc * tile)
+        return (rows + tile - 1) // tile * tile
+
+    def replace(self, **kw) -> "MoEConfig":
+        return dataclasses.replace(self, **kw)
+
+
+def env_flag(name: str, default: int = 0) -> int:
+    """Integer debug switch read from the environment (CCFUSER_<NAME>)."""
+    try:
+        return int(os.environ.get("CCFUSER_" + name, default))
+    except ValueError:
+        return default

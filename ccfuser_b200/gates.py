@@ -1,0 +1,94 @@
+"""Routers. Same parameter names as the reference gate (``gate.weight`` / ``gate.bias`` inside the
+module, i.e. ``<layer>.gate.gate.weight`` in a state dict; mix_moe/mix_moe/gates/naive_gate.py:22)."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class BaseGate(nn.Module):
+    """Holds the expert counts and an auxiliary loss slot (mix_moe/mix_moe/gates/base_gate.py:7-29)."""
+
+    def __init__(self, num_expert: int, world_size: int):
+        super().__init__()
+        self.world_size = world_size
+        self.num_expert = num_expert
+        self.tot_expert = world_size * num_expert
+        self.loss = None
+
+    def forward(self, x):
+        raise NotImplementedError("Base gate cannot be used directly")
+
+    def set_loss(self, loss):
+        self.loss = loss
+
+    def get_loss(self, clear: bool = True):
+        loss = self.loss
+        if clear:
+            self.loss = None
+        return loss
+
+    @property
+    def has_loss(self):
+        return self.loss is not None
+
+
+def topk_softmax_reference(logits: torch.Tensor, k: int):
+    """fp32 top-k then softmax over the k selected logits (mix_moe/mix_moe/gates/naive_gate.py:31-38).
+
+    Ties are broken towards the lower expert id so CPU, GPU and the CUDA kernel agree."""
+    lg = logits.float()
+    e = lg.shape[-1]
+    # stable descending order with lowest index first among equals
+    order = torch.sort(lg, dim=-1, descending=True, stable=True).indices[..., :k]
+    val = torch.gather(lg, -1, order)
+    score = torch.softmax(val, dim=-1)
+    return order, score
+
+
+class NaiveGate(BaseGate):
+    """Linear router + top-k + softmax over the selected logits.
+
+    ``forward`` returns ``(idx [T,k] int64, score [T,k] fp32)``. With ``return_all_scores`` the raw
+    logits are returned as a third value. An optional load-balance auxiliary loss (the reference
+    sets a dummy zero, naive_gate.py:41) is stored with ``set_loss``.
+    """
+
+    def __init__(self, d_model: int, num_expert: int, world_size: int, top_k: int = 2,
+                 bias: bool = True, aux_loss_coef: float = 0.0):
+        super().__init__(num_expert, world_size)
+        self.gate = nn.Linear(d_model, self.tot_expert, bias=bias)
+        self.top_k = top_k
+        self.aux_loss_coef = aux_loss_coef
+
+    def logits(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(x, self.gate.weight, self.gate.bias)
+
+    def forward(self, x: torch.Tensor, return_all_scores: bool = False):
+        logits = self.logits(x)
+        idx, score = topk_softmax_reference(logits, self.top_k)
+        if self.aux_loss_coef > 0:
+            probs = torch.softmax(logits.float(), dim=-1)
+            frac = torch.zeros(self.tot_expert, device=x.device, dtype=torch.float32)
+            frac.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), device=x.device))
+            frac = frac / max(1, idx.numel())
+            self.set_loss(self.aux_loss_coef * self.tot_expert * (frac * probs.mean(0)).sum())
+        else:
+            self.set_loss(torch.zeros(1, device=x.device, dtype=torch.float32))
+        if return_all_scores:
+            return idx, score, logits
+        return idx, score
+
+
+def zipf_router_bias(num_experts: int, s: float = 1.2, scale: float = 1.0, seed: int = 0) -> torch.Tensor:
+    """Bias that makes expert popularity follow Zipf(s) when the logits are otherwise exchangeable:
+    bias_e = scale * log(p_e) with p_e ~ rank^-s, experts permuted by a fixed seed."""
+    ranks = torch.arange(1, num_experts + 1, dtype=torch.float64)
+    p = ranks.pow(-s)
+    p = p / p.sum()
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_experts, generator=g)
+    bias = torch.empty(num_experts, dtype=torch.float64)
+    bias[perm] = scale * torch.log(p)
+    return bias.float()

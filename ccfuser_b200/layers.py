@@ -1,0 +1,149 @@
+"""The user-facing MoE FFN layer.
+
+``MoELayer`` is the new API; ``MixMOETransformerMLP`` / ``MixMOE`` keep the constructor of the reference
+(mix_moe/mix_moe/transformer.py:428-448, mix_moe/mix_moe/layers.py:33-60) so its users can switch over.
+Forward semantics follow mix_moe/mix_moe/transformer.py:475-497 and layers.py:550-568: flatten to
+``[T, d_model]``, route top-k, run each kept (token, slot) through its expert, sum the slots weighted by the
+gate scores, reshape back. Planning is done on the device; there is no Python planner thread
+(transformer.py:102-426).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .config import MoEConfig
+from .experts import Experts, scan_expert_params
+from .gates import NaiveGate
+from .parallel.a2a import moe_forward_a2a
+
+
+class MoELayer(nn.Module):
+    """Expert-parallel MoE FFN: ``y = sum_j keep_j * g_j * FFN_{e_j}(x)``.
+
+    Parameters live under ``gate.gate.{weight,bias}`` and ``experts.{htoh4,h4toh}.{weight,bias}``
+    (plus ``experts.htoh4_gate.*`` for SwiGLU). Each rank of ``ep_group`` owns
+    ``num_experts / ep_size`` consecutive experts (mix_moe/mix_moe/transformer.py:120-122).
+    """
+
+    def __init__(self, config: MoEConfig, ep_group=None, device=None, gate: Optional[nn.Module] = None):
+        super().__init__()
+        self.config = config
+        if ep_group is None and dist.is_initialized() and config.ep_size > 1:
+            ep_group = dist.group.WORLD
+        self.ep_group = ep_group
+        world = dist.get_world_size(ep_group) if (dist.is_initialized() and config.ep_size > 1) else 1
+        if world != config.ep_size:
+            raise ValueError(f"config.ep_size={config.ep_size} but the expert-parallel group has {world} ranks")
+        self.ep_rank = dist.get_rank(ep_group) if world > 1 else 0
+        e_loc = config.experts_per_rank
+        self.gate = gate if gate is not None else NaiveGate(
+            config.d_model, e_loc, config.ep_size, config.top_k, bias=config.router_bias)
+        self.gate.to(device=device, dtype=config.dtype)
+        self.experts = Experts(e_loc, config.d_model, config.d_ffn, config.activation, config.bias,
+                               dtype=config.dtype, device=device)
+        scan_expert_params(self.experts)
+        for p in self.gate.parameters():
+            setattr(p, "dp_comm", "gate")
+        self._fused = None
+        self.last_stats = {}
+
+    # ---- backend selection -------------------------------------------------------------------
+    def backend(self, x: torch.Tensor) -> str:
+        b = self.config.backend
+        if b == "auto":
+            return "fused" if x.is_cuda else "cpu"
+        return b
+
+    def _fused_impl(self):
+        if self._fused is None:
+            from .ops.fused import FusedMoE  # needs the CUDA library
+            self._fused = FusedMoE(self)
+        return self._fused
+
+    # ---- forward -----------------------------------------------------------------------------
+    def forward(self, inp: torch.Tensor) -> torch.Tensor:
+        cfg = self.config
+        shape = inp.shape
+        x = inp.reshape(-1, cfg.d_model)
+        backend = self.backend(x)
+        if backend == "fused":
+            y = self._fused_impl()(x)
+        else:
+            idx, score = self.gate(x)
+            y = moe_forward_a2a(x, idx, score, self.experts, num_experts=cfg.num_experts,
+                                capacity=cfg.capacity(x.shape[0]),
+                                group=self.ep_group if cfg.ep_size > 1 else None)
+            y = y.to(inp.dtype)
+        return y.reshape(shape[:-1] + (y.shape[-1],))
+
+    def extra_repr(self):
+        c = self.config
+        return (f"experts={c.num_experts} (local {c.experts_per_rank}), top_k={c.top_k}, d_model={c.d_model}, "
+                f"d_ffn={c.d_ffn}, act={c.activation}, capacity_factor={c.capacity_factor}, backend={c.backend}")
+
+
+class MixMOE(MoELayer):
+    """Constructor-compatible stand-in for the reference base class (mix_moe/mix_moe/layers.py:33-60)."""
+
+    def __init__(self, num_expert=32, d_model=1024, world_size=1, top_k=2, gate=NaiveGate,
+                 d_hidden=4096, activation="gelu", moe_group=None, capacity_factor=None,
+                 dtype=torch.float32, backend="auto", max_tokens=4096, device=None):
+        cfg = MoEConfig(d_model=d_model, d_ffn=d_hidden, num_experts=num_expert * world_size, top_k=top_k,
+                        capacity_factor=capacity_factor, activation=_act_name(activation), dtype=dtype,
+                        ep_size=world_size, backend=backend, max_tokens=max_tokens)
+        gate_mod = gate(d_model, num_expert, world_size, top_k) if isinstance(gate, type) else gate
+        super().__init__(cfg, ep_group=moe_group, device=device, gate=gate_mod)
+        self.num_expert, self.d_model, self.world_size, self.top_k = num_expert, d_model, world_size, top_k
+
+    def mark_parallel_comm(self, expert_dp_comm="none"):
+        """FastMoE-style communication tags (mix_moe/mix_moe/layers.py:70-83)."""
+        for p in self.experts.parameters():
+            setattr(p, "dp_comm", expert_dp_comm)
+        for p in self.gate.parameters():
+            setattr(p, "dp_comm", "gate")
+
+
+class MixMOETransformerMLP(MixMOE):
+    """``MixMOETransformerMLP(gate_type, experts, model_dim, expert_rank, world_size, ...)`` as in
+    mix_moe/mix_moe/transformer.py:435-448. ``experts`` is the reference's dict
+    (``count_per_node``, ``hidden_size_per_expert``, optional ``activation_fn``); unlike the reference
+    the activation named there is honoured (``'gelu' | 'relu' | 'swiglu'`` or an nn.Module)."""
+
+    def __init__(self, gate_type=None, experts=None, model_dim=1024, expert_rank=0, world_size=1,
+                 scan_expert_func=None, total_batch_size=4096, expert_dp_comm="none",
+                 activation=None, top_k=None, moe_group=None, capacity_factor=None,
+                 dtype=torch.float32, backend="auto", device=None):
+        experts = experts or {}
+        gate_type = gate_type or {}
+        k = top_k if top_k is not None else gate_type.get("k", 2)
+        act = activation if activation is not None else experts.get("activation_fn", "gelu")
+        super().__init__(num_expert=experts.get("count_per_node", 1), d_model=model_dim,
+                         world_size=world_size, top_k=k, d_hidden=experts.get("hidden_size_per_expert", 4 * model_dim),
+                         activation=act, moe_group=moe_group,
+                         capacity_factor=capacity_factor if capacity_factor is not None else gate_type.get("capacity_factor"),
+                         dtype=dtype, backend=backend, max_tokens=total_batch_size, device=device)
+        if scan_expert_func is not None:
+            for n, p in self.experts.named_parameters():
+                scan_expert_func(n, p)
+        self.mark_parallel_comm(expert_dp_comm)
+
+    def async_expert_assignment(self, x):
+        """Kept as a no-op: routing and planning run on the device inside ``forward``, so there is
+        nothing to overlap on a host thread (mix_moe/mix_moe/transformer.py:463-466)."""
+        return None
+
+
+def _act_name(a) -> str:
+    if isinstance(a, str):
+        return a.lower()
+    if isinstance(a, nn.GELU) or a is torch.nn.functional.gelu:
+        return "gelu"
+    if isinstance(a, nn.ReLU) or a is torch.nn.functional.relu:
+        return "relu"
+    if a is None:
+        return "gelu"
+    raise ValueError(f"unsupported expert activation {a!r} (use 'gelu', 'relu' or 'swiglu')")

@@ -1,0 +1,105 @@
+"""CPU plumbing: the gloo all-to-all path against the dense oracle (fwd and grads)."""
+import torch
+import pytest
+
+from ccfuser_b200 import MoEConfig, MoELayer, MixMOETransformerMLP
+from ccfuser_b200.ops.reference import dense_moe_oracle
+from tests.mp_util import run_ranks
+
+
+def _full_params(cfg, seed, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    e, d, f = cfg.num_experts, cfg.d_model, cfg.d_ffn
+    p = {
+        "gate.weight": torch.randn(e, d, generator=g) * 0.02,
+        "gate.bias": torch.randn(e, generator=g) * 0.02,
+        "htoh4.weight": torch.randn(e, f, d, generator=g) * 0.02,
+        "htoh4.bias": torch.randn(e, f, generator=g) * 0.02,
+        "h4toh.weight": torch.randn(e, d, f, generator=g) * 0.02,
+        "h4toh.bias": torch.randn(e, d, generator=g) * 0.02,
+    }
+    if cfg.activation == "swiglu":
+        p["htoh4_gate.weight"] = torch.randn(e, f, d, generator=g) * 0.02
+        p["htoh4_gate.bias"] = torch.randn(e, f, generator=g) * 0.02
+    return {k: v.to(dtype) for k, v in p.items()}
+
+
+def load_shard(layer, full, rank):
+    e_loc = layer.config.experts_per_rank
+    sl = slice(rank * e_loc, (rank + 1) * e_loc)
+    with torch.no_grad():
+        layer.gate.gate.weight.copy_(full["gate.weight"])
+        layer.gate.gate.bias.copy_(full["gate.bias"])
+        for name in ("htoh4", "h4toh", "htoh4_gate"):
+            if name + ".weight" in full and hasattr(layer.experts, name):
+                getattr(layer.experts, name).weight.copy_(full[name + ".weight"][sl])
+                getattr(layer.experts, name).bias.copy_(full[name + ".bias"][sl])
+
+
+def _inputs(world, tokens, d, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(tokens, d, generator=g) for _ in range(world)]
+
+
+def _rank_fn(rank, world, cfg_kw, tokens):
+    cfg = MoEConfig(**cfg_kw)
+    full = _full_params(cfg, 0)
+    layer = MoELayer(cfg)
+    load_shard(layer, full, rank)
+    x = _inputs(world, tokens, cfg.d_model)[rank].clone().requires_grad_(True)
+    y = layer(x)
+    (y * torch.linspace(-1, 1, y.numel()).view_as(y)).sum().backward()
+    grads = {n: p.grad.clone() for n, p in layer.named_parameters()}
+    return y.detach(), x.grad.clone(), grads
+
+
+def _oracle(cfg, world, tokens):
+    full = {k: v.clone().requires_grad_(True) for k, v in _full_params(cfg, 0).items()}
+    xs = [x.clone().requires_grad_(True) for x in _inputs(world, tokens, cfg.d_model)]
+    ys = dense_moe_oracle(xs, full, top_k=cfg.top_k, capacity=cfg.capacity(tokens), activation=cfg.activation)
+    loss = sum((y * torch.linspace(-1, 1, y.numel()).view_as(y)).sum() for y in ys)
+    loss.backward()
+    return ys, xs, full
+
+
+@pytest.mark.parametrize("activation,cf", [("gelu", 1.25), ("swiglu", 1.0), ("relu", None)])
+def test_two_rank_layer_matches_oracle(activation, cf):
+    """Per rank 512 tokens (4 x 128), d_model 256, 8 experts (4 per rank), FFN 256->1024->256, top-2."""
+    world, tokens = 2, 512
+    kw = dict(d_model=256, d_ffn=1024, num_experts=8, top_k=2, capacity_factor=cf, activation=activation,
+              dtype=torch.float32, ep_size=world, backend="cpu", max_tokens=tokens)
+    cfg = MoEConfig(**kw)
+    res = run_ranks(_rank_fn, world, kw, tokens)
+    ys, xs, full = _oracle(cfg, world, tokens)
+    e_loc = cfg.experts_per_rank
+    gate_w = sum(r[2]["gate.gate.weight"] for r in res)
+    for r in range(world):
+        y, gx, grads = res[r]
+        assert torch.allclose(y, ys[r].detach(), atol=1e-5, rtol=1e-4)
+        assert torch.allclose(gx, xs[r].grad, atol=1e-5, rtol=1e-4)
+        sl = slice(r * e_loc, (r + 1) * e_loc)
+        for name in ("htoh4", "h4toh") + (("htoh4_gate",) if activation == "swiglu" else ()):
+            assert torch.allclose(grads[f"experts.{name}.weight"], full[name + ".weight"].grad[sl], atol=1e-5, rtol=1e-4)
+            assert torch.allclose(grads[f"experts.{name}.bias"], full[name + ".bias"].grad[sl], atol=1e-5, rtol=1e-4)
+    # the router is replicated: its gradient is the sum over ranks (what DDP's all-reduce produces)
+    assert torch.allclose(gate_w, full["gate.weight"].grad, atol=1e-5, rtol=1e-4)
+
+
+def test_single_process_and_compat_constructor():
+    torch.manual_seed(0)
+    layer = MixMOETransformerMLP(gate_type={"type": "top", "k": 2},
+                                 experts={"count_per_node": 4, "hidden_size_per_expert": 64, "type": "ffn"},
+                                 model_dim=32, world_size=1, total_batch_size=64, backend="cpu")
+    keys = set(layer.state_dict().keys())
+    assert keys == {"gate.gate.weight", "gate.gate.bias", "experts.htoh4.weight", "experts.htoh4.bias",
+                    "experts.h4toh.weight", "experts.h4toh.bias"}
+    assert layer.experts.htoh4.weight.shape == (4, 64, 32)
+    assert layer.experts.h4toh.weight.shape == (4, 32, 64)
+    assert all(getattr(p, "skip_allreduce", False) for p in layer.experts.parameters())
+    x = torch.randn(2, 8, 32)
+    y = layer(x)
+    assert y.shape == x.shape
+    full = {k.split(".", 1)[1] if k.startswith("experts.") else "gate." + k.split(".")[-1]: v
+            for k, v in layer.state_dict().items()}
+    ref = dense_moe_oracle([x.reshape(-1, 32)], full, top_k=2, capacity=None)[0]
+    assert torch.allclose(y.reshape(-1, 32), ref, atol=1e-5)

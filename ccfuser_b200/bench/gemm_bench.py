@@ -1,0 +1,109 @@
+"""Device-timed throughput of the tcgen05 grouped GEMM variants on one GPU (CUDA events, L2 flushed
+between timed launches). Prints one JSON line per case with achieved TFLOP/s and the fraction of the
+measured cuBLAS bf16 peak (MEASURED_PEAKS.json at the repository root when present)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from .. import native as N
+from ..ops import gemm as G
+
+
+def measured_peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+def time_fn(fn, iters=10, warmup=3, flush_mb=256):
+    flush = torch.empty(flush_mb * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--cases", default="square,fwd1,fwd2,dgrad,wgrad,cublas")
+    ap.add_argument("--rows", type=int, default=4096 * 8)
+    ap.add_argument("--experts", type=int, default=8)
+    ap.add_argument("--d", type=int, default=4096)
+    ap.add_argument("--f", type=int, default=14336)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    peak, _, src = measured_peaks()
+    dev = "cuda"
+    e, d, f = args.experts, args.d, args.f
+    rows_per = args.rows // e
+    gb = torch.arange(e, dtype=torch.int32, device=dev) * rows_per
+    gr = torch.full((e,), rows_per, dtype=torch.int32, device=dev)
+    r = rows_per * e
+    out = []
+
+    def report(name, flops, fn):
+        med, best = time_fn(fn, args.iters)
+        G.Workspace.get(dev).check(name)
+        rec = {"case": name, "ms_median": round(med, 4), "ms_best": round(best, 4),
+               "tflops_median": round(flops / med / 1e9, 1), "frac_of_" + src + "_cublas_peak": round(flops / med / 1e9 / peak, 3)}
+        print(json.dumps(rec), flush=True)
+        out.append(rec)
+
+    cases = args.cases.split(",")
+    if "square" in cases:
+        m = 8192
+        x = torch.randn(m, m, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(m, m, device=dev, dtype=torch.bfloat16)
+        report("square_8192_ours", 2 * m ** 3, lambda: G.linear(x, w))
+        if "cublas" in cases:
+            report("square_8192_cublas", 2 * m ** 3, lambda: torch.matmul(x, w.t()))
+        del x, w
+    x = torch.randn(r, d, device=dev, dtype=torch.bfloat16)
+    w1 = torch.randn(e, f, d, device=dev, dtype=torch.bfloat16) * 0.02
+    h = torch.empty(r, f, device=dev, dtype=torch.bfloat16)
+    pre = torch.empty(r, f, device=dev, dtype=torch.bfloat16)
+    if "fwd1" in cases:
+        report("fwd1_gelu", 2 * r * d * f, lambda: G.launch(
+            a0=x, b0=w1.view(e * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT, n=f, k=d,
+            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=f, out0=h, out1=pre, act=N.ACT_GELU))
+    w2 = torch.randn(e, d, f, device=dev, dtype=torch.bfloat16) * 0.02
+    y = torch.empty(r, d, device=dev, dtype=torch.bfloat16)
+    if "fwd2" in cases:
+        report("fwd2_store", 2 * r * d * f, lambda: G.launch(
+            a0=h, b0=w2.view(e * d, f), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_STORE, n=d, k=f,
+            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=y))
+    if "dgrad" in cases:
+        report("dgrad2_dact", 2 * r * d * f, lambda: G.launch(
+            a0=y, b0=w2.view(e * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DACT, n=f, k=d,
+            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=h, aux0=pre, act=N.ACT_GELU))
+    if "wgrad" in cases:
+        dw = torch.empty(e, d, f, device=dev, dtype=torch.bfloat16)
+        report("wgrad2", 2 * r * d * f, lambda: G.launch(
+            a0=y, b0=h, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True, m_per_group=d,
+            group_base=gb, group_rows=gr, num_groups=e, out0=dw, ld_out=f))
+    os.makedirs("gpurun_out", exist_ok=True)
+    with open("gpurun_out/gemm_bench.json", "w") as fh:
+        json.dump(out, fh, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,122 @@
+// Dispatch role: push routed token rows straight into the expert input buffers of their owner GPUs
+// (peer stores over NVLink, plain 16-byte vector stores, never TMA multicast) and bump the arrival
+// counter of the 128-row tile each row lands in. The same device function is used by the stand-alone
+// dispatch kernel and by the first CTAs of the fused dispatch+GEMM kernel.
+//
+// Replaces _local_scatter_kernel + nvshmemx_get16_nbi_block of the reference
+// (mix_moe/csrc/cuda/mix_moe_kernel.cu:18-33, mix_moe/csrc/cuda/mix_gemm.cu:304-307): the reference sorts
+// rows locally and lets the owner pull 64-row blocks after a global barrier; here the source pushes
+// and the owner's GEMM starts tile by tile as the counters fill, with no barrier.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "gemm_args.h"
+#include "sm100.cuh"
+
+namespace ccf {
+
+__device__ __forceinline__ void report_status(int* status, int code, int detail) {
+  if (status) atomicCAS(status, 0, (detail << 8) | code);
+}
+
+__device__ __forceinline__ float2 unpack2(uint32_t u, int fp16) {
+  if (fp16) {
+    __half2 h = *reinterpret_cast<__half2*>(&u);
+    return __half22float2(h);
+  }
+  __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&u);
+  return __bfloat1622float2(b);
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int fp16) {
+  if (fp16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One warp works on chunks of kChunk consecutive slots taken from a shared counter.
+template <int kChunk>
+__device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
+  static_assert(kChunk <= 32, "one lane per slot of a chunk");
+  const int S = a.tokens * a.top_k;
+  const int lane = threadIdx.x & 31;
+  const int vecs = a.d >> 3;  // 16-byte vectors per row
+  for (;;) {
+    int c = 0;
+    if (lane == 0) c = atomicAdd(a.work_counter, 1);
+    c = __shfl_sync(0xffffffffu, c, 0);
+    const int s0 = c * kChunk;
+    if (s0 >= S) break;
+    const int ns = min(kChunk, S - s0);
+    // lane i plans slot s0 + i
+    int my_row = -1, my_owner = 0;
+    float my_gate = 0.f;
+    if (lane < ns) {
+      const int s = s0 + lane;
+      const int e = a.slot_expert[s];
+      const int p = a.slot_pos[s];
+      my_gate = a.slot_gate[s];
+      if (p < a.capacity) {
+        my_owner = e / a.experts_per_rank;
+        my_row = a.dst_base[e] + p;
+        if (my_row < 0 || my_row >= a.max_rows || my_owner >= CCF_MAX_RANKS) {
+          report_status(status, CCF_ERR_OVERFLOW, s & 0xffffff);
+          my_row = -1;
+        }
+      }
+      if (a.slot_row) a.slot_row[s] = my_row;
+      if (my_row >= 0) {
+        a.peer_row_src[my_owner][my_row] = (a.my_rank << 24) | s;
+        a.peer_row_gate[my_owner][my_row] = my_gate;
+      } else if (a.backward && a.dgate) {
+        a.dgate[s] = 0.f;
+      }
+    }
+    for (int i = 0; i < ns; ++i) {
+      const int row = __shfl_sync(0xffffffffu, my_row, i);
+      if (row < 0) continue;
+      const int owner = __shfl_sync(0xffffffffu, my_owner, i);
+      const int s = s0 + i;
+      const int t = s / a.top_k;
+      const uint4* src = reinterpret_cast<const uint4*>(a.x) + static_cast<size_t>(t) * vecs;
+      uint4* dst = reinterpret_cast<uint4*>(a.peer_recv[owner]) + static_cast<size_t>(row) * vecs;
+      if (!a.backward) {
+#pragma unroll 4
+        for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);
+      } else {
+        // rows of the backward pass carry g * dy; the gate gradient is <dy, saved scaled output> / g
+        const float g = __shfl_sync(0xffffffffu, my_gate, i);
+        const uint4* sv = reinterpret_cast<const uint4*>(a.saved_comb) + static_cast<size_t>(s) * vecs;
+        float dot = 0.f;
+#pragma unroll 2
+        for (int v = lane; v < vecs; v += 32) {
+          uint4 xv = __ldg(src + v);
+          uint4 cv = a.saved_comb ? __ldg(sv + v) : make_uint4(0, 0, 0, 0);
+          uint32_t xi[4] = {xv.x, xv.y, xv.z, xv.w};
+          uint32_t ci[4] = {cv.x, cv.y, cv.z, cv.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float2 xf = unpack2(xi[q], a.fp16);
+            float2 cf = unpack2(ci[q], a.fp16);
+            dot += xf.x * cf.x + xf.y * cf.y;
+            o[q] = pack2(xf.x * g, xf.y * g, a.fp16);
+          }
+          dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        if (lane == 0 && a.dgate) a.dgate[s] = (g != 0.f) ? dot / g : 0.f;
+      }
+    }
+    // make the rows visible before the counters move
+    __threadfence_system();
+    __syncwarp();
+    if (lane < ns && my_row >= 0) red_release_sys_add(a.peer_tile_flags[my_owner] + (my_row >> 7), 1);
+  }
+}
+
+}  // namespace ccf

@@ -1,0 +1,715 @@
+// Grouped GEMM for sm_100a: TMA (local memory, no multicast) -> 128B-swizzled shared memory ->
+// tcgen05.mma with fp32 accumulators in TMEM -> tcgen05.ld epilogue. One persistent CTA per SM,
+// 6 warps: warp 0 = tile scheduler + TMA producer, warp 1 = MMA issuer (one elected thread),
+// warps 2..5 = epilogue (one TMEM lane quarter each). Tiles are 128 x 256 x 64, four shared-memory
+// stages, two TMEM accumulator stages (2 x 256 columns) so the epilogue of a tile overlaps the
+// main loop of the next one.
+//
+// The kernel replaces the reference's wmma tile GEMM and its callers (mix_moe/csrc/cuda/mix_gemm.cu:22-244
+// myHGEMMAlignedV5, :282-436 moe_first_mm, :439-555 moe_second_mm, :780-974 the wgrad block-gather GEMM)
+// with fp32 accumulation (the reference accumulates in fp16, mix_gemm.cu:43).
+//
+//   row-grouped mode   C[rows of group g, N] = A[rows of g, K] * B_g       (forward and dgrad GEMMs)
+//   k-grouped mode     C_g[M, N] = sum over rows r of group g  A[r, M]^T B[r, N]   (wgrad)
+//
+// Operand majors: A and B may each be K-major (reduction index contiguous) or MN-major; weights are
+// read in their [expert, out, in] layout for x W^T (K-major) and for dy W (MN-major), activations are
+// read MN-major for wgrad, so nothing is ever transposed in memory.
+//
+// Fusion with the collectives:
+//   * A tiles may be gated on per-tile arrival counters that remote dispatch roles increment
+//     (args.tile_flags); the TMA producer polls its own GPU's memory with a bounded acquire loop.
+//   * The first args.n_comm_ctas CTAs run the dispatch role (dispatch.cuh) before joining the tile loop,
+//     so the all-to-all dispatch and the first GEMM are one kernel.
+//   * EPI_COMBINE stores each output row, scaled by its gate weight, directly into the combine buffer of
+//     the rank the token came from and bumps that rank's completion counter.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+
+#include "dispatch.cuh"
+#include "gemm_args.h"
+#include "sm100.cuh"
+
+namespace ccf {
+
+constexpr int BM = 128, BN = 256, BK = 64, UK = 16;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = BN * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSchedSlots = 4;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int MAJ_K = 0, MAJ_MN = 1;
+
+struct __align__(16) Ctrl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint64_t sched_full[kSchedSlots];
+  uint64_t sched_empty[kSchedSlots];
+  uint32_t tmem_base;
+  int abort_word;
+  int total_tiles;
+  int n_tiles;
+  int sched_tile[kSchedSlots];
+  int mt_prefix[CCF_MAX_GROUPS + 1];
+};
+
+constexpr int kSmemBytes = 1024 + kStages * kStageBytes + static_cast<int>(sizeof(Ctrl));
+
+struct Tile {
+  int g;           // group (expert)
+  int row0;        // row-grouped: first A/C row; k-grouped: first output row inside the group (m0)
+  int n0;          // first output column (for SWIGLU: first *output* column, 128 per tile)
+  int rows_valid;  // valid rows of the tile
+  int kblocks;     // 64-deep reduction steps
+  int krow0;       // k-grouped: first reduction row
+};
+
+template <bool kKGroup, int kEpi>
+__device__ __forceinline__ Tile decode_tile(int t, const CcfGemmArgs& a, const Ctrl* c) {
+  Tile ti;
+  constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
+  if constexpr (!kKGroup) {
+    const int nt = c->n_tiles;
+    int lo = 0, hi = a.num_groups;  // largest g with nt * mt_prefix[g] <= t
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (nt * c->mt_prefix[mid] <= t) lo = mid; else hi = mid;
+    }
+    ti.g = lo;
+    const int mt_g = c->mt_prefix[lo + 1] - c->mt_prefix[lo];
+    const int local = t - nt * c->mt_prefix[lo];
+    const int j = local / mt_g, i = local - j * mt_g;
+    const int rows = a.group_rows[lo];
+    ti.row0 = a.group_base[lo] + i * BM;
+    ti.rows_valid = min(BM, rows - i * BM);
+    ti.n0 = j * bn_out;
+    ti.kblocks = a.kseg * ((a.k + BK - 1) / BK);
+    ti.krow0 = 0;
+  } else {
+    const int mt = a.m_per_group / BM;
+    const int tpg = mt * c->n_tiles;
+    ti.g = t / tpg;
+    const int local = t - ti.g * tpg;
+    const int j = local / mt, i = local - j * mt;
+    ti.row0 = i * BM;
+    ti.rows_valid = BM;
+    ti.n0 = j * BN;
+    ti.kblocks = (a.group_rows[ti.g] + BK - 1) / BK;
+    ti.krow0 = a.group_base[ti.g];
+  }
+  return ti;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// epilogue math
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+__device__ __forceinline__ float act_f(float x, int act) {
+  if (act == CCF_ACT_GELU) return gelu_f(x);
+  if (act == CCF_ACT_RELU) return fmaxf(x, 0.f);
+  return x;
+}
+__device__ __forceinline__ float act_grad_f(float x, int act) {
+  if (act == CCF_ACT_GELU) return gelu_grad_f(x);
+  if (act == CCF_ACT_RELU) return x > 0.f ? 1.f : 0.f;
+  return 1.f;
+}
+
+// 32 consecutive 2-byte elements -> floats (64 bytes, 16-byte aligned)
+__device__ __forceinline__ void load32(const void* p, float (&f)[32], int fp16) {
+  const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 v = __ldg(q + i);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack2(w[j], fp16);
+      f[i * 8 + j * 2] = t.x;
+      f[i * 8 + j * 2 + 1] = t.y;
+    }
+  }
+}
+
+__device__ __forceinline__ void store32(void* p, const float (&f)[32], int fp16) {
+  uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 v;
+    v.x = pack2(f[i * 8 + 0], f[i * 8 + 1], fp16);
+    v.y = pack2(f[i * 8 + 2], f[i * 8 + 3], fp16);
+    v.z = pack2(f[i * 8 + 4], f[i * 8 + 5], fp16);
+    v.w = pack2(f[i * 8 + 6], f[i * 8 + 7], fp16);
+    q[i] = v;
+  }
+}
+
+__device__ __forceinline__ void store32_f32(float* p, const float (&f)[32]) {
+  float4* q = reinterpret_cast<float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = make_float4(f[i * 4], f[i * 4 + 1], f[i * 4 + 2], f[i * 4 + 3]);
+}
+
+__device__ __forceinline__ void acc_to_float(const uint32_t (&r)[32], float (&f)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------------------------------
+template <int kAMajor, int kBMajor, int kEpi, bool kKGroup>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                    const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                    const __grid_constant__ CcfGemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kStages * kStageBytes);
+  const uint32_t smem_base = smem_u32(smem);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_word = &ctrl->abort_word;
+  const uint64_t limit = args.wait_limit_ns;
+  constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
+
+  // ---- set-up ------------------------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&ctrl->acc_full[s]), 1);
+      mbar_init(smem_u32(&ctrl->acc_empty[s]), 4);
+    }
+    for (int s = 0; s < kSchedSlots; ++s) {
+      mbar_init(smem_u32(&ctrl->sched_full[s]), 1);
+      mbar_init(smem_u32(&ctrl->sched_empty[s]), 5);
+    }
+    ctrl->abort_word = 0;
+    const int nt = (args.n + bn_out - 1) / bn_out;
+    ctrl->n_tiles = nt;
+    if constexpr (!kKGroup) {
+      int acc = 0;
+      for (int g = 0; g < args.num_groups; ++g) {
+        ctrl->mt_prefix[g] = acc;
+        acc += (args.group_rows[g] + BM - 1) / BM;
+      }
+      ctrl->mt_prefix[args.num_groups] = acc;
+      ctrl->total_tiles = acc * nt;
+    } else {
+      ctrl->total_tiles = args.num_groups * (args.m_per_group / BM) * nt;
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+    prefetch_tensormap(&tmA0);
+    prefetch_tensormap(&tmB0);
+    if (args.kseg > 1 || kEpi == CCF_EPI_SWIGLU) {
+      prefetch_tensormap(&tmA1);
+      prefetch_tensormap(&tmB1);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const int total_tiles = ctrl->total_tiles;
+
+  // ---- dispatch role (fused all-to-all dispatch) -----------------------------------------------------
+  if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) {
+    dispatch_rows<8>(args.disp, args.status);
+    __syncthreads();
+  }
+
+  if (warp == 0) {
+    // ======================= tile scheduler + TMA producer =======================
+    int stage = 0, phase = 0, ss = 0, sphase = 0;
+    bool ok = true;
+    while (ok) {
+      if (!mbar_wait(smem_u32(&ctrl->sched_empty[ss]), sphase ^ 1, abort_word, limit)) {
+        report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 1);
+        break;
+      }
+      int t = 0;
+      if (lane == 0) t = atomicAdd(args.sched, 1);
+      t = __shfl_sync(0xffffffffu, t, 0);
+      if (t >= total_tiles) t = -1;
+      if (lane == 0) {
+        ctrl->sched_tile[ss] = t;
+        mbar_arrive(smem_u32(&ctrl->sched_full[ss]));
+      }
+      if (++ss == kSchedSlots) { ss = 0; sphase ^= 1; }
+      if (t < 0) break;
+      const Tile ti = decode_tile<kKGroup, kEpi>(t, args, ctrl);
+      if constexpr (!kKGroup) {
+        if (args.tile_flags != nullptr) {
+          // rows of this tile are pushed by other GPUs; wait until all of them have landed
+          bool arrived = true;
+          if (lane == 0) arrived = wait_flag_ge(args.tile_flags + (ti.row0 >> 7), ti.rows_valid, limit);
+          arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
+          if (!arrived) {
+            report_status(args.status, CCF_ERR_FLAG_TIMEOUT, ti.row0 >> 7);
+            *abort_word = 1;
+            break;
+          }
+          fence_proxy_async();  // generic-proxy peer stores -> async-proxy (TMA) reads
+        }
+      }
+      const int kb_per_seg = kKGroup ? ti.kblocks : (args.k + BK - 1) / BK;
+      for (int kb = 0; kb < ti.kblocks; ++kb) {
+        if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_word, limit)) {
+          report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 2);
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t fullb = smem_u32(&ctrl->full[stage]);
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+          mbar_arrive_expect_tx(fullb, kStageBytes);
+          const int seg = kKGroup ? 0 : kb / kb_per_seg;
+          const int kk = kKGroup ? 0 : (kb - seg * kb_per_seg) * BK;
+          const CUtensorMap* ma = seg ? &tmA1 : &tmA0;
+          const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
+          // A operand
+          if constexpr (kAMajor == MAJ_K) {
+            tma_load_2d(sa, ma, fullb, kk, ti.row0);
+          } else {
+            const int r = ti.krow0 + kb * BK;
+            tma_load_2d(sa, ma, fullb, ti.row0, r);
+            tma_load_2d(sa + 8192, ma, fullb, ti.row0 + 64, r);
+          }
+          // B operand
+          if constexpr (kBMajor == MAJ_K) {
+            if constexpr (kEpi == CCF_EPI_SWIGLU) {
+              const int brow = ti.g * args.b_group_rows + ti.n0;
+              tma_load_2d(sb, &tmB1, fullb, kk, brow);          // gate rows -> accumulator columns [0,128)
+              tma_load_2d(sb + 16384, &tmB0, fullb, kk, brow);  // up rows   -> accumulator columns [128,256)
+            } else {
+              tma_load_2d(sb, mb, fullb, kk, ti.g * args.b_group_rows + ti.n0);
+            }
+          } else {
+            const int r = kKGroup ? ti.krow0 + kb * BK : ti.g * args.b_group_rows + kk;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tma_load_2d(sb + i * 8192, mb, fullb, ti.n0 + 64 * i, r);
+          }
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ======================= MMA issuer =======================
+    const uint32_t idesc = make_idesc(BM, BN, args.fp16, kAMajor, kBMajor);
+    int stage = 0, phase = 0, ss = 0, sphase = 0, as = 0, aphase = 0;
+    bool ok = true;
+    while (ok) {
+      if (!mbar_wait(smem_u32(&ctrl->sched_full[ss]), sphase, abort_word, limit)) {
+        report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 3);
+        break;
+      }
+      const int t = ctrl->sched_tile[ss];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[ss]));
+      if (++ss == kSchedSlots) { ss = 0; sphase ^= 1; }
+      if (t < 0) break;
+      const Tile ti = decode_tile<kKGroup, kEpi>(t, args, ctrl);
+      if (ti.kblocks == 0) continue;  // empty group: the epilogue writes zeros
+      if (!mbar_wait(smem_u32(&ctrl->acc_empty[as]), aphase ^ 1, abort_word, limit)) {
+        report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 4);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + as * BN;
+      for (int kb = 0; kb < ti.kblocks; ++kb) {
+        if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_word, limit)) {
+          report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 5);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t da = (kAMajor == MAJ_K) ? make_smem_desc(sa + k * 32, 16, 1024)
+                                                   : make_smem_desc(sa + k * 2048, 8192, 1024);
+            const uint64_t db = (kBMajor == MAJ_K) ? make_smem_desc(sb + k * 32, 16, 1024)
+                                                   : make_smem_desc(sb + k * 2048, 8192, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&ctrl->empty[stage]));
+          if (kb == ti.kblocks - 1) umma_commit(smem_u32(&ctrl->acc_full[as]));
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      if (++as == 2) { as = 0; aphase ^= 1; }
+    }
+  } else {
+    // ======================= epilogue (warps 2..5) =======================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int fp16 = args.fp16;
+    int ss = 0, sphase = 0, as = 0, aphase = 0;
+    while (true) {
+      if (!mbar_wait(smem_u32(&ctrl->sched_full[ss]), sphase, abort_word, limit)) {
+        report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 6);
+        break;
+      }
+      const int t = ctrl->sched_tile[ss];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[ss]));
+      if (++ss == kSchedSlots) { ss = 0; sphase ^= 1; }
+      if (t < 0) break;
+      const Tile ti = decode_tile<kKGroup, kEpi>(t, args, ctrl);
+      const bool have_acc = ti.kblocks > 0;
+      if (have_acc) {
+        if (!mbar_wait(smem_u32(&ctrl->acc_full[as]), aphase, abort_word, limit)) {
+          report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 7);
+          break;
+        }
+        tc_fence_after();
+      }
+      const int r_in_tile = q * 32 + lane;
+      const bool valid = r_in_tile < ti.rows_valid;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * BN;
+      // output row (elements offset)
+      long long orow;
+      if constexpr (kKGroup) orow = static_cast<long long>(ti.g) * args.m_per_group + ti.row0 + r_in_tile;
+      else orow = static_cast<long long>(ti.row0) + r_in_tile;
+
+      // COMBINE: where this row goes
+      int c_rank = 0, c_slot = 0;
+      float c_gate = 1.f;
+      bool c_ok = false;
+      if constexpr (kEpi == CCF_EPI_COMBINE) {
+        if (valid) {
+          const int packed = args.row_src[orow];
+          c_rank = (packed >> 24) & 0xff;
+          c_slot = packed & 0xffffff;
+          c_gate = args.row_gate ? args.row_gate[orow] : 1.f;
+          c_ok = c_rank < args.world && c_slot < args.max_slots;
+          if (!c_ok) report_status(args.status, CCF_ERR_BOUNDS, static_cast<int>(orow) & 0xffffff);
+        }
+      }
+
+      constexpr int n_chunks = (kEpi == CCF_EPI_SWIGLU) ? 4 : 8;
+#pragma unroll 1
+      for (int c = 0; c < n_chunks; ++c) {
+        const int n = ti.n0 + c * 32;
+        uint32_t r[32];
+        float f[32];
+        if (have_acc) {
+          tmem_ld32(t_row + c * 32, r);
+          tmem_ld_wait();
+          acc_to_float(r, f);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = 0.f;
+        }
+        if (n >= args.n) continue;  // column edge (tile wider than the matrix)
+        if constexpr (kEpi == CCF_EPI_STORE) {
+          if (args.bias0) {
+            float b[32];
+            load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] += b[i];
+          }
+          if (valid) {
+            if (args.out_fp32) store32_f32(reinterpret_cast<float*>(args.out0) + orow * args.ld_out + n, f);
+            else store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, f, fp16);
+          }
+        } else if constexpr (kEpi == CCF_EPI_BIAS_ACT) {
+          if (args.bias0) {
+            float b[32];
+            load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] += b[i];
+          }
+          if (!valid) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = 0.f;
+          }
+          if (args.out1) store32(reinterpret_cast<uint16_t*>(args.out1) + orow * args.ld_out + n, f, fp16);
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = act_f(f[i], args.act);
+          }
+          store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, f, fp16);
+        } else if constexpr (kEpi == CCF_EPI_SWIGLU) {
+          // f = gate pre-activation (accumulator columns c*32..), u = up pre-activation (+128)
+          uint32_t ru[32];
+          float u[32];
+          if (have_acc) {
+            tmem_ld32(t_row + 128 + c * 32, ru);
+            tmem_ld_wait();
+            acc_to_float(ru, u);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) u[i] = 0.f;
+          }
+          if (args.bias1) {
+            float b[32];
+            load32(reinterpret_cast<const uint16_t*>(args.bias1) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] += b[i];
+          }
+          if (args.bias0) {
+            float b[32];
+            load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) u[i] += b[i];
+          }
+          if (!valid) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { f[i] = 0.f; u[i] = 0.f; }
+          }
+          if (args.out1) store32(reinterpret_cast<uint16_t*>(args.out1) + orow * args.ld_out + n, f, fp16);
+          if (args.out2) store32(reinterpret_cast<uint16_t*>(args.out2) + orow * args.ld_out + n, u, fp16);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float sg = 1.f / (1.f + __expf(-f[i]));
+            f[i] = f[i] * sg * u[i];
+          }
+          store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, f, fp16);
+        } else if constexpr (kEpi == CCF_EPI_COMBINE) {
+          if (args.bias0) {
+            float b[32];
+            load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] += b[i];
+          }
+          if (c_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] *= c_gate;
+            uint16_t* dst = reinterpret_cast<uint16_t*>(args.peer_comb[c_rank]) +
+                            static_cast<size_t>(c_slot) * args.ld_out + n;
+            store32(dst, f, fp16);  // peer store over NVLink (or local when c_rank is this rank)
+          }
+        } else if constexpr (kEpi == CCF_EPI_DACT) {
+          if (valid) {
+            float p[32];
+            load32(reinterpret_cast<const uint16_t*>(args.aux0) + orow * args.ld_out + n, p, fp16);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] *= act_grad_f(p[i], args.act);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = 0.f;
+          }
+          store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, f, fp16);
+        } else if constexpr (kEpi == CCF_EPI_DSWIGLU) {
+          float dg[32], du[32];
+          if (valid) {
+            float gp[32], up[32];
+            load32(reinterpret_cast<const uint16_t*>(args.aux0) + orow * args.ld_out + n, gp, fp16);
+            load32(reinterpret_cast<const uint16_t*>(args.aux1) + orow * args.ld_out + n, up, fp16);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float sg = 1.f / (1.f + __expf(-gp[i]));
+              const float silu = gp[i] * sg;
+              dg[i] = f[i] * up[i] * (sg * (1.f + gp[i] * (1.f - sg)));
+              du[i] = f[i] * silu;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { dg[i] = 0.f; du[i] = 0.f; }
+          }
+          store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, dg, fp16);
+          store32(reinterpret_cast<uint16_t*>(args.out1) + orow * args.ld_out + n, du, fp16);
+        }
+      }
+      if (have_acc) {
+        // all TMEM reads of this accumulator stage are complete: hand it back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[as]));
+        if (++as == 2) { as = 0; aphase ^= 1; }
+      }
+      if constexpr (kEpi == CCF_EPI_COMBINE) {
+        // tell every source rank how many of its rows (for this column tile) are now in its buffer
+        __threadfence_system();
+        __syncwarp();
+        for (int s = 0; s < args.world; ++s) {
+          const unsigned m = __ballot_sync(0xffffffffu, c_ok && c_rank == s);
+          if (m != 0u && lane == 0) red_release_sys_add(args.peer_done[s], __popc(m));
+        }
+      }
+    }
+  }
+
+  // ---- tear-down -----------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (ctrl->abort_word) {
+    // give copies still in flight time to land before shared memory and TMEM go away
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 50000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int done = atomicAdd(args.sched + 1, 1);
+    if (done == static_cast<int>(gridDim.x) - 1) {
+      // last CTA: every tile of this rank is finished
+      if constexpr (kEpi == CCF_EPI_COMBINE) {
+        if (args.send_finish) {
+          __threadfence_system();
+          for (int s = 0; s < args.world; ++s) red_release_sys_add(args.peer_done[s], 1);
+        }
+      }
+      args.sched[0] = 0;
+      args.sched[1] = 0;
+      args.sched[2] = 0;
+      __threadfence();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major view [rows, cols] of 2-byte elements, box = {box_cols, box_rows}, 128-byte swizzle
+static int make_tmap(CUtensorMap* m, const void* base, long long rows, long long cols, int box_cols, int box_rows,
+                     int fp16) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstr[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
+}
+
+template <int A, int B, int E, bool KG>
+static int launch_variant(const CUtensorMap* tm, const CcfGemmArgs& args, int grid, cudaStream_t stream) {
+  auto kern = grouped_gemm_kernel<A, B, E, KG>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return -static_cast<int>(e);
+    configured = true;
+  }
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(tm[0], tm[1], tm[2], tm[3], args);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+}  // namespace ccf
+
+extern "C" {
+
+struct CcfGemmLaunch {
+  CcfGemmArgs args;
+  const void* a0;
+  const void* a1;
+  const void* b0;
+  const void* b1;
+  long long a_rows, a_cols;  // 2-D views, cols contiguous
+  long long b_rows, b_cols;
+  int a_major, b_major;      // 0 = K-major, 1 = MN-major
+  int epi;                   // CcfEpilogue
+  int kgroup;                // 1 = k-grouped (wgrad)
+  int grid;                  // 0 = one CTA per SM
+  int pad0;
+};
+
+int ccf_gemm_smem_bytes() { return ccf::kSmemBytes; }
+
+// sizes of the argument blocks, so the Python mirror of the structures can be checked at load time
+int ccf_sizeof_gemm_args() { return static_cast<int>(sizeof(CcfGemmArgs)); }
+int ccf_sizeof_dispatch_args() { return static_cast<int>(sizeof(CcfDispatchArgs)); }
+int ccf_sizeof_gemm_launch() { return static_cast<int>(sizeof(CcfGemmLaunch)); }
+
+// Returns 0 on success, a negative number on a host-side error (bad combination, encode or launch failure).
+int ccf_gemm_launch(const CcfGemmLaunch* L, void* stream_v) {
+  using namespace ccf;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  const CcfGemmArgs& a = L->args;
+  if (a.num_groups < 1 || a.num_groups > CCF_MAX_GROUPS) return -2;
+  if (a.n % 32 != 0) return -3;
+  if (L->kgroup && (a.m_per_group % BM != 0)) return -4;
+  if (!L->kgroup && (a.k % 8 != 0)) return -5;
+  CUtensorMap tm[4];
+  const int fp16 = a.fp16;
+  const int a_box_rows = (L->a_major == MAJ_K) ? BM : BK;
+  int b_box_rows = (L->b_major == MAJ_K) ? BN : BK;
+  if (L->epi == CCF_EPI_SWIGLU) b_box_rows = BN / 2;
+  int rc;
+  if ((rc = make_tmap(&tm[0], L->a0, L->a_rows, L->a_cols, 64, a_box_rows, fp16))) return rc;
+  if ((rc = make_tmap(&tm[1], L->a1 ? L->a1 : L->a0, L->a_rows, L->a_cols, 64, a_box_rows, fp16))) return rc;
+  if ((rc = make_tmap(&tm[2], L->b0, L->b_rows, L->b_cols, 64, b_box_rows, fp16))) return rc;
+  if ((rc = make_tmap(&tm[3], L->b1 ? L->b1 : L->b0, L->b_rows, L->b_cols, 64, b_box_rows, fp16))) return rc;
+  int grid = L->grid;
+  if (grid <= 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    grid = sms;
+  }
+  const int key = (L->a_major << 12) | (L->b_major << 8) | (L->epi << 4) | (L->kgroup ? 1 : 0);
+  switch (key) {
+    case (MAJ_K << 12) | (MAJ_K << 8) | (CCF_EPI_STORE << 4):
+      return launch_variant<MAJ_K, MAJ_K, CCF_EPI_STORE, false>(tm, a, grid, stream);
+    case (MAJ_K << 12) | (MAJ_K << 8) | (CCF_EPI_BIAS_ACT << 4):
+      return launch_variant<MAJ_K, MAJ_K, CCF_EPI_BIAS_ACT, false>(tm, a, grid, stream);
+    case (MAJ_K << 12) | (MAJ_K << 8) | (CCF_EPI_SWIGLU << 4):
+      return launch_variant<MAJ_K, MAJ_K, CCF_EPI_SWIGLU, false>(tm, a, grid, stream);
+    case (MAJ_K << 12) | (MAJ_K << 8) | (CCF_EPI_COMBINE << 4):
+      return launch_variant<MAJ_K, MAJ_K, CCF_EPI_COMBINE, false>(tm, a, grid, stream);
+    case (MAJ_K << 12) | (MAJ_MN << 8) | (CCF_EPI_STORE << 4):
+      return launch_variant<MAJ_K, MAJ_MN, CCF_EPI_STORE, false>(tm, a, grid, stream);
+    case (MAJ_K << 12) | (MAJ_MN << 8) | (CCF_EPI_DACT << 4):
+      return launch_variant<MAJ_K, MAJ_MN, CCF_EPI_DACT, false>(tm, a, grid, stream);
+    case (MAJ_K << 12) | (MAJ_MN << 8) | (CCF_EPI_DSWIGLU << 4):
+      return launch_variant<MAJ_K, MAJ_MN, CCF_EPI_DSWIGLU, false>(tm, a, grid, stream);
+    case (MAJ_K << 12) | (MAJ_MN << 8) | (CCF_EPI_COMBINE << 4):
+      return launch_variant<MAJ_K, MAJ_MN, CCF_EPI_COMBINE, false>(tm, a, grid, stream);
+    case (MAJ_MN << 12) | (MAJ_MN << 8) | (CCF_EPI_STORE << 4) | 1:
+      return launch_variant<MAJ_MN, MAJ_MN, CCF_EPI_STORE, true>(tm, a, grid, stream);
+    default:
+      return -6;
+  }
+}
+
+}  // extern "C"

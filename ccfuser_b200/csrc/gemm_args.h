@@ -1,0 +1,95 @@
+// Argument blocks shared by the host launchers and the kernels. Plain C structs: the Python side fills
+// them through ctypes, so every field has a fixed width and the layout has no hidden padding surprises
+// (pointers first, then 64-bit, then 32-bit fields).
+#pragma once
+#include <stdint.h>
+
+#define CCF_MAX_RANKS 8
+#define CCF_MAX_GROUPS 256
+
+// Epilogues of the grouped GEMM kernel
+enum CcfEpilogue {
+  CCF_EPI_STORE = 0,     // out0 = acc (+ bias0)
+  CCF_EPI_BIAS_ACT = 1,  // out1 = acc + bias0 (pre-activation, optional), out0 = act(acc + bias0)
+  CCF_EPI_SWIGLU = 2,    // B tile = [128 gate rows | 128 up rows]; out1 = g, out2 = u, out0 = silu(g) * u
+  CCF_EPI_COMBINE = 3,   // (acc + bias0) * row_gate -> row `slot` of the source rank's combine buffer (peer store)
+  CCF_EPI_DACT = 4,      // out0 = acc * act'(aux0)
+  CCF_EPI_DSWIGLU = 5    // out0 = acc * aux1 * silu'(aux0) (d gate), out1 = acc * silu(aux0) (d up)
+};
+
+enum CcfAct { CCF_ACT_NONE = 0, CCF_ACT_GELU = 1, CCF_ACT_RELU = 2 };
+
+// status word values (low 8 bits = code, upper bits = detail such as a tile index)
+enum CcfStatus {
+  CCF_OK = 0,
+  CCF_ERR_MBAR_TIMEOUT = 1,   // a pipeline barrier inside one CTA never completed
+  CCF_ERR_FLAG_TIMEOUT = 2,   // a peer's arrival flag / counter never reached its target
+  CCF_ERR_BOUNDS = 3,         // an index failed a debug bounds check; the access was skipped
+  CCF_ERR_OVERFLOW = 4        // more rows routed to a rank than its receive buffer holds
+};
+
+// Rows pushed by the dispatch role. All peer_* pointers are addresses in *this* process' address space
+// (own memory for this rank, IPC mappings for the others).
+struct CcfDispatchArgs {
+  const void* x;            // [T, D] rows to send (2-byte elements)
+  const int* slot_expert;   // [S] expert id of each slot, S = T * top_k
+  const int* slot_pos;      // [S] position of the slot inside (this rank, expert)
+  const int* dst_base;      // [E_total] first destination row of this rank's rows of expert e on its owner
+  const float* slot_gate;   // [S] gate weight of the slot
+  const void* saved_comb;   // backward only: [S, D] scaled expert outputs saved by the forward pass
+  float* dgate;             // backward only: [S] gradient of the gate weight
+  int* slot_row;            // [S] out: destination row, -1 if dropped
+  void* peer_recv[CCF_MAX_RANKS];      // receive buffer [R, D] of every rank
+  int* peer_row_src[CCF_MAX_RANKS];    // [R] packed (source rank << 24 | slot)
+  float* peer_row_gate[CCF_MAX_RANKS]; // [R]
+  int* peer_tile_flags[CCF_MAX_RANKS]; // [R / 128] rows arrived per 128-row tile
+  int* work_counter;        // dynamic chunk counter (zero before launch; the kernel restores zero)
+  int tokens;
+  int top_k;
+  int d;                    // row length in elements (multiple of 8)
+  int capacity;
+  int experts_per_rank;
+  int my_rank;
+  int backward;             // 1: rows are scaled by the gate weight and dgate is produced
+  int fp16;                 // 1: fp16 rows, 0: bf16 rows
+  int max_rows;             // rows of a receive buffer (bounds check)
+  int pad0;
+};
+
+struct CcfGemmArgs {
+  // grouping
+  const int* group_base;    // [G] first row of each group (multiple of 128)
+  const int* group_rows;    // [G] valid rows of each group
+  const int* tile_flags;    // optional [R / 128] arrival counters gating the A tiles (row-grouped only)
+  // epilogue operands
+  void* out0;
+  void* out1;
+  void* out2;
+  const void* bias0;        // [G, N]
+  const void* bias1;        // [G, N] (swiglu gate bias)
+  const void* aux0;         // [R, N] saved pre-activation (DACT / DSWIGLU: gate pre-activation)
+  const void* aux1;         // [R, N] DSWIGLU: up pre-activation
+  const int* row_src;       // [R] COMBINE: packed (source rank << 24 | slot)
+  const float* row_gate;    // [R] COMBINE: gate weight (null = 1)
+  void* peer_comb[CCF_MAX_RANKS];   // COMBINE: combine buffer [S, N] of every rank
+  int* peer_done[CCF_MAX_RANKS];    // COMBINE: this rank's completion counter on every rank
+  int* sched;               // {tile counter, finished CTAs, spare, spare}; zero before the first launch
+  int* status;              // error word (first error wins)
+  unsigned long long wait_limit_ns;
+  long long ld_out;         // leading dimension (elements) of out0/out1/out2/aux0/aux1
+  int n;                    // output columns
+  int k;                    // reduction length per k segment (row-grouped)
+  int num_groups;
+  int m_per_group;          // k-grouped: output rows per group
+  int kseg;                 // 1 or 2 reduction segments (second one uses the *1 tensor maps)
+  int b_group_rows;         // rows of one group inside B's 2-D view
+  int act;                  // CcfAct
+  int fp16;                 // operand/output element type: 1 fp16, 0 bf16
+  int out_fp32;             // EPI_STORE: write fp32
+  int world;                // COMBINE: number of ranks
+  int send_finish;          // COMBINE: the last CTA adds 1 to every rank's completion counter
+  int n_comm_ctas;          // CTAs that run the dispatch role before taking GEMM tiles (0 = none)
+  int max_slots;            // COMBINE: rows of a combine buffer (bounds check)
+  int pad0;
+  CcfDispatchArgs disp;
+};

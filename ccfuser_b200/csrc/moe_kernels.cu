@@ -1,0 +1,459 @@
+// Routing, planning, dispatch, combine-reduce and bias-gradient kernels of the fused MoE layer.
+// Everything here is bandwidth- or latency-bound glue around the tcgen05 GEMMs in gemm.cu; nothing
+// involves the host (the reference plans on the CPU in Python, mix_moe/mix_moe/transformer.py:150-250,
+// after a count all-gather and two device-to-host copies, mix_moe/mix_moe/functions.py:83-105).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "dispatch.cuh"
+#include "gemm_args.h"
+#include "sm100.cuh"
+
+namespace ccf {
+
+// ---------------------------------------------------------------------------------------------------
+// gate: top-k over E logits + softmax over the k selected values, one warp per token
+// (mix_moe/mix_moe/gates/naive_gate.py:31-38). Ties go to the lower expert id.
+// ---------------------------------------------------------------------------------------------------
+template <int kMaxPerLane>
+__global__ void topk_softmax_kernel(const void* logits, int fp16, int is_f32, int T, int E, int K, int* idx_out,
+                                    float* w_out) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  float v[kMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int e = i * 32 + lane;
+    float x = -INFINITY;
+    if (e < E) {
+      if (is_f32) x = reinterpret_cast<const float*>(logits)[static_cast<size_t>(warp) * E + e];
+      else if (fp16) x = __half2float(reinterpret_cast<const __half*>(logits)[static_cast<size_t>(warp) * E + e]);
+      else x = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[static_cast<size_t>(warp) * E + e]);
+    }
+    v[i] = x;
+  }
+  float sel_v[8];
+  int sel_i[8];
+  for (int j = 0; j < K; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+      const int e = i * 32 + lane;
+      if (e < E && (v[i] > best || (v[i] == best && e < bi))) { best = v[i]; bi = e; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    sel_v[j] = best;
+    sel_i[j] = bi;
+    // remove the winner (unrolled select keeps v[] in registers)
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i)
+      if ((bi & 31) == lane && (bi >> 5) == i) v[i] = -INFINITY;
+  }
+  if (lane == 0) {
+    const float mx = sel_v[0];
+    float sum = 0.f;
+    for (int j = 0; j < K; ++j) { sel_v[j] = __expf(sel_v[j] - mx); sum += sel_v[j]; }
+    for (int j = 0; j < K; ++j) {
+      idx_out[static_cast<size_t>(warp) * K + j] = sel_i[j];
+      w_out[static_cast<size_t>(warp) * K + j] = sel_v[j] / sum;
+    }
+  }
+}
+
+// dlogits[t, idx_j] = w_j * (dw_j - sum_i w_i dw_i), zero elsewhere. One thread per token.
+__global__ void topk_softmax_bwd_kernel(const int* idx, const float* w, const float* dw, int T, int E, int K,
+                                        void* dlogits, int fp16, int is_f32) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float dot = 0.f;
+  for (int j = 0; j < K; ++j) dot += w[static_cast<size_t>(t) * K + j] * dw[static_cast<size_t>(t) * K + j];
+  for (int j = 0; j < K; ++j) {
+    const float g = w[static_cast<size_t>(t) * K + j] * (dw[static_cast<size_t>(t) * K + j] - dot);
+    const size_t o = static_cast<size_t>(t) * E + idx[static_cast<size_t>(t) * K + j];
+    if (is_f32) reinterpret_cast<float*>(dlogits)[o] = g;
+    else if (fp16) reinterpret_cast<__half*>(dlogits)[o] = __float2half(g);
+    else reinterpret_cast<__nv_bfloat16*>(dlogits)[o] = __float2bfloat16(g);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// deterministic position of every slot inside its expert (prefix count in slot order), counts, capacity
+// (replaces expert_count_kernel + assign_pos_kernel, mix_moe/csrc/cuda/local_exchange.cu:6-70)
+// ---------------------------------------------------------------------------------------------------
+constexpr int kRouteBlock = 1024;
+
+__global__ void __launch_bounds__(kRouteBlock)
+route_hist_kernel(const int* __restrict__ expert, int S, int E, int cap, int* pos, int* block_hist, int* block_off,
+                  int* count_raw, int* count_kept, int* ticket) {
+  __shared__ int wh[32][CCF_MAX_GROUPS];
+  __shared__ int is_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nb = gridDim.x;
+  for (int i = tid; i < 32 * CCF_MAX_GROUPS; i += kRouteBlock) (&wh[0][0])[i] = 0;
+  __syncthreads();
+  const int s = blockIdx.x * kRouteBlock + tid;
+  int e = (s < S) ? expert[s] : -1;
+  if (e < 0 || e >= E) e = -1;
+  const unsigned m = __match_any_sync(0xffffffffu, e);
+  const int rank = __popc(m & ((1u << lane) - 1u));
+  if (e >= 0 && rank == 0) wh[warp][e] = __popc(m);
+  __syncthreads();
+  if (tid < E) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = wh[w][tid];
+      wh[w][tid] = run;
+      run += c;
+    }
+    block_hist[blockIdx.x * E + tid] = run;
+  }
+  __syncthreads();
+  if (s < S) pos[s] = (e >= 0) ? wh[warp][e] + rank : 0x3fffffff;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = (atomicAdd(ticket, 1) == nb - 1);
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    if (tid < E) {
+      int run = 0;
+      for (int b = 0; b < nb; ++b) {
+        const int c = __ldcg(block_hist + b * E + tid);
+        block_off[b * E + tid] = run;
+        run += c;
+      }
+      count_raw[tid] = run;
+      count_kept[tid] = min(run, cap);
+    }
+    if (tid == 0) *ticket = 0;
+  }
+}
+
+__global__ void route_pos_kernel(const int* __restrict__ expert, int S, int E, const int* __restrict__ block_off,
+                                 int* pos) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= S) return;
+  const int e = expert[s];
+  if (e >= 0 && e < E) pos[s] += block_off[(s / kRouteBlock) * E + e];
+}
+
+// ---------------------------------------------------------------------------------------------------
+// count exchange + plan. One CTA. Every rank writes its kept counts into every rank's table (peer
+// stores + release flag carrying the step epoch), waits (bounded) for all rows of its own table, then
+// computes the row layout of every owner's receive buffer:
+//   rows of expert e start at base[e] (multiple of 128) on owner e / E_loc,
+//   rows sent by source r start at base[e] + sum_{r' < r} count[r'][e].
+// Replaces the NCCL all-gather + .cpu() + Python block planner of the reference
+// (mix_moe/csrc/cuda/global_exchange.cpp:139-177, mix_moe/mix_moe/transformer.py:150-250).
+// ---------------------------------------------------------------------------------------------------
+struct PlanArgs {
+  const int* count_kept;               // [E_total] this rank's kept rows per expert
+  int* peer_table[CCF_MAX_RANKS];      // count table [W, E_total] of every rank
+  int* peer_flag[CCF_MAX_RANKS];       // epoch flags [W] of every rank
+  int* dst_base;                       // out [E_total]
+  int* group_base;                     // out [E_loc]
+  int* group_rows;                     // out [E_loc]
+  int* sent_rows;                      // out [W] kept rows this rank sends to each owner
+  int* table_copy;                     // out [W, E_total] snapshot of the table (routing statistics)
+  int* status;
+  unsigned long long wait_limit_ns;
+  int world, my_rank, e_total, e_loc, epoch, max_rows;
+};
+
+__global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanArgs a) {
+  __shared__ int rows[CCF_MAX_GROUPS];
+  __shared__ int myoff[CCF_MAX_GROUPS];
+  __shared__ int base[CCF_MAX_GROUPS];
+  __shared__ int failed;
+  const int tid = threadIdx.x;
+  if (tid == 0) failed = 0;
+  // 1. publish my counts
+  for (int i = tid; i < a.world * a.e_total; i += blockDim.x) {
+    const int p = i / a.e_total, e = i - p * a.e_total;
+    a.peer_table[p][a.my_rank * a.e_total + e] = a.count_kept[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < a.world) st_release_sys(a.peer_flag[tid] + a.my_rank, a.epoch);
+  // 2. wait for everyone's counts (my own table, local memory)
+  if (tid < a.world) {
+    if (!wait_flag_ge(a.peer_flag[a.my_rank] + tid, a.epoch, a.wait_limit_ns)) {
+      report_status(a.status, CCF_ERR_FLAG_TIMEOUT, 0x800000 | tid);
+      failed = 1;
+    }
+  }
+  __syncthreads();
+  if (failed) {
+    for (int e = tid; e < a.e_total; e += blockDim.x) a.dst_base[e] = 0;
+    for (int e = tid; e < a.e_loc; e += blockDim.x) { a.group_base[e] = 0; a.group_rows[e] = 0; }
+    if (tid < a.world) a.sent_rows[tid] = 0;
+    return;
+  }
+  // 3. plan
+  const int* table = a.peer_table[a.my_rank];
+  for (int e = tid; e < a.e_total; e += blockDim.x) {
+    int tot = 0, off = 0;
+    for (int r = 0; r < a.world; ++r) {
+      const int c = ld_relaxed_sys(table + r * a.e_total + e);
+      if (a.table_copy) a.table_copy[r * a.e_total + e] = c;
+      if (r < a.my_rank) off += c;
+      tot += c;
+    }
+    rows[e] = tot;
+    myoff[e] = off;
+  }
+  __syncthreads();
+  if (tid < a.world) {
+    int run = 0, sent = 0;
+    for (int i = 0; i < a.e_loc; ++i) {
+      const int e = tid * a.e_loc + i;
+      base[e] = run;
+      run += (rows[e] + 127) & ~127;
+      sent += a.count_kept[e];
+    }
+    a.sent_rows[tid] = sent;
+    if (run > a.max_rows) report_status(a.status, CCF_ERR_OVERFLOW, tid);
+  }
+  __syncthreads();
+  for (int e = tid; e < a.e_total; e += blockDim.x) a.dst_base[e] = base[e] + myoff[e];
+  for (int i = tid; i < a.e_loc; i += blockDim.x) {
+    const int e = a.my_rank * a.e_loc + i;
+    a.group_base[i] = base[e];
+    a.group_rows[i] = min(rows[e], max(0, a.max_rows - base[e]));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// stand-alone dispatch kernel (the same role also runs inside the fused GEMM kernel)
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) dispatch_kernel(const __grid_constant__ CcfDispatchArgs a, int* status,
+                                                       int* done_ctas) {
+  dispatch_rows<8>(a, status);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_ctas, 1) == static_cast<int>(gridDim.x) - 1) {
+      *a.work_counter = 0;
+      *done_ctas = 0;
+      __threadfence();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// combine: wait until every owner has stored all rows of this rank (and finished its kernel), then
+// sum the top-k slots of each token. Counters are monotonic; `cum` holds the value already consumed.
+// ---------------------------------------------------------------------------------------------------
+__global__ void combine_wait_kernel(const int* done, int* cum, const int* sent_rows, int n_tiles, int world,
+                                    unsigned long long limit_ns, int* status) {
+  const int o = threadIdx.x;
+  if (o >= world) return;
+  const int target = cum[o] + sent_rows[o] * n_tiles + 1;
+  if (!wait_flag_ge(done + o, target, limit_ns)) report_status(status, CCF_ERR_FLAG_TIMEOUT, 0x400000 | o);
+  cum[o] = target;
+}
+
+// y[t, :] = sum_j keep(t, j) * comb[t * k + j, :]; one warp per token, 16-byte vectors, fp32 accumulate.
+__global__ void combine_reduce_kernel(const void* comb, const int* slot_row, void* y, int T, int K, int d, int fp16) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  const int vecs = d >> 3;
+  const uint4* c = reinterpret_cast<const uint4*>(comb);
+  uint4* out = reinterpret_cast<uint4*>(y) + static_cast<size_t>(warp) * vecs;
+  for (int v = lane; v < vecs; v += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < K; ++j) {
+      const int s = warp * K + j;
+      if (slot_row[s] < 0) continue;
+      const uint4 x = c[static_cast<size_t>(s) * vecs + v];
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = unpack2(w[q], fp16);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack2(acc[0], acc[1], fp16);
+    o.y = pack2(acc[2], acc[3], fp16);
+    o.z = pack2(acc[4], acc[5], fp16);
+    o.w = pack2(acc[6], acc[7], fp16);
+    out[v] = o;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// bias gradients: out[g, n] = sum over the rows of group g of x[r, n]. Block = 128 columns x 8 row lanes.
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) colsum_grouped_kernel(const void* x, long long ld, int n, const int* group_base,
+                                                             const int* group_rows, void* out, int fp16) {
+  __shared__ float red[8][128];
+  const int g = blockIdx.y;
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 128 + cx * 4;
+  float acc[4] = {0, 0, 0, 0};
+  if (col < n) {
+    const int r0 = group_base[g], nr = group_rows[g];
+    const uint16_t* base = reinterpret_cast<const uint16_t*>(x);
+    for (int r = ry; r < nr; r += 8) {
+      const uint2 v = *reinterpret_cast<const uint2*>(base + static_cast<size_t>(r0 + r) * ld + col);
+      const float2 a = unpack2(v.x, fp16), b = unpack2(v.y, fp16);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) red[ry][cx * 4 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    if (c < n) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += red[i][threadIdx.x];
+      if (fp16) reinterpret_cast<__half*>(out)[static_cast<size_t>(g) * n + c] = __float2half(s);
+      else reinterpret_cast<__nv_bfloat16*>(out)[static_cast<size_t>(g) * n + c] = __float2bfloat16(s);
+    }
+  }
+}
+
+// A wait that nothing satisfies unless `flag` already holds `target`: used to exercise the timeout path.
+__global__ void wait_probe_kernel(const int* flag, int target, unsigned long long limit_ns, int* status) {
+  if (!wait_flag_ge(flag, target, limit_ns)) report_status(status, CCF_ERR_FLAG_TIMEOUT, 0x123);
+}
+
+}  // namespace ccf
+
+// ---------------------------------------------------------------------------------------------------
+// C entry points
+// ---------------------------------------------------------------------------------------------------
+extern "C" {
+
+static int last_err() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+int ccf_topk_softmax(const void* logits, int fp16, int is_f32, int T, int E, int K, int* idx, float* w, void* stream) {
+  if (E > 256 || K > 8 || K < 1) return -2;
+  if (T == 0) return 0;
+  const int threads = 256, blocks = (T * 32 + threads - 1) / threads;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (E <= 64) ccf::topk_softmax_kernel<2><<<blocks, threads, 0, st>>>(logits, fp16, is_f32, T, E, K, idx, w);
+  else if (E <= 128) ccf::topk_softmax_kernel<4><<<blocks, threads, 0, st>>>(logits, fp16, is_f32, T, E, K, idx, w);
+  else ccf::topk_softmax_kernel<8><<<blocks, threads, 0, st>>>(logits, fp16, is_f32, T, E, K, idx, w);
+  return last_err();
+}
+
+int ccf_topk_softmax_bwd(const int* idx, const float* w, const float* dw, int T, int E, int K, void* dlogits, int fp16,
+                         int is_f32, void* stream) {
+  if (T == 0) return 0;
+  ccf::topk_softmax_bwd_kernel<<<(T + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      idx, w, dw, T, E, K, dlogits, fp16, is_f32);
+  return last_err();
+}
+
+// scratch: block_hist [nb*E] + block_off [nb*E] ints, ticket 1 int (zero before the first call)
+int ccf_route(const int* expert, int S, int E, int cap, int* pos, int* block_hist, int* block_off, int* count_raw,
+              int* count_kept, int* ticket, void* stream) {
+  if (E > CCF_MAX_GROUPS) return -2;
+  if (S == 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int nb = (S + ccf::kRouteBlock - 1) / ccf::kRouteBlock;
+  ccf::route_hist_kernel<<<nb, ccf::kRouteBlock, 0, st>>>(expert, S, E, cap, pos, block_hist, block_off, count_raw,
+                                                          count_kept, ticket);
+  ccf::route_pos_kernel<<<(S + 255) / 256, 256, 0, st>>>(expert, S, E, block_off, pos);
+  return last_err();
+}
+
+int ccf_sizeof_plan_args() { return static_cast<int>(sizeof(ccf::PlanArgs)); }
+
+int ccf_plan(const ccf::PlanArgs* a, void* stream) {
+  if (a->e_total > CCF_MAX_GROUPS || a->world > CCF_MAX_RANKS) return -2;
+  ccf::plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
+  return last_err();
+}
+
+int ccf_dispatch(const CcfDispatchArgs* a, int* status, int* done_ctas, int grid, void* stream) {
+  if (a->d % 8 != 0) return -2;
+  if (grid <= 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    grid = sms * 2;
+  }
+  ccf::dispatch_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a, status, done_ctas);
+  return last_err();
+}
+
+int ccf_combine_wait(const int* done, int* cum, const int* sent_rows, int n_tiles, int world,
+                     unsigned long long limit_ns, int* status, void* stream) {
+  ccf::combine_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(done, cum, sent_rows, n_tiles, world,
+                                                                                 limit_ns, status);
+  return last_err();
+}
+
+int ccf_combine_reduce(const void* comb, const int* slot_row, void* y, int T, int K, int d, int fp16, void* stream) {
+  if (d % 8 != 0) return -2;
+  if (T == 0) return 0;
+  const int threads = 256, blocks = (T * 32 + threads - 1) / threads;
+  ccf::combine_reduce_kernel<<<blocks, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(comb, slot_row, y, T, K,
+                                                                                             d, fp16);
+  return last_err();
+}
+
+int ccf_colsum_grouped(const void* x, long long ld, int n, int groups, const int* group_base, const int* group_rows,
+                       void* out, int fp16, void* stream) {
+  if (n % 4 != 0) return -2;
+  dim3 grid((n + 127) / 128, groups);
+  ccf::colsum_grouped_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, ld, n, group_base,
+                                                                                        group_rows, out, fp16);
+  return last_err();
+}
+
+int ccf_wait_probe(const int* flag, int target, unsigned long long limit_ns, int* status, void* stream) {
+  ccf::wait_probe_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, target, limit_ns, status);
+  return last_err();
+}
+
+// ---- symmetric memory: plain device allocations shared through CUDA IPC ------------------------------
+// The allocator stands in for nvshmem_malloc of the reference (mix_moe/csrc/mix_moe.h:75-77): every rank
+// allocates the same size, exports a handle, and maps every peer's allocation, which gives the
+// peer_base[rank] table the kernels index (the role of NVSHMEM's peer_heap_base).
+int ccf_symm_alloc(unsigned long long bytes, void** ptr) {
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  e = cudaMemset(*ptr, 0, bytes);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+int ccf_symm_free(void* ptr) { return -static_cast<int>(cudaFree(ptr)); }
+int ccf_symm_handle_bytes() { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
+int ccf_symm_get_handle(void* ptr, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  memcpy(handle_out, &h, sizeof(h));
+  return 0;
+}
+int ccf_symm_open_handle(const void* handle, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+int ccf_symm_close_handle(void* ptr) { return -static_cast<int>(cudaIpcCloseMemHandle(ptr)); }
+
+const char* ccf_error_string(int neg_code) { return cudaGetErrorString(static_cast<cudaError_t>(-neg_code)); }
+
+}  // extern "C"

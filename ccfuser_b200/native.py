@@ -1,0 +1,159 @@
+"""ctypes binding of the in-tree CUDA library (``ccfuser_b200/lib/libccfuser_b200.so``).
+
+The library exposes plain ``extern "C"`` launchers that take raw device pointers and a stream handle;
+the structures below mirror ``csrc/gemm_args.h`` field by field. On a machine with a GPU a missing
+library is an error, never a silent fallback to a torch implementation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+MAX_RANKS = 8
+MAX_GROUPS = 256
+
+EPI_STORE, EPI_BIAS_ACT, EPI_SWIGLU, EPI_COMBINE, EPI_DACT, EPI_DSWIGLU = range(6)
+ACT_NONE, ACT_GELU, ACT_RELU = range(3)
+MAJ_K, MAJ_MN = 0, 1
+ACT_CODE = {"gelu": ACT_GELU, "relu": ACT_RELU, "none": ACT_NONE, "swiglu": ACT_NONE}
+
+ERR_NAMES = {1: "pipeline barrier timeout", 2: "peer flag timeout", 3: "bounds check", 4: "receive buffer overflow"}
+
+_vp = C.c_void_p
+
+
+class DispatchArgs(C.Structure):
+    _fields_ = [
+        ("x", _vp), ("slot_expert", _vp), ("slot_pos", _vp), ("dst_base", _vp), ("slot_gate", _vp),
+        ("saved_comb", _vp), ("dgate", _vp), ("slot_row", _vp),
+        ("peer_recv", _vp * MAX_RANKS), ("peer_row_src", _vp * MAX_RANKS),
+        ("peer_row_gate", _vp * MAX_RANKS), ("peer_tile_flags", _vp * MAX_RANKS),
+        ("work_counter", _vp),
+        ("tokens", C.c_int), ("top_k", C.c_int), ("d", C.c_int), ("capacity", C.c_int),
+        ("experts_per_rank", C.c_int), ("my_rank", C.c_int), ("backward", C.c_int), ("fp16", C.c_int),
+        ("max_rows", C.c_int), ("pad0", C.c_int),
+    ]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("group_base", _vp), ("group_rows", _vp), ("tile_flags", _vp),
+        ("out0", _vp), ("out1", _vp), ("out2", _vp), ("bias0", _vp), ("bias1", _vp), ("aux0", _vp), ("aux1", _vp),
+        ("row_src", _vp), ("row_gate", _vp),
+        ("peer_comb", _vp * MAX_RANKS), ("peer_done", _vp * MAX_RANKS),
+        ("sched", _vp), ("status", _vp),
+        ("wait_limit_ns", C.c_ulonglong), ("ld_out", C.c_longlong),
+        ("n", C.c_int), ("k", C.c_int), ("num_groups", C.c_int), ("m_per_group", C.c_int), ("kseg", C.c_int),
+        ("b_group_rows", C.c_int), ("act", C.c_int), ("fp16", C.c_int), ("out_fp32", C.c_int), ("world", C.c_int),
+        ("send_finish", C.c_int), ("n_comm_ctas", C.c_int), ("max_slots", C.c_int), ("pad0", C.c_int),
+        ("disp", DispatchArgs),
+    ]
+
+
+class GemmLaunch(C.Structure):
+    _fields_ = [
+        ("args", GemmArgs),
+        ("a0", _vp), ("a1", _vp), ("b0", _vp), ("b1", _vp),
+        ("a_rows", C.c_longlong), ("a_cols", C.c_longlong), ("b_rows", C.c_longlong), ("b_cols", C.c_longlong),
+        ("a_major", C.c_int), ("b_major", C.c_int), ("epi", C.c_int), ("kgroup", C.c_int), ("grid", C.c_int),
+        ("pad0", C.c_int),
+    ]
+
+
+class PlanArgs(C.Structure):
+    _fields_ = [
+        ("count_kept", _vp), ("peer_table", _vp * MAX_RANKS), ("peer_flag", _vp * MAX_RANKS),
+        ("dst_base", _vp), ("group_base", _vp), ("group_rows", _vp), ("sent_rows", _vp), ("table_copy", _vp),
+        ("status", _vp), ("wait_limit_ns", C.c_ulonglong),
+        ("world", C.c_int), ("my_rank", C.c_int), ("e_total", C.c_int), ("e_loc", C.c_int), ("epoch", C.c_int),
+        ("max_rows", C.c_int),
+    ]
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def lib_path() -> str:
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libccfuser_b200.so")
+
+
+def load(build_if_missing: bool = True):
+    """Load (building first if the sources are newer and nvcc exists) and return the ctypes library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = lib_path()
+        if build_if_missing:
+            from . import build as _build
+            try:
+                if _build.needs_build():
+                    _build.build()
+            except Exception:
+                if not os.path.exists(path):
+                    raise
+        if not os.path.exists(path):
+            raise RuntimeError(f"{path} is missing: run `python -m ccfuser_b200.build` (needs nvcc, sm_100a)")
+        lib = C.CDLL(path)
+        _declare(lib)
+        for name, struct in (("gemm_args", GemmArgs), ("dispatch_args", DispatchArgs),
+                             ("gemm_launch", GemmLaunch), ("plan_args", PlanArgs)):
+            want = getattr(lib, "ccf_sizeof_" + name)()
+            if want != C.sizeof(struct):
+                raise RuntimeError(f"ctypes mirror of {name} is {C.sizeof(struct)} bytes, library has {want}")
+        _lib = lib
+        return lib
+
+
+def _declare(lib):
+    i, p, ull, ll = C.c_int, _vp, C.c_ulonglong, C.c_longlong
+    sig = {
+        "ccf_gemm_launch": ([C.POINTER(GemmLaunch), p], i),
+        "ccf_gemm_smem_bytes": ([], i),
+        "ccf_topk_softmax": ([p, i, i, i, i, i, p, p, p], i),
+        "ccf_topk_softmax_bwd": ([p, p, p, i, i, i, p, i, i, p], i),
+        "ccf_route": ([p, i, i, i, p, p, p, p, p, p, p], i),
+        "ccf_plan": ([C.POINTER(PlanArgs), p], i),
+        "ccf_dispatch": ([C.POINTER(DispatchArgs), p, p, i, p], i),
+        "ccf_combine_wait": ([p, p, p, i, i, ull, p, p], i),
+        "ccf_combine_reduce": ([p, p, p, i, i, i, i, p], i),
+        "ccf_colsum_grouped": ([p, ll, i, i, p, p, p, i, p], i),
+        "ccf_wait_probe": ([p, i, ull, p, p], i),
+        "ccf_symm_alloc": ([ull, C.POINTER(p)], i),
+        "ccf_symm_free": ([p], i),
+        "ccf_symm_handle_bytes": ([], i),
+        "ccf_symm_get_handle": ([p, p], i),
+        "ccf_symm_open_handle": ([p, C.POINTER(p)], i),
+        "ccf_symm_close_handle": ([p], i),
+        "ccf_error_string": ([i], C.c_char_p),
+    }
+    for name, (argtypes, restype) in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = restype
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        msg = ""
+        if -1000 < rc < 0:
+            try:
+                msg = load().ccf_error_string(rc).decode()
+            except Exception:
+                pass
+        raise RuntimeError(f"{what} failed with code {rc} {msg}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int:
+    """Device address of a tensor (0 for None)."""
+    return 0 if t is None else t.data_ptr()

@@ -1,0 +1,118 @@
+"""Python launchers of the tcgen05 grouped GEMM (csrc/gemm.cu).
+
+All tensors are 2-byte (bf16 or fp16) CUDA tensors except where noted. ``group_base`` / ``group_rows`` are
+int32 device tensors: rows of group ``g`` are ``[group_base[g], group_base[g] + group_rows[g])`` and every
+base is a multiple of 128.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from .. import native as N
+
+
+class Workspace:
+    """Per-device scratch the kernels share: tile scheduler counters and the status word."""
+
+    _by_device = {}
+
+    def __init__(self, device):
+        self.sched = torch.zeros(8, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.dispatch_done = torch.zeros(1, dtype=torch.int32, device=device)
+
+    @classmethod
+    def get(cls, device) -> "Workspace":
+        device = torch.device(device)
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        ws = cls._by_device.get(key)
+        if ws is None:
+            ws = cls._by_device[key] = Workspace(device)
+        return ws
+
+    def check(self, what: str = "kernel"):
+        """Host read of the status word; raises if a kernel recorded an error, then clears it."""
+        v = int(self.status.item())
+        if v:
+            self.status.zero_()
+            code, detail = v & 0xff, v >> 8
+            from ..errors import MoECommError, MoECommTimeout, MoEOverflow
+            msg = f"{what}: {N.ERR_NAMES.get(code, 'error')} (code {code}, detail {detail:#x})"
+            if code in (1, 2):
+                raise MoECommTimeout(msg, where=what, tile=detail)
+            if code == 4:
+                raise MoEOverflow(msg)
+            raise MoECommError(msg)
+
+
+DEFAULT_WAIT_NS = 5_000_000_000
+
+
+def _is_fp16(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return 1
+    if t.dtype == torch.bfloat16:
+        return 0
+    raise TypeError(f"grouped GEMM operands must be bf16 or fp16, got {t.dtype}")
+
+
+def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num_groups,
+           a1=None, b1=None, kgroup=False, m_per_group=0, kseg=1, b_group_rows=0,
+           out0=None, out1=None, out2=None, bias0=None, bias1=None, aux0=None, aux1=None, ld_out=None,
+           act=N.ACT_NONE, out_fp32=False, tile_flags=None, row_src=None, row_gate=None,
+           peer_comb=None, peer_done=None, world=1, send_finish=0, max_slots=0,
+           dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, wait_ns=DEFAULT_WAIT_NS, grid=0,
+           workspace: Optional[Workspace] = None):
+    """Fill a CcfGemmLaunch and launch on the current stream. a0/b0 are 2-D contiguous views."""
+    lib = N.load()
+    ws = workspace or Workspace.get(a0.device)
+    L = N.GemmLaunch()
+    g = L.args
+    g.group_base, g.group_rows = N.ptr(group_base), N.ptr(group_rows)
+    g.tile_flags = N.ptr(tile_flags)
+    g.out0, g.out1, g.out2 = N.ptr(out0), N.ptr(out1), N.ptr(out2)
+    g.bias0, g.bias1, g.aux0, g.aux1 = N.ptr(bias0), N.ptr(bias1), N.ptr(aux0), N.ptr(aux1)
+    g.row_src, g.row_gate = N.ptr(row_src), N.ptr(row_gate)
+    if peer_comb is not None:
+        for i, v in enumerate(peer_comb):
+            g.peer_comb[i] = v
+    if peer_done is not None:
+        for i, v in enumerate(peer_done):
+            g.peer_done[i] = v
+    g.sched, g.status = ws.sched.data_ptr(), ws.status.data_ptr()
+    g.wait_limit_ns = int(wait_ns)
+    g.ld_out = int(ld_out if ld_out is not None else n)
+    g.n, g.k, g.num_groups, g.m_per_group, g.kseg = int(n), int(k), int(num_groups), int(m_per_group), int(kseg)
+    g.b_group_rows, g.act, g.fp16, g.out_fp32 = int(b_group_rows), int(act), _is_fp16(a0), int(bool(out_fp32))
+    g.world, g.send_finish, g.n_comm_ctas, g.max_slots = int(world), int(send_finish), int(n_comm_ctas), int(max_slots)
+    if dispatch is not None:
+        g.disp = dispatch
+        g.disp.work_counter = ws.sched.data_ptr() + 8
+    assert a0.dim() == 2 and b0.dim() == 2 and a0.is_contiguous() and b0.is_contiguous()
+    L.a0, L.a1, L.b0, L.b1 = N.ptr(a0), N.ptr(a1), N.ptr(b0), N.ptr(b1)
+    L.a_rows, L.a_cols = a0.shape
+    L.b_rows, L.b_cols = b0.shape
+    L.a_major, L.b_major, L.epi, L.kgroup, L.grid = int(a_major), int(b_major), int(epi), int(bool(kgroup)), int(grid)
+    N.check(lib.ccf_gemm_launch(C.byref(L), N.stream_ptr()), "ccf_gemm_launch")
+    return ws
+
+
+def single_group(rows: int, device):
+    """group_base / group_rows of an ungrouped GEMM with `rows` rows."""
+    return (torch.zeros(1, dtype=torch.int32, device=device),
+            torch.full((1,), rows, dtype=torch.int32, device=device))
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out_fp32: bool = False):
+    """y = x @ w.T (+ bias) for 2-D x [M,K], w [N,K]; plain (ungrouped) use of the kernel."""
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty(m, n, dtype=torch.float32 if out_fp32 else x.dtype, device=x.device)
+    gb, gr = single_group(m, x.device)
+    launch(a0=x.contiguous(), b0=w.contiguous(), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_STORE, n=n, k=k,
+           group_base=gb, group_rows=gr, num_groups=1, b_group_rows=n, out0=out,
+           bias0=None if bias is None else bias.contiguous(), out_fp32=out_fp32)
+    return out

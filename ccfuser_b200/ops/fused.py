@@ -1,0 +1,374 @@
+"""The fused expert-parallel forward and backward of one MoE FFN layer on sm_100a.
+
+Per call, on every rank (nothing touches the host, nothing calls a library collective):
+
+    route        top-k softmax kernel -> deterministic positions and kept counts per expert
+    plan         kept counts are stored into every rank's count table (peer stores + epoch flag); each
+                 rank derives the dense row layout of every owner's receive buffer
+    GEMM-1       ONE kernel: its first CTAs push this rank's routed rows into the owners' receive buffers
+                 (peer stores, per-128-row-tile arrival counters); all CTAs then run tcgen05 tiles, each
+                 tile starting as soon as its rows have landed; epilogue = bias + activation
+    GEMM-2       tcgen05 tiles; the epilogue adds the bias, multiplies by the gate weight and stores each
+                 row into the combine buffer of the rank the token came from, then bumps that rank's
+                 completion counter
+    reduce       the source waits for its counters and sums the k slots of every token
+
+Backward mirrors it: g*dy rows are pushed (same kernel as dgrad-2, whose epilogue applies the activation
+derivative), wgrad-2 / wgrad-1 reduce over the saved rows with MN-major operands, dgrad-1's epilogue
+stores dx rows into the source's buffer.
+
+Call stack being replaced: mix_moe/mix_moe/linear.py:60-173 (MixMOELinear1/2 autograd functions) ->
+mix_moe/csrc/mix_moe.h:236-505 (first/second_gemm_forward/backward) -> mix_moe/csrc/cuda/mix_gemm.cu.
+Buffer hazards between calls are covered by the completion counters: a rank cannot start the dispatch of
+call i+1 before every owner has finished the last kernel of call i, so one receive buffer per role is
+enough (the reference aliases one buffer for everything and separates uses with global barriers,
+mix_moe/csrc/mix_moe.h:271,336,420,467).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+from .. import native as N
+from ..config import env_flag
+from ..parallel.symm import SymmBuffer
+from . import gemm as G
+
+TILE = 128
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class CommContext:
+    """Symmetric state shared by all fused layers of one expert-parallel group: backward receive and
+    combine buffers, row metadata, tile arrival counters, the count table and the completion counters."""
+
+    _instances: Dict[tuple, "CommContext"] = {}
+
+    def __init__(self, group, world, rank, device, max_rows, max_slots, d_model, e_total, dtype):
+        self.group, self.world, self.rank, self.device = group, world, rank, device
+        self.max_rows, self.max_slots, self.d_model, self.e_total, self.dtype = max_rows, max_slots, d_model, e_total, dtype
+        esz = 2
+        sizes = {
+            "grecv": max_rows * d_model * esz,
+            "gcomb": max_slots * d_model * esz,
+            "row_src": max_rows * 4,
+            "row_gate": max_rows * 4,
+            "tile_flags": (max_rows // TILE + 1) * 4,
+            "cnt_table": world * e_total * 4,
+            "cnt_flag": N.MAX_RANKS * 4,
+            "done": N.MAX_RANKS * 4,
+        }
+        total = sum(_round_up(v, 1024) for v in sizes.values()) + 1024
+        self.buf = SymmBuffer(total, group if world > 1 else None, device)
+        self.off = {k: self.buf.carve(v) for k, v in sizes.items()}
+        v = self.buf.view
+        self.grecv = v(self.off["grecv"], (max_rows, d_model), dtype)
+        self.gcomb = v(self.off["gcomb"], (max_slots, d_model), dtype)
+        self.row_src = v(self.off["row_src"], (max_rows,), torch.int32)
+        self.row_gate = v(self.off["row_gate"], (max_rows,), torch.float32)
+        self.tile_flags = v(self.off["tile_flags"], (max_rows // TILE + 1,), torch.int32)
+        self.cnt_table = v(self.off["cnt_table"], (world, e_total), torch.int32)
+        self.cnt_flag = v(self.off["cnt_flag"], (N.MAX_RANKS,), torch.int32)
+        self.done = v(self.off["done"], (N.MAX_RANKS,), torch.int32)
+        self.done_cum = torch.zeros(N.MAX_RANKS, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.ws = G.Workspace.get(device)
+        # scratch of the routing kernels
+        s_max = max_slots
+        nb = (s_max + 1023) // 1024
+        self.block_hist = torch.zeros(nb * e_total, dtype=torch.int32, device=device)
+        self.block_off = torch.zeros(nb * e_total, dtype=torch.int32, device=device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+        self.wait_ns = int(float(os.environ.get("CCFUSER_WAIT_LIMIT_S", "5")) * 1e9)
+        self.n_comm = env_flag("COMM_CTAS", 24)
+
+    @classmethod
+    def get(cls, group, world, rank, device, max_rows, max_slots, d_model, e_total, dtype) -> "CommContext":
+        key = (id(group) if group is not None else 0, world, str(device), d_model, e_total, dtype)
+        ctx = cls._instances.get(key)
+        if ctx is None or ctx.max_rows < max_rows or ctx.max_slots < max_slots:
+            # (re)allocation is collective: every rank constructs its layers in the same order
+            ctx = cls(group, world, rank, device, max_rows, max_slots, d_model, e_total, dtype)
+            cls._instances[key] = ctx
+        return ctx
+
+    def peer(self, name: str):
+        return self.buf.peer_ptrs(self.off[name])
+
+    def check_status(self, what="fused MoE"):
+        self.ws.check(what)
+
+
+class _TopKSoftmax(torch.autograd.Function):
+    """idx, w = top-k + softmax over the selected logits (csrc/moe_kernels.cu)."""
+
+    @staticmethod
+    def forward(ctx, logits, k):
+        lib = N.load()
+        t, e = logits.shape
+        logits = logits.contiguous()
+        idx = torch.empty(t, k, dtype=torch.int32, device=logits.device)
+        w = torch.empty(t, k, dtype=torch.float32, device=logits.device)
+        N.check(lib.ccf_topk_softmax(logits.data_ptr(), int(logits.dtype == torch.float16),
+                                     int(logits.dtype == torch.float32), t, e, k, idx.data_ptr(), w.data_ptr(),
+                                     N.stream_ptr()), "ccf_topk_softmax")
+        ctx.save_for_backward(idx, w)
+        ctx.e, ctx.dtype = e, logits.dtype
+        ctx.mark_non_differentiable(idx)
+        return idx, w
+
+    @staticmethod
+    def backward(ctx, _gidx, gw):
+        lib = N.load()
+        idx, w = ctx.saved_tensors
+        t, k = idx.shape
+        dlogits = torch.zeros(t, ctx.e, dtype=ctx.dtype, device=idx.device)
+        gw = gw.contiguous().float()
+        N.check(lib.ccf_topk_softmax_bwd(idx.data_ptr(), w.data_ptr(), gw.data_ptr(), t, ctx.e, k,
+                                         dlogits.data_ptr(), int(ctx.dtype == torch.float16),
+                                         int(ctx.dtype == torch.float32), N.stream_ptr()), "ccf_topk_softmax_bwd")
+        return dlogits, None
+
+
+def topk_softmax(logits: torch.Tensor, k: int):
+    return _TopKSoftmax.apply(logits, k)
+
+
+class FusedMoE:
+    """Per-layer state of the fused path: symmetric forward buffers, saved activations, launch helpers."""
+
+    def __init__(self, layer):
+        cfg = layer.config
+        if cfg.dtype not in (torch.bfloat16, torch.float16):
+            raise TypeError("the fused backend computes in bf16 or fp16")
+        if cfg.d_model % 64 or cfg.d_ffn % 128:
+            raise ValueError("fused backend: d_model must be a multiple of 64 and d_ffn a multiple of 128")
+        if cfg.num_experts > N.MAX_GROUPS or cfg.ep_size > N.MAX_RANKS or cfg.top_k > 8:
+            raise ValueError("fused backend: at most 256 experts, 8 ranks, top-8")
+        self.layer, self.cfg = layer, cfg
+        self.device = layer.experts.htoh4.weight.device
+        self.world, self.rank = cfg.ep_size, layer.ep_rank
+        self.max_rows = cfg.max_recv_rows()
+        self.max_slots = cfg.max_tokens * cfg.top_k
+        group = layer.ep_group if self.world > 1 else None
+        self.ctx = CommContext.get(group, self.world, self.rank, self.device, self.max_rows, self.max_slots,
+                                   cfg.d_model, cfg.num_experts, cfg.dtype)
+        # rows of the context may exceed this layer's bound (shared with bigger layers)
+        self.max_rows = self.ctx.max_rows
+        self.max_slots = self.ctx.max_slots
+        nbytes = _round_up(self.max_rows * cfg.d_model * 2, 1024) + _round_up(self.max_slots * cfg.d_model * 2, 1024)
+        self.buf = SymmBuffer(nbytes, group, self.device)
+        self.off_xrecv = self.buf.carve(self.max_rows * cfg.d_model * 2)
+        self.off_comb = self.buf.carve(self.max_slots * cfg.d_model * 2)
+        self.xrecv = self.buf.view(self.off_xrecv, (self.max_rows, cfg.d_model), cfg.dtype)
+        self.comb = self.buf.view(self.off_comb, (self.max_slots, cfg.d_model), cfg.dtype)
+        f = cfg.d_ffn
+        dev, dt = self.device, cfg.dtype
+        self.h_act = torch.zeros(self.max_rows, f, dtype=dt, device=dev)
+        self.h_pre = torch.zeros(self.max_rows, f, dtype=dt, device=dev)
+        self.h_pre2 = torch.zeros(self.max_rows, f, dtype=dt, device=dev) if cfg.activation == "swiglu" else None
+        e_loc = cfg.experts_per_rank
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.slot_pos = torch.zeros(self.max_slots, **i32)
+        self.slot_row = torch.full((self.max_slots,), -1, **i32)
+        self.count_raw = torch.zeros(cfg.num_experts, **i32)
+        self.count_kept = torch.zeros(cfg.num_experts, **i32)
+        self.dst_base = torch.zeros(cfg.num_experts, **i32)
+        self.group_base = torch.zeros(e_loc, **i32)
+        self.group_rows = torch.zeros(e_loc, **i32)
+        self.sent_rows = torch.zeros(N.MAX_RANKS, **i32)
+        self.table_copy = torch.zeros(self.world, cfg.num_experts, **i32)
+        self.check_every_call = bool(env_flag("CHECK_STATUS", 0))
+        self.launches = 0
+
+    # ------------------------------------------------------------------------------------------
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        cfg, layer = self.cfg, self.layer
+        if x.shape[0] > cfg.max_tokens:
+            raise ValueError(f"{x.shape[0]} tokens exceed config.max_tokens={cfg.max_tokens}")
+        x = x.contiguous()
+        logits = layer.gate.logits(x) if hasattr(layer.gate, "logits") else None
+        if logits is None:
+            raise TypeError("the fused backend needs a gate with a .logits(x) method (NaiveGate)")
+        idx, w = topk_softmax(logits, cfg.top_k)
+        ex = layer.experts
+        wg = ex.htoh4_gate.weight if cfg.activation == "swiglu" else None
+        bg = ex.htoh4_gate.bias if cfg.activation == "swiglu" else None
+        y = _FusedMoEFn.apply(x, w, idx, ex.htoh4.weight, ex.htoh4.bias, wg, bg, ex.h4toh.weight, ex.h4toh.bias, self)
+        if self.check_every_call:
+            self.ctx.check_status("fused MoE forward")
+        return y
+
+    # ---- launch helpers ------------------------------------------------------------------------
+    def _dispatch_args(self, src: torch.Tensor, tokens: int, idx: torch.Tensor, gate_w: torch.Tensor,
+                       recv_name_ctx: Optional[str], backward: bool, dgate=None) -> N.DispatchArgs:
+        cfg, ctx = self.cfg, self.ctx
+        a = N.DispatchArgs()
+        a.x = src.data_ptr()
+        a.slot_expert = idx.data_ptr()
+        a.slot_pos = self.slot_pos.data_ptr()
+        a.dst_base = self.dst_base.data_ptr()
+        a.slot_gate = gate_w.data_ptr()
+        a.saved_comb = self.comb.data_ptr() if backward else 0
+        a.dgate = N.ptr(dgate)
+        a.slot_row = self.slot_row.data_ptr()
+        recv = ctx.peer("grecv") if backward else self.buf.peer_ptrs(self.off_xrecv)
+        rs, rg, tf = ctx.peer("row_src"), ctx.peer("row_gate"), ctx.peer("tile_flags")
+        for r in range(self.world):
+            a.peer_recv[r], a.peer_row_src[r], a.peer_row_gate[r], a.peer_tile_flags[r] = recv[r], rs[r], rg[r], tf[r]
+        a.work_counter = ctx.ws.sched.data_ptr() + 8
+        a.tokens, a.top_k, a.d = tokens, cfg.top_k, cfg.d_model
+        a.capacity = cfg.capacity(tokens)
+        a.experts_per_rank, a.my_rank = cfg.experts_per_rank, self.rank
+        a.backward, a.fp16, a.max_rows = int(backward), int(cfg.dtype == torch.float16), self.max_rows
+        return a
+
+    def _combine_kw(self, peer_comb, row_gate):
+        ctx = self.ctx
+        done = [p + 4 * self.rank for p in ctx.peer("done")]
+        return dict(row_src=ctx.row_src, row_gate=row_gate, peer_comb=peer_comb, peer_done=done, world=self.world,
+                    send_finish=1, max_slots=self.max_slots)
+
+    def _wait_and_reduce(self, comb: torch.Tensor, tokens: int, n_tiles: int, out: torch.Tensor):
+        lib, ctx, cfg = N.load(), self.ctx, self.cfg
+        st = N.stream_ptr()
+        N.check(lib.ccf_combine_wait(ctx.done.data_ptr(), ctx.done_cum.data_ptr(), self.sent_rows.data_ptr(), n_tiles,
+                                     self.world, ctx.wait_ns, ctx.ws.status.data_ptr(), st), "ccf_combine_wait")
+        N.check(lib.ccf_combine_reduce(comb.data_ptr(), self.slot_row.data_ptr(), out.data_ptr(), tokens, cfg.top_k,
+                                       cfg.d_model, int(cfg.dtype == torch.float16), st), "ccf_combine_reduce")
+        self.launches += 2
+
+
+class _FusedMoEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate_w, idx, w1, b1, wg, bg, w2, b2, fm: FusedMoE):
+        lib = N.load()
+        cfg, cc = fm.cfg, fm.ctx
+        st = N.stream_ptr()
+        t, d = x.shape
+        f, e_loc, e_tot = cfg.d_ffn, cfg.experts_per_rank, cfg.num_experts
+        s = t * cfg.top_k
+        idx = idx.contiguous()
+        gate_w = gate_w.contiguous()
+        # 1. positions / counts
+        N.check(lib.ccf_route(idx.data_ptr(), s, e_tot, cfg.capacity(t), fm.slot_pos.data_ptr(),
+                              cc.block_hist.data_ptr(), cc.block_off.data_ptr(), fm.count_raw.data_ptr(),
+                              fm.count_kept.data_ptr(), cc.ticket.data_ptr(), st), "ccf_route")
+        # 2. count exchange + plan
+        cc.epoch += 1
+        p = N.PlanArgs()
+        p.count_kept = fm.count_kept.data_ptr()
+        tb, fl = cc.peer("cnt_table"), cc.peer("cnt_flag")
+        for r in range(fm.world):
+            p.peer_table[r], p.peer_flag[r] = tb[r], fl[r]
+        p.dst_base, p.group_base, p.group_rows = fm.dst_base.data_ptr(), fm.group_base.data_ptr(), fm.group_rows.data_ptr()
+        p.sent_rows, p.table_copy, p.status = fm.sent_rows.data_ptr(), fm.table_copy.data_ptr(), cc.ws.status.data_ptr()
+        p.wait_limit_ns = cc.wait_ns
+        p.world, p.my_rank, p.e_total, p.e_loc, p.epoch, p.max_rows = fm.world, fm.rank, e_tot, e_loc, cc.epoch, fm.max_rows
+        N.check(lib.ccf_plan(C.byref(p), st), "ccf_plan")
+        # 3. dispatch + GEMM-1 (one kernel)
+        disp = fm._dispatch_args(x, t, idx, gate_w, None, backward=False)
+        common = dict(group_base=fm.group_base, group_rows=fm.group_rows, num_groups=e_loc, tile_flags=cc.tile_flags,
+                      dispatch=disp, n_comm_ctas=cc.n_comm, wait_ns=cc.wait_ns, workspace=cc.ws)
+        if cfg.activation == "swiglu":
+            G.launch(a0=fm.xrecv, b0=w1.view(e_loc * f, d), b1=wg.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K,
+                     epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=fm.h_act, out1=fm.h_pre, out2=fm.h_pre2,
+                     bias0=b1, bias1=bg, **common)
+        else:
+            G.launch(a0=fm.xrecv, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT,
+                     n=f, k=d, b_group_rows=f, out0=fm.h_act, out1=fm.h_pre, bias0=b1, act=N.ACT_CODE[cfg.activation],
+                     **common)
+        cc.tile_flags.zero_()
+        # 4. GEMM-2 + combine into the source ranks' buffers
+        G.launch(a0=fm.h_act, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_COMBINE, n=d, k=f,
+                 group_base=fm.group_base, group_rows=fm.group_rows, num_groups=e_loc, b_group_rows=d, bias0=b2,
+                 ld_out=d, wait_ns=cc.wait_ns, workspace=cc.ws,
+                 **fm._combine_kw(fm.buf.peer_ptrs(fm.off_comb), cc.row_gate))
+        # 5. wait for my rows, sum the k slots
+        y = torch.empty(t, d, dtype=x.dtype, device=x.device)
+        fm._wait_and_reduce(fm.comb, t, (d + 255) // 256, y)
+        fm.launches += 6
+        ctx.fm = fm
+        ctx.tokens = t
+        ctx.save_for_backward(idx, gate_w, w1, wg, w2)
+        ctx.has_bias = (b1 is not None, bg is not None, b2 is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = N.load()
+        fm: FusedMoE = ctx.fm
+        cfg, cc = fm.cfg, fm.ctx
+        idx, gate_w, w1, wg, w2 = ctx.saved_tensors
+        st = N.stream_ptr()
+        t, d, f, e_loc = ctx.tokens, cfg.d_model, cfg.d_ffn, cfg.experts_per_rank
+        fp16 = int(cfg.dtype == torch.float16)
+        dy = dy.contiguous()
+        dgate = torch.empty(t * cfg.top_k, dtype=torch.float32, device=dy.device)
+        swiglu = cfg.activation == "swiglu"
+        # 1+2. push g*dy rows (dispatch role) + dgrad-2 with the activation derivative in the epilogue
+        disp = fm._dispatch_args(dy, t, idx, gate_w, "grecv", backward=True, dgate=dgate)
+        common = dict(group_base=fm.group_base, group_rows=fm.group_rows, num_groups=e_loc, wait_ns=cc.wait_ns,
+                      workspace=cc.ws)
+        dh = torch.empty(fm.max_rows, f, dtype=cfg.dtype, device=dy.device)
+        dh2 = torch.empty_like(dh) if swiglu else None
+        if swiglu:
+            G.launch(a0=cc.grecv, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DSWIGLU, n=f, k=d,
+                     b_group_rows=d, out0=dh, out1=dh2, aux0=fm.h_pre, aux1=fm.h_pre2, tile_flags=cc.tile_flags,
+                     dispatch=disp, n_comm_ctas=cc.n_comm, **common)
+        else:
+            G.launch(a0=cc.grecv, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DACT, n=f, k=d,
+                     b_group_rows=d, out0=dh, aux0=fm.h_pre, act=N.ACT_CODE[cfg.activation], tile_flags=cc.tile_flags,
+                     dispatch=disp, n_comm_ctas=cc.n_comm, **common)
+        cc.tile_flags.zero_()
+        # 3. wgrad-2: dW2[e] = (g dy)^T h_act   [d, f]
+        dw2 = torch.empty_like(w2)
+        G.launch(a0=cc.grecv, b0=fm.h_act, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True,
+                 m_per_group=d, out0=dw2, ld_out=f, **common)
+        has_b1, has_bg, has_b2 = ctx.has_bias
+
+        def colsum(src, n):
+            out = torch.empty(e_loc, n, dtype=cfg.dtype, device=dy.device)
+            N.check(lib.ccf_colsum_grouped(src.data_ptr(), n, n, e_loc, fm.group_base.data_ptr(),
+                                           fm.group_rows.data_ptr(), out.data_ptr(), fp16, st), "ccf_colsum_grouped")
+            fm.launches += 1
+            return out
+
+        db2 = colsum(cc.grecv, d) if has_b2 else None
+        # 4. wgrad-1: dW1[e] = dh^T x_e   [f, d]
+        dw1 = torch.empty_like(w1)
+        dwg = dbg = None
+        if swiglu:
+            # dh = d(gate pre-activation), dh2 = d(up pre-activation)
+            dwg = torch.empty_like(wg)
+            G.launch(a0=dh, b0=fm.xrecv, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True,
+                     m_per_group=f, out0=dwg, ld_out=d, **common)
+            G.launch(a0=dh2, b0=fm.xrecv, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True,
+                     m_per_group=f, out0=dw1, ld_out=d, **common)
+            db1 = colsum(dh2, f) if has_b1 else None
+            dbg = colsum(dh, f) if has_bg else None
+        else:
+            G.launch(a0=dh, b0=fm.xrecv, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True,
+                     m_per_group=f, out0=dw1, ld_out=d, **common)
+            db1 = colsum(dh, f) if has_b1 else None
+        # 5. dgrad-1 + combine: dx rows go back to the ranks the tokens came from
+        ck = fm._combine_kw(cc.peer("gcomb"), None)
+        if swiglu:
+            G.launch(a0=dh, a1=dh2, b0=wg.view(e_loc * f, d), b1=w1.view(e_loc * f, d), a_major=N.MAJ_K,
+                     b_major=N.MAJ_MN, epi=N.EPI_COMBINE, n=d, k=f, kseg=2, b_group_rows=f, ld_out=d, **common, **ck)
+        else:
+            G.launch(a0=dh, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_COMBINE, n=d, k=f,
+                     b_group_rows=f, ld_out=d, **common, **ck)
+        dx = torch.empty(t, d, dtype=dy.dtype, device=dy.device)
+        fm._wait_and_reduce(cc.gcomb, t, (d + 255) // 256, dx)
+        fm.launches += 5 + int(swiglu)
+        if fm.check_every_call:
+            cc.check_status("fused MoE backward")
+        return dx, dgate.view(t, cfg.top_k), None, dw1, db1, dwg, dbg, dw2, db2, None

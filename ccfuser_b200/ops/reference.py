@@ -30,18 +30,24 @@ def expert_ffn(x, w1, b1, w2, b2, activation: str, wg=None, bg=None):
 
 
 def dense_moe_oracle(xs: List[torch.Tensor], params: Dict[str, torch.Tensor], *, top_k: int,
-                     capacity: Optional[int], activation: str = "gelu") -> List[torch.Tensor]:
+                     capacity: Optional[int], activation: str = "gelu", routing=None) -> List[torch.Tensor]:
     """xs: one [T_r, d] tensor per rank. params: full (all experts) tensors under the keys
     ``gate.weight [E,d]``, ``gate.bias [E]|None``, ``htoh4.weight [E,F,d]``, ``htoh4.bias``,
     ``h4toh.weight [E,d,F]``, ``h4toh.bias`` and for swiglu ``htoh4_gate.weight/bias``.
-    Everything is computed in the dtype of ``params`` (use fp32/fp64). Differentiable."""
+    Everything is computed in the dtype of ``params`` (use fp32/fp64). Differentiable.
+    ``routing`` optionally gives one ``(idx [T,k], score [T,k])`` pair per rank instead of running the
+    router (used to test expert kernels with the routing decisions of the implementation under test)."""
     gw, gb = params["gate.weight"], params.get("gate.bias")
     e_total = gw.shape[0]
     outs = []
     for x in xs:
         t, d = x.shape
-        logits = F.linear(x.to(gw.dtype), gw, gb)
-        idx, score = topk_softmax_reference(logits, top_k)
+        if routing is None:
+            logits = F.linear(x.to(gw.dtype), gw, gb)
+            idx, score = topk_softmax_reference(logits, top_k)
+        else:
+            idx, score = routing[len(outs)]
+            idx = idx.to(torch.int64)
         score = score.to(gw.dtype)
         cap = capacity if capacity is not None else t * top_k
         plan = route_local(idx, e_total, cap)

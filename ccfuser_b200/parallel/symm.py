@@ -1,0 +1,99 @@
+"""Symmetric device memory: every rank of a group allocates a buffer of the same size and maps all the
+others' through CUDA IPC, so kernels can store straight into a peer's HBM over NVLink.
+
+Stands in for the NVSHMEM symmetric heap of the reference (``nvshmem_malloc`` in
+mix_moe/csrc/mix_moe.h:75-77 and NVSHMEM's ``peer_heap_base`` table); the exchange of handles goes through
+the torch process group instead of MPI. With one rank nothing is exported.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .. import native as N
+
+_TYPESTR = {torch.bfloat16: None, torch.float16: "<f2", torch.float32: "<f4", torch.int32: "<i4",
+            torch.uint8: "|u1", torch.int64: "<i8"}
+
+
+class _DeviceView:
+    """Minimal __cuda_array_interface__ carrier so torch can wrap raw device memory without a copy."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+        self._owner = owner
+
+
+class SymmBuffer:
+    """One symmetric allocation. ``local`` is a uint8 tensor over this rank's memory; ``peer_ptr(r)``
+    is the address at which rank r's copy is mapped in this process."""
+
+    def __init__(self, nbytes: int, group=None, device=None):
+        lib = N.load()
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not None) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.nbytes = (int(nbytes) + 1023) // 1024 * 1024
+        self.device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+        p = C.c_void_p()
+        with torch.cuda.device(self.device):
+            N.check(lib.ccf_symm_alloc(self.nbytes, C.byref(p)), "ccf_symm_alloc")
+        self.base = p.value
+        self._peer_base: List[int] = [0] * self.world
+        self._peer_base[self.rank] = self.base
+        self._opened: List[int] = []
+        if self.world > 1:
+            hb = lib.ccf_symm_handle_bytes()
+            buf = C.create_string_buffer(hb)
+            N.check(lib.ccf_symm_get_handle(self.base, buf), "ccf_symm_get_handle")
+            handles: List[Optional[bytes]] = [None] * self.world
+            dist.all_gather_object(handles, bytes(buf.raw), group=group)
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    continue
+                q = C.c_void_p()
+                N.check(lib.ccf_symm_open_handle(C.create_string_buffer(h, hb), C.byref(q)), "ccf_symm_open_handle")
+                self._peer_base[r] = q.value
+                self._opened.append(q.value)
+            dist.barrier(group=group)
+        self.local = torch.as_tensor(_DeviceView(self.base, self.nbytes, self), device=self.device)
+        self._cursor = 0
+
+    def peer_ptr(self, rank: int, offset: int = 0) -> int:
+        return self._peer_base[rank] + offset
+
+    def peer_ptrs(self, offset: int = 0) -> List[int]:
+        return [b + offset for b in self._peer_base]
+
+    def carve(self, nbytes: int, align: int = 1024) -> int:
+        """Bump-allocate a sub-range; every rank must carve in the same order. Returns the byte offset."""
+        off = (self._cursor + align - 1) // align * align
+        if off + nbytes > self.nbytes:
+            raise MemoryError(f"symmetric buffer exhausted ({off + nbytes} > {self.nbytes})")
+        self._cursor = off + nbytes
+        return off
+
+    def view(self, offset: int, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.local[offset:offset + nbytes].view(dtype).view(*shape)
+
+    def close(self):
+        if self.base is None:
+            return
+        lib = N.load()
+        for q in self._opened:
+            lib.ccf_symm_close_handle(q)
+        self._opened = []
+        self.local = None
+        lib.ccf_symm_free(self.base)
+        self.base = None
+
+    def __del__(self):
+        # freed explicitly with close(); at interpreter exit the driver reclaims the allocation
+        pass

@@ -75,6 +75,11 @@ class PlanArgs(C.Structure):
 
 _lib = None
 _lock = threading.Lock()
+LAUNCHES = [0]   # kernels of this library launched by this process (bench.py reports the count)
+
+
+def count(n: int = 1):
+    LAUNCHES[0] += n
 
 
 def lib_path() -> str:

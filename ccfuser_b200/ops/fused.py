@@ -119,6 +119,7 @@ class _TopKSoftmax(torch.autograd.Function):
         N.check(lib.ccf_topk_softmax(logits.data_ptr(), int(logits.dtype == torch.float16),
                                      int(logits.dtype == torch.float32), t, e, k, idx.data_ptr(), w.data_ptr(),
                                      N.stream_ptr()), "ccf_topk_softmax")
+        N.count(1)
         ctx.save_for_backward(idx, w)
         ctx.e, ctx.dtype = e, logits.dtype
         ctx.mark_non_differentiable(idx)
@@ -134,6 +135,7 @@ class _TopKSoftmax(torch.autograd.Function):
         N.check(lib.ccf_topk_softmax_bwd(idx.data_ptr(), w.data_ptr(), gw.data_ptr(), t, ctx.e, k,
                                          dlogits.data_ptr(), int(ctx.dtype == torch.float16),
                                          int(ctx.dtype == torch.float32), N.stream_ptr()), "ccf_topk_softmax_bwd")
+        N.count(1)
         return dlogits, None
 
 
@@ -186,7 +188,6 @@ class FusedMoE:
         self.sent_rows = torch.zeros(N.MAX_RANKS, **i32)
         self.table_copy = torch.zeros(self.world, cfg.num_experts, **i32)
         self.check_every_call = bool(env_flag("CHECK_STATUS", 0))
-        self.launches = 0
 
     # ------------------------------------------------------------------------------------------
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
@@ -243,7 +244,7 @@ class FusedMoE:
                                      self.world, ctx.wait_ns, ctx.ws.status.data_ptr(), st), "ccf_combine_wait")
         N.check(lib.ccf_combine_reduce(comb.data_ptr(), self.slot_row.data_ptr(), out.data_ptr(), tokens, cfg.top_k,
                                        cfg.d_model, int(cfg.dtype == torch.float16), st), "ccf_combine_reduce")
-        self.launches += 2
+        N.count(2)
 
 
 class _FusedMoEFn(torch.autograd.Function):
@@ -294,7 +295,7 @@ class _FusedMoEFn(torch.autograd.Function):
         # 5. wait for my rows, sum the k slots
         y = torch.empty(t, d, dtype=x.dtype, device=x.device)
         fm._wait_and_reduce(fm.comb, t, (d + 255) // 256, y)
-        fm.launches += 6
+        N.count(3)  # route (2 kernels) + plan; the GEMM launches count themselves
         ctx.fm = fm
         ctx.tokens = t
         ctx.save_for_backward(idx, gate_w, w1, wg, w2)
@@ -338,7 +339,7 @@ class _FusedMoEFn(torch.autograd.Function):
             out = torch.empty(e_loc, n, dtype=cfg.dtype, device=dy.device)
             N.check(lib.ccf_colsum_grouped(src.data_ptr(), n, n, e_loc, fm.group_base.data_ptr(),
                                            fm.group_rows.data_ptr(), out.data_ptr(), fp16, st), "ccf_colsum_grouped")
-            fm.launches += 1
+            N.count(1)
             return out
 
         db2 = colsum(cc.grecv, d) if has_b2 else None
@@ -368,7 +369,6 @@ class _FusedMoEFn(torch.autograd.Function):
                      b_group_rows=f, ld_out=d, **common, **ck)
         dx = torch.empty(t, d, dtype=dy.dtype, device=dy.device)
         fm._wait_and_reduce(cc.gcomb, t, (d + 255) // 256, dx)
-        fm.launches += 5 + int(swiglu)
         if fm.check_every_call:
             cc.check_status("fused MoE backward")
         return dx, dgate.view(t, cfg.top_k), None, dw1, db1, dwg, dbg, dw2, db2, None

@@ -1,0 +1,61 @@
+"""Training step used by the examples and the benchmark: host batch in, loss out.
+
+``TrainStep.step(ids, labels)`` takes pinned host tensors, copies them to the device, runs forward,
+backward, the data-parallel all-reduce of the replicated parameters and the optimizer, and returns the
+loss as a Python float (one device-to-host read). The reference's loops do the same by hand
+(mix_moe/mix_moe/examples/models/moe_gpt_ddp.py:344-381, plain SGD in mix_moe/mix_moe/examples/mix_moe_ddp.py:155).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .parallel.ddp import allreduce_replicated_grads, wrap_ddp
+
+
+class TrainStep:
+    def __init__(self, model: nn.Module, lr: float = 1e-3, optimizer: str = "sgd", dp_group=None,
+                 use_ddp: bool = True, aux_loss: bool = False):
+        self.raw_model = model
+        self.dp_group = dp_group
+        self.distributed = dist.is_initialized() and dist.get_world_size(dp_group) > 1
+        self.use_ddp = use_ddp and self.distributed
+        self.model = wrap_ddp(model, dp_group) if self.use_ddp else model
+        params = [p for p in model.parameters() if p.requires_grad]
+        if optimizer == "sgd":
+            self.opt = torch.optim.SGD(params, lr=lr, foreach=True)
+        elif optimizer == "adamw":
+            self.opt = torch.optim.AdamW(params, lr=lr, fused=params[0].is_cuda)
+        else:
+            raise ValueError(optimizer)
+        self.device = params[0].device
+        self.aux_loss = aux_loss
+        self._ids = self._labels = None
+
+    def step_device(self, ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """One optimisation step on device tensors; returns the loss tensor (no host sync)."""
+        self.opt.zero_grad(set_to_none=True)
+        loss = self.model(ids, labels)
+        if self.aux_loss:
+            aux = self.raw_model.aux_loss()
+            if aux is not None:
+                loss = loss + aux.to(loss.dtype).sum()
+        loss.backward()
+        if self.distributed and not self.use_ddp:
+            allreduce_replicated_grads(self.raw_model, self.dp_group)
+        self.opt.step()
+        return loss.detach()
+
+    def step(self, ids: torch.Tensor, labels: Optional[torch.Tensor] = None) -> float:
+        """ids/labels: host tensors (pinned for an asynchronous copy). Returns the loss."""
+        if labels is None:
+            labels = ids
+        if self._ids is None or self._ids.shape != ids.shape:
+            self._ids = torch.empty(ids.shape, dtype=ids.dtype, device=self.device)
+            self._labels = torch.empty(labels.shape, dtype=labels.dtype, device=self.device)
+        self._ids.copy_(ids, non_blocking=True)
+        self._labels.copy_(labels, non_blocking=True)
+        return float(self.step_device(self._ids, self._labels).item())

@@ -60,7 +60,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if p.returncode:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
     tmp = LIB_PATH + ".tmp"
-    subprocess.check_call([_nvcc(), "-shared", "-o", tmp, *objs, "-lcudart"])
+    subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", tmp, *objs, "-lcudart"])
     os.replace(tmp, LIB_PATH)
     return LIB_PATH
 

@@ -651,7 +651,7 @@ struct CcfGemmLaunch {
   int epi;                   // CcfEpilogue
   int kgroup;                // 1 = k-grouped (wgrad)
   int grid;                  // 0 = one CTA per SM
-  int pad0;
+  int device;                // CUDA device of the operands; made current for the calling thread (-1 = leave)
 };
 
 int ccf_gemm_smem_bytes() { return ccf::kSmemBytes; }
@@ -666,6 +666,9 @@ int ccf_gemm_launch(const CcfGemmLaunch* L, void* stream_v) {
   using namespace ccf;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const CcfGemmArgs& a = L->args;
+  // Tensor maps are encoded through the driver API, which needs a context bound to the calling thread;
+  // a framework worker thread (autograd) may not have touched the runtime yet.
+  if (L->device >= 0 && cudaSetDevice(L->device) != cudaSuccess) return -7;
   if (a.num_groups < 1 || a.num_groups > CCF_MAX_GROUPS) return -2;
   if (a.n % 32 != 0) return -3;
   if (L->kgroup && (a.m_per_group % BM != 0)) return -4;

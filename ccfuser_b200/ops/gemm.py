@@ -96,6 +96,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     L.a_rows, L.a_cols = a0.shape
     L.b_rows, L.b_cols = b0.shape
     L.a_major, L.b_major, L.epi, L.kgroup, L.grid = int(a_major), int(b_major), int(epi), int(bool(kgroup)), int(grid)
+    L.device = a0.device.index if a0.device.index is not None else torch.cuda.current_device()
     N.check(lib.ccf_gemm_launch(C.byref(L), N.stream_ptr()), "ccf_gemm_launch")
     N.count(1)
     return ws

@@ -19,7 +19,10 @@ from ccfuser_b200.utils.dist import init_distributed  # noqa: E402
 
 
 def rel(a, b):
-    return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+    """Relative Frobenius error. (A max-norm check is too sharp for ReLU: a pre-activation whose sign differs
+    between the bf16 kernel and the fp32 oracle flips one gradient element completely.)"""
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / b.norm().clamp_min(1e-6))
 
 
 def gather(t, world):
@@ -90,7 +93,7 @@ def run_case(rank, world, act, cf, tokens, e_loc, d, f, iters=3):
         for n in names:
             errs["d" + n + ".w"] = rel(getattr(ex, n).weight.grad, fp[n + ".weight"].grad[sl])
             errs["d" + n + ".b"] = rel(getattr(ex, n).bias.grad, fp[n + ".bias"].grad[sl])
-        bad = {k: v for k, v in errs.items() if not v < 5e-2}
+        bad = {k: v for k, v in errs.items() if not v < 3e-2}
         if bad:
             raise AssertionError(f"rank {rank} {act} cf={cf} it={it}: {bad}")
         worst = max(worst, max(errs.values()))

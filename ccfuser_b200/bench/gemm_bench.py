@@ -44,7 +44,7 @@ def time_fn(fn, iters=10, warmup=3, flush_mb=256):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--cases", default="square,fwd1,fwd2,dgrad,wgrad,cublas")
+    ap.add_argument("--cases", default="square,fwd1,fwd2,dgrad,dgrad_plain,wgrad,cublas")
     ap.add_argument("--rows", type=int, default=4096 * 8)
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--d", type=int, default=4096)
@@ -95,6 +95,10 @@ def main():
         report("dgrad2_dact", 2 * r * d * f, lambda: G.launch(
             a0=y, b0=w2.view(e * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DACT, n=f, k=d,
             group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=h, aux0=pre, act=N.ACT_GELU))
+    if "dgrad_plain" in cases:
+        report("dgrad2_plain_store", 2 * r * d * f, lambda: G.launch(
+            a0=y, b0=w2.view(e * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, k=d,
+            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=h))
     if "wgrad" in cases:
         dw = torch.empty(e, d, f, device=dev, dtype=torch.bfloat16)
         report("wgrad2", 2 * r * d * f, lambda: G.launch(

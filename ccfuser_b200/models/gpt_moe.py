@@ -113,7 +113,10 @@ class GPTMoE(nn.Module):
     def __init__(self, c: GPTMoEConfig, ep_group=None, device=None):
         super().__init__()
         self.config = c
-        self.wte = nn.Embedding(c.vocab_size, c.d_model, device=device, dtype=c.dtype)
+        # the embedding / LM-head matrix is padded to a multiple of 128 rows so the vocabulary GEMM runs on an
+        # aligned tensor-core kernel; the padding columns of the logits are masked out of the softmax
+        self.vocab_padded = (c.vocab_size + 127) // 128 * 128
+        self.wte = nn.Embedding(self.vocab_padded, c.d_model, device=device, dtype=c.dtype)
         self.wpe = nn.Embedding(c.seq_len, c.d_model, device=device, dtype=c.dtype)
         self.h = nn.ModuleList([Block(c, c.is_moe(i), ep_group, device) for i in range(c.n_layer)])
         self.ln_f = nn.LayerNorm(c.d_model, device=device, dtype=c.dtype)
@@ -143,8 +146,10 @@ class GPTMoE(nn.Module):
             x = blk(x)
         x = self.ln_f(x)
         logits = F.linear(x, self.wte.weight)
+        if self.vocab_padded != self.config.vocab_size:
+            logits[..., self.config.vocab_size:] = float("-inf")
         if labels is None:
-            return logits
+            return logits[..., :self.config.vocab_size]
         return F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), labels.reshape(-1))
 
     def moe_layers(self):

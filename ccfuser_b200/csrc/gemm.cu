@@ -1,7 +1,7 @@
 // Grouped GEMM for sm_100a: TMA (local memory, no multicast) -> 128B-swizzled shared memory ->
 // tcgen05.mma with fp32 accumulators in TMEM -> tcgen05.ld epilogue. One persistent CTA per SM,
-// 6 warps: warp 0 = tile scheduler + TMA producer, warp 1 = MMA issuer (one elected thread),
-// warps 2..5 = epilogue (one TMEM lane quarter each). Tiles are 128 x 256 x 64, four shared-memory
+// 10 warps: warp 0 = tile scheduler + TMA producer, warp 1 = MMA issuer (one elected thread),
+// warps 2..9 = epilogue (two per TMEM lane quarter, each taking half of the tile's columns). Tiles are 128 x 256 x 64, four shared-memory
 // stages, two TMEM accumulator stages (2 x 256 columns) so the epilogue of a tile overlaps the
 // main loop of the next one.
 //
@@ -40,7 +40,8 @@ constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kSchedSlots = 4;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;            // two per TMEM lane quarter, each takes half of the columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kTmemCols = 512;
 constexpr int MAJ_K = 0, MAJ_MN = 1;
 
@@ -59,7 +60,8 @@ struct __align__(16) Ctrl {
   int mt_prefix[CCF_MAX_GROUPS + 1];
 };
 
-constexpr int kSmemBytes = 1024 + kStages * kStageBytes + static_cast<int>(sizeof(Ctrl));
+constexpr int kEpiStageBytes = 2048;  // per epilogue warp: 32 rows x 64 bytes, XOR-swizzled
+constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiWarps * kEpiStageBytes + static_cast<int>(sizeof(Ctrl));
 
 struct Tile {
   int g;           // group (expert)
@@ -109,21 +111,53 @@ __device__ __forceinline__ Tile decode_tile(int t, const CcfGemmArgs& a, const C
 // ---------------------------------------------------------------------------------------------------
 // epilogue math
 // ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+// erf by Abramowitz-Stegun 7.1.26 (|error| <= 1.5e-7, far below bf16/fp16 resolution): two MUFU ops and
+// a degree-5 polynomial instead of libm's branchy erff, which made the epilogue the bottleneck at small K.
+// e2 = exp(-x*x) is passed in so the derivative can share the exponential.
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // branch-free, 1 ulp: keeps the element loops interleavable
+  return y;
+}
+__device__ __forceinline__ float erf_from_exp(float ax, float e2) {
+  const float t = fast_rcp(fmaf(0.3275911f, ax, 1.f));
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  return 1.f - p * t * e2;
+}
+__device__ __forceinline__ float gelu_f(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  const float e = erf_from_exp(z, __expf(-z * z));
+  return 0.5f * x * (1.f + copysignf(e, x));
+}
 __device__ __forceinline__ float gelu_grad_f(float x) {
-  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  const float z = fabsf(x) * 0.70710678118654752f;
+  const float e2 = __expf(-z * z);  // exp(-x^2 / 2)
+  const float cdf = 0.5f * (1.f + copysignf(erf_from_exp(z, e2), x));
+  return fmaf(x * 0.3989422804014327f, e2, cdf);
 }
-__device__ __forceinline__ float act_f(float x, int act) {
-  if (act == CCF_ACT_GELU) return gelu_f(x);
-  if (act == CCF_ACT_RELU) return fmaxf(x, 0.f);
-  return x;
+// The activation switch sits outside the element loop: with a branch per element the compiler cannot
+// interleave the 32 independent dependency chains and the epilogue ran ~200 clocks per element.
+__device__ __forceinline__ void act32(float (&f)[32], int act) {
+  if (act == CCF_ACT_GELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = gelu_f(f[i]);
+  } else if (act == CCF_ACT_RELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = fmaxf(f[i], 0.f);
+  }
 }
-__device__ __forceinline__ float act_grad_f(float x, int act) {
-  if (act == CCF_ACT_GELU) return gelu_grad_f(x);
-  if (act == CCF_ACT_RELU) return x > 0.f ? 1.f : 0.f;
-  return 1.f;
+// f[i] *= act'(pz[i])
+__device__ __forceinline__ void act_grad32(float (&f)[32], const float (&pz)[32], int act) {
+  if (act == CCF_ACT_GELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] *= gelu_grad_f(pz[i]);
+  } else if (act == CCF_ACT_RELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = pz[i] > 0.f ? f[i] : 0.f;
+  }
 }
 
 // 32 consecutive 2-byte elements -> floats (64 bytes, 16-byte aligned)
@@ -166,6 +200,88 @@ __device__ __forceinline__ void acc_to_float(const uint32_t (&r)[32], float (&f)
   for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Epilogue row I/O through a per-warp shared-memory staging buffer (32 rows x 64 bytes, XOR-swizzled).
+// In the TMEM register layout every lane owns one row, so a direct vector store writes 16 bytes to 32
+// different rows per instruction: 4096 partial-sector requests per 128x256 tile and output, which capped
+// the tensor pipe at ~46 % for two-output epilogues. Staged, each instruction moves 8 rows x 64 contiguous
+// bytes (full 32-byte sectors). Lane l owns row l; `row_ptr` is the global address of this lane's
+// 64-byte segment (0 = skip the row).
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t stage_off(int row, int piece) {
+  return static_cast<uint32_t>(row * 64 + ((piece ^ ((row >> 1) & 3)) << 4));
+}
+
+__device__ __forceinline__ void staged_store64(uint32_t stage, int lane, const uint32_t (&w)[16],
+                                               unsigned long long row_ptr) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + stage_off(lane, j)), "r"(w[4 * j]),
+                 "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                 : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = 8 * i + (lane >> 2), piece = lane & 3;
+    const unsigned long long p = __shfl_sync(0xffffffffu, row_ptr, row);
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(stage + stage_off(row, piece))
+                 : "memory");
+    if (p != 0ull) *reinterpret_cast<uint4*>(p + piece * 16) = v;
+  }
+  __syncwarp();
+}
+
+__device__ __forceinline__ void staged_load64(uint32_t stage, int lane, uint32_t (&w)[16],
+                                              unsigned long long row_ptr) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = 8 * i + (lane >> 2), piece = lane & 3;
+    const unsigned long long p = __shfl_sync(0xffffffffu, row_ptr, row);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (p != 0ull) v = __ldg(reinterpret_cast<const uint4*>(p + piece * 16));
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + stage_off(row, piece)), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w)
+                 : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w[4 * j]), "=r"(w[4 * j + 1]), "=r"(w[4 * j + 2]), "=r"(w[4 * j + 3])
+                 : "r"(stage + stage_off(lane, j))
+                 : "memory");
+  }
+  __syncwarp();
+}
+
+__device__ __forceinline__ void pack32(const float (&f)[32], uint32_t (&w)[16], int fp16) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = pack2(f[2 * i], f[2 * i + 1], fp16);
+}
+__device__ __forceinline__ void unpack32(const uint32_t (&w)[16], float (&f)[32], int fp16) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 t = unpack2(w[i], fp16);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+// byte address of element (row, col) of a 2-byte matrix with leading dimension ld
+__device__ __forceinline__ unsigned long long addr2(const void* base, long long row, long long ld, int col) {
+  return reinterpret_cast<unsigned long long>(base) + static_cast<unsigned long long>((row * ld + col) * 2);
+}
+
+// Optional per-tile trace: slot `ev` of tile number `seq` of this CTA gets the SM clock (clock64).
+__device__ __forceinline__ void trace_ev(const CcfGemmArgs& a, int seq, int ev) {
+  if (a.trace != nullptr && seq < a.trace_tiles)
+    a.trace[(static_cast<size_t>(blockIdx.x) * a.trace_tiles + seq) * 8 + ev] = clock64();
+}
+
 // ---------------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------------
@@ -176,7 +292,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     const __grid_constant__ CcfGemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kStages * kStageBytes);
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kStages * kStageBytes + kEpiWarps * kEpiStageBytes);
   const uint32_t smem_base = smem_u32(smem);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -192,11 +308,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&ctrl->acc_full[s]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[s]), 4);
+      mbar_init(smem_u32(&ctrl->acc_empty[s]), kEpiWarps);
     }
     for (int s = 0; s < kSchedSlots; ++s) {
       mbar_init(smem_u32(&ctrl->sched_full[s]), 1);
-      mbar_init(smem_u32(&ctrl->sched_empty[s]), 5);
+      mbar_init(smem_u32(&ctrl->sched_empty[s]), 1 + kEpiWarps);
     }
     ctrl->abort_word = 0;
     const int nt = (args.n + bn_out - 1) / bn_out;
@@ -241,22 +357,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     // ======================= tile scheduler + TMA producer =======================
     int stage = 0, phase = 0, ss = 0, sphase = 0;
     bool ok = true;
+    // The index of the next tile is requested one tile ahead, so the latency of the global atomic is
+    // hidden behind the loads of the current tile (lane 0 holds it until the next iteration).
+    int t_next = 0, seq = 0;
+    if (lane == 0) t_next = atomicAdd(args.sched, 1);
     while (ok) {
       if (!mbar_wait(smem_u32(&ctrl->sched_empty[ss]), sphase ^ 1, abort_word, limit)) {
         report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 1);
         break;
       }
-      int t = 0;
-      if (lane == 0) t = atomicAdd(args.sched, 1);
-      t = __shfl_sync(0xffffffffu, t, 0);
+      int t = __shfl_sync(0xffffffffu, t_next, 0);
       if (t >= total_tiles) t = -1;
       if (lane == 0) {
         ctrl->sched_tile[ss] = t;
         mbar_arrive(smem_u32(&ctrl->sched_full[ss]));
+        if (t >= 0) t_next = atomicAdd(args.sched, 1);
       }
       if (++ss == kSchedSlots) { ss = 0; sphase ^= 1; }
       if (t < 0) break;
       const Tile ti = decode_tile<kKGroup, kEpi>(t, args, ctrl);
+      if (lane == 0) trace_ev(args, seq, 0);
       if constexpr (!kKGroup) {
         if (args.tile_flags != nullptr) {
           // rows of this tile are pushed by other GPUs; wait until all of them have landed
@@ -271,6 +391,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
           fence_proxy_async();  // generic-proxy peer stores -> async-proxy (TMA) reads
         }
       }
+      if (lane == 0) trace_ev(args, seq, 1);
       const int kb_per_seg = kKGroup ? ti.kblocks : (args.k + BK - 1) / BK;
       for (int kb = 0; kb < ti.kblocks; ++kb) {
         if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_word, limit)) {
@@ -313,13 +434,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
+      if (lane == 0) trace_ev(args, seq, 2);
+      ++seq;
     }
   } else if (warp == 1) {
     // ======================= MMA issuer =======================
     const uint32_t idesc = make_idesc(BM, BN, args.fp16, kAMajor, kBMajor);
-    int stage = 0, phase = 0, ss = 0, sphase = 0, as = 0, aphase = 0;
+    int stage = 0, phase = 0, ss = 0, sphase = 0, as = 0, aphase = 0, seq = -1;
     bool ok = true;
     while (ok) {
+      ++seq;
       if (!mbar_wait(smem_u32(&ctrl->sched_full[ss]), sphase, abort_word, limit)) {
         report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 3);
         break;
@@ -336,6 +460,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         break;
       }
       tc_fence_after();
+      if (lane == 0) trace_ev(args, seq, 3);
       const uint32_t d_tmem = tmem_base + as * BN;
       for (int kb = 0; kb < ti.kblocks; ++kb) {
         if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_word, limit)) {
@@ -345,6 +470,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         }
         tc_fence_after();
         if (lane == 0) {
+          if (kb == 0) trace_ev(args, seq, 4);
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kABytes;
 #pragma unroll
@@ -356,7 +482,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             umma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&ctrl->empty[stage]));
-          if (kb == ti.kblocks - 1) umma_commit(smem_u32(&ctrl->acc_full[as]));
+          if (kb == ti.kblocks - 1) {
+            umma_commit(smem_u32(&ctrl->acc_full[as]));
+            trace_ev(args, seq, 5);
+          }
         }
         __syncwarp();
         if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -364,11 +493,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       if (++as == 2) { as = 0; aphase ^= 1; }
     }
   } else {
-    // ======================= epilogue (warps 2..5) =======================
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ======================= epilogue (warps 2..9) =======================
+    const int q = warp & 3;               // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
     const int fp16 = args.fp16;
-    int ss = 0, sphase = 0, as = 0, aphase = 0;
+    int ss = 0, sphase = 0, as = 0, aphase = 0, seq = -1;
     while (true) {
+      ++seq;
       if (!mbar_wait(smem_u32(&ctrl->sched_full[ss]), sphase, abort_word, limit)) {
         report_status(args.status, CCF_ERR_MBAR_TIMEOUT, 6);
         break;
@@ -387,6 +518,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         }
         tc_fence_after();
       }
+      if (warp == 2 && lane == 0) trace_ev(args, seq, 6);
       const int r_in_tile = q * 32 + lane;
       const bool valid = r_in_tile < ti.rows_valid;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * BN;
@@ -410,131 +542,153 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         }
       }
 
-      constexpr int n_chunks = (kEpi == CCF_EPI_SWIGLU) ? 4 : 8;
-#pragma unroll 1
+      // chunks of 32 accumulator columns; this warp takes n_chunks of them starting at chunk0
+      constexpr int n_chunks = (kEpi == CCF_EPI_SWIGLU) ? 2 : 4;
+      const int chunk0 = half * n_chunks;
+      const uint32_t stage = smem_base + kStages * kStageBytes + (warp - 2) * kEpiStageBytes;
+      uint32_t racc[2][32];
+      if (have_acc) tmem_ld32(t_row + chunk0 * 32, racc[0]);
+#pragma unroll
       for (int c = 0; c < n_chunks; ++c) {
-        const int n = ti.n0 + c * 32;
-        uint32_t r[32];
+        const int cg = chunk0 + c;
+        const int n = ti.n0 + cg * 32;
         float f[32];
+        uint32_t w[16];
         if (have_acc) {
-          tmem_ld32(t_row + c * 32, r);
           tmem_ld_wait();
-          acc_to_float(r, f);
+          if constexpr (kEpi != CCF_EPI_SWIGLU && kEpi != CCF_EPI_DSWIGLU) {
+            // next chunk's TMEM load overlaps this chunk's math and stores
+            if (c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc[(c + 1) & 1]);
+          }
+          acc_to_float(racc[c & 1], f);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) f[i] = 0.f;
         }
-        if (n >= args.n) continue;  // column edge (tile wider than the matrix)
-        if constexpr (kEpi == CCF_EPI_STORE) {
-          if (args.bias0) {
-            float b[32];
-            load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] += b[i];
-          }
-          if (valid) {
-            if (args.out_fp32) store32_f32(reinterpret_cast<float*>(args.out0) + orow * args.ld_out + n, f);
-            else store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, f, fp16);
-          }
-        } else if constexpr (kEpi == CCF_EPI_BIAS_ACT) {
-          if (args.bias0) {
-            float b[32];
-            load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] += b[i];
-          }
-          if (!valid) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = 0.f;
-          }
-          if (args.out1) store32(reinterpret_cast<uint16_t*>(args.out1) + orow * args.ld_out + n, f, fp16);
-          if (valid) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = act_f(f[i], args.act);
-          }
-          store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, f, fp16);
-        } else if constexpr (kEpi == CCF_EPI_SWIGLU) {
-          // f = gate pre-activation (accumulator columns c*32..), u = up pre-activation (+128)
-          uint32_t ru[32];
+        if constexpr (kEpi == CCF_EPI_SWIGLU) {
+          // f = gate pre-activation (accumulator columns cg*32..), u = up pre-activation (+128)
           float u[32];
           if (have_acc) {
-            tmem_ld32(t_row + 128 + c * 32, ru);
+            tmem_ld32(t_row + 128 + cg * 32, racc[(c + 1) & 1]);
             tmem_ld_wait();
-            acc_to_float(ru, u);
+            acc_to_float(racc[(c + 1) & 1], u);
+            if (c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc[(c + 1) & 1]);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) u[i] = 0.f;
           }
-          if (args.bias1) {
-            float b[32];
-            load32(reinterpret_cast<const uint16_t*>(args.bias1) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+          if (n < args.n) {
+            if (args.bias1) {
+              float b[32];
+              load32(reinterpret_cast<const uint16_t*>(args.bias1) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] += b[i];
-          }
-          if (args.bias0) {
-            float b[32];
-            load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+              for (int i = 0; i < 32; ++i) f[i] += b[i];
+            }
+            if (args.bias0) {
+              float b[32];
+              load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) u[i] += b[i];
-          }
-          if (!valid) {
+              for (int i = 0; i < 32; ++i) u[i] += b[i];
+            }
+            if (!valid) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { f[i] = 0.f; u[i] = 0.f; }
-          }
-          if (args.out1) store32(reinterpret_cast<uint16_t*>(args.out1) + orow * args.ld_out + n, f, fp16);
-          if (args.out2) store32(reinterpret_cast<uint16_t*>(args.out2) + orow * args.ld_out + n, u, fp16);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float sg = 1.f / (1.f + __expf(-f[i]));
-            f[i] = f[i] * sg * u[i];
-          }
-          store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, f, fp16);
-        } else if constexpr (kEpi == CCF_EPI_COMBINE) {
-          if (args.bias0) {
-            float b[32];
-            load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] += b[i];
-          }
-          if (c_ok) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] *= c_gate;
-            uint16_t* dst = reinterpret_cast<uint16_t*>(args.peer_comb[c_rank]) +
-                            static_cast<size_t>(c_slot) * args.ld_out + n;
-            store32(dst, f, fp16);  // peer store over NVLink (or local when c_rank is this rank)
-          }
-        } else if constexpr (kEpi == CCF_EPI_DACT) {
-          if (valid) {
-            float p[32];
-            load32(reinterpret_cast<const uint16_t*>(args.aux0) + orow * args.ld_out + n, p, fp16);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] *= act_grad_f(p[i], args.act);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = 0.f;
-          }
-          store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, f, fp16);
-        } else if constexpr (kEpi == CCF_EPI_DSWIGLU) {
-          float dg[32], du[32];
-          if (valid) {
-            float gp[32], up[32];
-            load32(reinterpret_cast<const uint16_t*>(args.aux0) + orow * args.ld_out + n, gp, fp16);
-            load32(reinterpret_cast<const uint16_t*>(args.aux1) + orow * args.ld_out + n, up, fp16);
+              for (int i = 0; i < 32; ++i) { f[i] = 0.f; u[i] = 0.f; }
+            }
+            if (args.out1) {
+              pack32(f, w, fp16);
+              staged_store64(stage, lane, w, addr2(args.out1, orow, args.ld_out, n));
+            }
+            if (args.out2) {
+              pack32(u, w, fp16);
+              staged_store64(stage, lane, w, addr2(args.out2, orow, args.ld_out, n));
+            }
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const float sg = 1.f / (1.f + __expf(-gp[i]));
-              const float silu = gp[i] * sg;
-              dg[i] = f[i] * up[i] * (sg * (1.f + gp[i] * (1.f - sg)));
-              du[i] = f[i] * silu;
+              const float sg = fast_rcp(1.f + __expf(-f[i]));
+              f[i] = f[i] * sg * u[i];
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) { dg[i] = 0.f; du[i] = 0.f; }
+            pack32(f, w, fp16);
+            staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
           }
-          store32(reinterpret_cast<uint16_t*>(args.out0) + orow * args.ld_out + n, dg, fp16);
-          store32(reinterpret_cast<uint16_t*>(args.out1) + orow * args.ld_out + n, du, fp16);
+        } else if (n < args.n) {  // column edge: chunks beyond the matrix are skipped
+          if constexpr (kEpi == CCF_EPI_STORE) {
+            if (args.bias0) {
+              float b[32];
+              load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] += b[i];
+            }
+            if (args.out_fp32) {
+              if (valid) store32_f32(reinterpret_cast<float*>(args.out0) + orow * args.ld_out + n, f);
+            } else {
+              pack32(f, w, fp16);
+              staged_store64(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);
+            }
+          } else if constexpr (kEpi == CCF_EPI_BIAS_ACT) {
+            if (args.bias0) {
+              float b[32];
+              load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] += b[i];
+            }
+            if (!valid) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] = 0.f;
+            }
+            if (args.out1) {
+              pack32(f, w, fp16);
+              staged_store64(stage, lane, w, addr2(args.out1, orow, args.ld_out, n));
+            }
+            act32(f, args.act);  // rows beyond the group hold zeros: act(0) = 0 for every supported activation
+            pack32(f, w, fp16);
+            staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
+          } else if constexpr (kEpi == CCF_EPI_COMBINE) {
+            if (args.bias0) {
+              float b[32];
+              load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] += b[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] *= c_gate;
+            pack32(f, w, fp16);
+            // peer stores over NVLink (or local when c_rank is this rank), 64 contiguous bytes per row
+            staged_store64(stage, lane, w, c_ok ? addr2(args.peer_comb[c_rank], c_slot, args.ld_out, n) : 0ull);
+          } else if constexpr (kEpi == CCF_EPI_DACT) {
+            staged_load64(stage, lane, w, valid ? addr2(args.aux0, orow, args.ld_out, n) : 0ull);
+            {
+              float pz[32];
+              unpack32(w, pz, fp16);
+              act_grad32(f, pz, args.act);
+              if (!valid) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) f[i] = 0.f;
+              }
+            }
+            pack32(f, w, fp16);
+            staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
+          } else if constexpr (kEpi == CCF_EPI_DSWIGLU) {
+            uint32_t wu[16];
+            staged_load64(stage, lane, w, valid ? addr2(args.aux0, orow, args.ld_out, n) : 0ull);
+            staged_load64(stage, lane, wu, valid ? addr2(args.aux1, orow, args.ld_out, n) : 0ull);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float2 gp = unpack2(w[j], fp16), up = unpack2(wu[j], fp16);
+              const float a0 = valid ? f[2 * j] : 0.f, a1 = valid ? f[2 * j + 1] : 0.f;
+              const float s0 = fast_rcp(1.f + __expf(-gp.x)), s1 = fast_rcp(1.f + __expf(-gp.y));
+              w[j] = pack2(a0 * up.x * (s0 * (1.f + gp.x * (1.f - s0))), a1 * up.y * (s1 * (1.f + gp.y * (1.f - s1))), fp16);
+              wu[j] = pack2(a0 * gp.x * s0, a1 * gp.y * s1, fp16);
+            }
+            staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
+            staged_store64(stage, lane, wu, addr2(args.out1, orow, args.ld_out, n));
+          }
+        }
+        if constexpr (kEpi == CCF_EPI_DSWIGLU) {
+          // register budget: this epilogue holds several 32-wide arrays, so its TMEM loads are not double-buffered
+          if (have_acc && c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc[(c + 1) & 1]);
         }
       }
+      if (warp == 2 && lane == 0) trace_ev(args, seq, 7);
       if (have_acc) {
         // all TMEM reads of this accumulator stage are complete: hand it back to the MMA warp
         tc_fence_before();
@@ -543,7 +697,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         if (++as == 2) { as = 0; aphase ^= 1; }
       }
       if constexpr (kEpi == CCF_EPI_COMBINE) {
-        // tell every source rank how many of its rows (for this column tile) are now in its buffer
+        // tell every source rank how many of its rows (for this half column tile) are now in its buffer
         __threadfence_system();
         __syncwarp();
         for (int s = 0; s < args.world; ++s) {

@@ -75,6 +75,7 @@ struct CcfGemmArgs {
   int* peer_done[CCF_MAX_RANKS];    // COMBINE: this rank's completion counter on every rank
   int* sched;               // {tile counter, finished CTAs, spare, spare}; zero before the first launch
   int* status;              // error word (first error wins)
+  long long* trace;         // optional [grid, trace_tiles, 8] clock stamps per tile and role (null = off)
   unsigned long long wait_limit_ns;
   long long ld_out;         // leading dimension (elements) of out0/out1/out2/aux0/aux1
   int n;                    // output columns
@@ -90,6 +91,6 @@ struct CcfGemmArgs {
   int send_finish;          // COMBINE: the last CTA adds 1 to every rank's completion counter
   int n_comm_ctas;          // CTAs that run the dispatch role before taking GEMM tiles (0 = none)
   int max_slots;            // COMBINE: rows of a combine buffer (bounds check)
-  int pad0;
+  int trace_tiles;          // tiles per CTA recorded in `trace`
   CcfDispatchArgs disp;
 };

@@ -44,11 +44,11 @@ class GemmArgs(C.Structure):
         ("out0", _vp), ("out1", _vp), ("out2", _vp), ("bias0", _vp), ("bias1", _vp), ("aux0", _vp), ("aux1", _vp),
         ("row_src", _vp), ("row_gate", _vp),
         ("peer_comb", _vp * MAX_RANKS), ("peer_done", _vp * MAX_RANKS),
-        ("sched", _vp), ("status", _vp),
+        ("sched", _vp), ("status", _vp), ("trace", _vp),
         ("wait_limit_ns", C.c_ulonglong), ("ld_out", C.c_longlong),
         ("n", C.c_int), ("k", C.c_int), ("num_groups", C.c_int), ("m_per_group", C.c_int), ("kseg", C.c_int),
         ("b_group_rows", C.c_int), ("act", C.c_int), ("fp16", C.c_int), ("out_fp32", C.c_int), ("world", C.c_int),
-        ("send_finish", C.c_int), ("n_comm_ctas", C.c_int), ("max_slots", C.c_int), ("pad0", C.c_int),
+        ("send_finish", C.c_int), ("n_comm_ctas", C.c_int), ("max_slots", C.c_int), ("trace_tiles", C.c_int),
         ("disp", DispatchArgs),
     ]
 

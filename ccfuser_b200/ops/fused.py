@@ -294,7 +294,7 @@ class _FusedMoEFn(torch.autograd.Function):
                  **fm._combine_kw(fm.buf.peer_ptrs(fm.off_comb), cc.row_gate))
         # 5. wait for my rows, sum the k slots
         y = torch.empty(t, d, dtype=x.dtype, device=x.device)
-        fm._wait_and_reduce(fm.comb, t, (d + 255) // 256, y)
+        fm._wait_and_reduce(fm.comb, t, G.combine_units(d), y)
         N.count(3)  # route (2 kernels) + plan; the GEMM launches count themselves
         ctx.fm = fm
         ctx.tokens = t
@@ -368,7 +368,7 @@ class _FusedMoEFn(torch.autograd.Function):
             G.launch(a0=dh, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_COMBINE, n=d, k=f,
                      b_group_rows=f, ld_out=d, **common, **ck)
         dx = torch.empty(t, d, dtype=dy.dtype, device=dy.device)
-        fm._wait_and_reduce(cc.gcomb, t, (d + 255) // 256, dx)
+        fm._wait_and_reduce(cc.gcomb, t, G.combine_units(d), dx)
         if fm.check_every_call:
             cc.check_status("fused MoE backward")
         return dx, dgate.view(t, cfg.top_k), None, dw1, db1, dwg, dbg, dw2, db2, None

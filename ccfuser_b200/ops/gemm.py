@@ -64,7 +64,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
            out0=None, out1=None, out2=None, bias0=None, bias1=None, aux0=None, aux1=None, ld_out=None,
            act=N.ACT_NONE, out_fp32=False, tile_flags=None, row_src=None, row_gate=None,
            peer_comb=None, peer_done=None, world=1, send_finish=0, max_slots=0,
-           dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, wait_ns=DEFAULT_WAIT_NS, grid=0,
+           dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
            workspace: Optional[Workspace] = None):
     """Fill a CcfGemmLaunch and launch on the current stream. a0/b0 are 2-D contiguous views."""
     lib = N.load()
@@ -83,6 +83,10 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
         for i, v in enumerate(peer_done):
             g.peer_done[i] = v
     g.sched, g.status = ws.sched.data_ptr(), ws.status.data_ptr()
+    if trace is not None:
+        # int64 tensor [grid, tiles, 8]: per tile clock64 stamps {0 tile fetched, 1 rows arrived, 2 last load issued,
+        # 3 accumulator free, 4 first operands landed, 5 last MMA committed, 6 accumulator full, 7 epilogue done}
+        g.trace, g.trace_tiles = trace.data_ptr(), int(trace.shape[1])
     g.wait_limit_ns = int(wait_ns)
     g.ld_out = int(ld_out if ld_out is not None else n)
     g.n, g.k, g.num_groups, g.m_per_group, g.kseg = int(n), int(k), int(num_groups), int(m_per_group), int(kseg)
@@ -100,6 +104,12 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     N.check(lib.ccf_gemm_launch(C.byref(L), N.stream_ptr()), "ccf_gemm_launch")
     N.count(1)
     return ws
+
+
+def combine_units(n: int) -> int:
+    """Completion-counter increments per output row of a COMBINE GEMM with n columns: every 256-column tile is
+    stored by two epilogue warps per row quarter (one per 128-column half), and each of them reports its rows."""
+    return 2 * ((n + 255) // 256)
 
 
 def single_group(rows: int, device):

@@ -202,7 +202,7 @@ def test_combine_epilogue_local_rank():
              peer_comb=[comb.data_ptr()], peer_done=[done.data_ptr()], world=1, send_finish=1, max_slots=nslots)
     torch.cuda.synchronize()
     G.Workspace.get(h.device).check("combine")
-    assert int(done[0]) == nslots * (n // 256) + 1
+    assert int(done[0]) == nslots * G.combine_units(n) + 1
     for i, r in enumerate(rows):
         s = int(gb[i])
         ref = F.linear(h[s:s + r].float(), w2[i].float(), b2[i].float()) * row_gate[s:s + r, None]

@@ -40,7 +40,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fp16) {
 // One warp works on chunks of kChunk consecutive slots taken from a shared counter.
 template <int kChunk>
 __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
-  static_assert(kChunk <= 32, "one lane per slot of a chunk");
+  static_assert(kChunk <= 16, "one lane per slot of a chunk; rows of a chunk are held in registers");
   const int S = a.tokens * a.top_k;
   const int lane = threadIdx.x & 31;
   const int vecs = a.d >> 3;  // 16-byte vectors per row
@@ -75,41 +75,70 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
         a.dgate[s] = 0.f;
       }
     }
-    for (int i = 0; i < ns; ++i) {
+    // Source and destination of the chunk's rows (null = dropped or past the end). All kChunk rows are
+    // copied together, one 16-byte column at a time, so kChunk independent loads are in flight per lane
+    // (one row at a time made the copy latency-bound: ~2 us per row and warp).
+    const uint4* src[kChunk];
+    uint4* dst[kChunk];
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) {
       const int row = __shfl_sync(0xffffffffu, my_row, i);
-      if (row < 0) continue;
       const int owner = __shfl_sync(0xffffffffu, my_owner, i);
-      const int s = s0 + i;
-      const int t = s / a.top_k;
-      const uint4* src = reinterpret_cast<const uint4*>(a.x) + static_cast<size_t>(t) * vecs;
-      uint4* dst = reinterpret_cast<uint4*>(a.peer_recv[owner]) + static_cast<size_t>(row) * vecs;
-      if (!a.backward) {
-#pragma unroll 4
-        for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);
-      } else {
-        // rows of the backward pass carry g * dy; the gate gradient is <dy, saved scaled output> / g
-        const float g = __shfl_sync(0xffffffffu, my_gate, i);
-        const uint4* sv = reinterpret_cast<const uint4*>(a.saved_comb) + static_cast<size_t>(s) * vecs;
-        float dot = 0.f;
-#pragma unroll 2
-        for (int v = lane; v < vecs; v += 32) {
-          uint4 xv = __ldg(src + v);
-          uint4 cv = a.saved_comb ? __ldg(sv + v) : make_uint4(0, 0, 0, 0);
-          uint32_t xi[4] = {xv.x, xv.y, xv.z, xv.w};
-          uint32_t ci[4] = {cv.x, cv.y, cv.z, cv.w};
+      const bool on = i < ns && row >= 0;
+      const int t = (s0 + i) / a.top_k;
+      src[i] = on ? reinterpret_cast<const uint4*>(a.x) + static_cast<size_t>(t) * vecs : nullptr;
+      dst[i] = on ? reinterpret_cast<uint4*>(a.peer_recv[owner]) + static_cast<size_t>(row) * vecs : nullptr;
+    }
+    if (!a.backward) {
+      for (int v = lane; v < vecs; v += 32) {
+        uint4 r[kChunk];
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i)
+          if (src[i]) r[i] = __ldg(src[i] + v);
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i)
+          if (dst[i]) dst[i][v] = r[i];
+      }
+    } else {
+      // rows of the backward pass carry g * dy; the gate gradient is <dy, saved scaled output> / g
+      float dot[kChunk], g[kChunk];
+      const uint4* sv[kChunk];
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) {
+        dot[i] = 0.f;
+        g[i] = __shfl_sync(0xffffffffu, my_gate, i);
+        sv[i] = (src[i] && a.saved_comb)
+                    ? reinterpret_cast<const uint4*>(a.saved_comb) + static_cast<size_t>(s0 + i) * vecs
+                    : nullptr;
+      }
+      for (int v = lane; v < vecs; v += 32) {
+        uint4 xr[kChunk], cr[kChunk];
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) {
+          if (src[i]) xr[i] = __ldg(src[i] + v);
+          cr[i] = sv[i] ? __ldg(sv[i] + v) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) {
+          if (!dst[i]) continue;
+          const uint32_t xi[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
+          const uint32_t ci[4] = {cr[i].x, cr[i].y, cr[i].z, cr[i].w};
           uint32_t o[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            float2 xf = unpack2(xi[q], a.fp16);
-            float2 cf = unpack2(ci[q], a.fp16);
-            dot += xf.x * cf.x + xf.y * cf.y;
-            o[q] = pack2(xf.x * g, xf.y * g, a.fp16);
+            const float2 xf = unpack2(xi[q], a.fp16);
+            const float2 cf = unpack2(ci[q], a.fp16);
+            dot[i] += xf.x * cf.x + xf.y * cf.y;
+            o[q] = pack2(xf.x * g[i], xf.y * g[i], a.fp16);
           }
-          dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+          dst[i][v] = make_uint4(o[0], o[1], o[2], o[3]);
         }
+      }
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-        if (lane == 0 && a.dgate) a.dgate[s] = (g != 0.f) ? dot / g : 0.f;
+      for (int i = 0; i < kChunk; ++i) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], off);
+        if (lane == 0 && dst[i] && a.dgate) a.dgate[s0 + i] = (g[i] != 0.f) ? dot[i] / g[i] : 0.f;
       }
     }
     // make the rows visible before the counters move

@@ -129,6 +129,7 @@ def layer_bench(torch, dist, world, rank, steps=5, warmup=3):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     flops = 3 * 2 * 3 * 4096 * 14336 * tokens * 2  # (fwd + 2x bwd) x 2 FLOP x 3 matrices x top-2 rows
+    layer.release()
     del layer
     torch.cuda.empty_cache()
     return {"fwd_bwd_ms": round(float(t.item()), 3), "tflops_per_gpu": round(flops / float(t.item()) / 1e9, 1),

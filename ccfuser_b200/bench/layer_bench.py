@@ -92,6 +92,7 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
            "zipf": args.zipf, "dtype": args.dtype, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
            "total_ms": round(total_ms, 4), "tflops_per_gpu": round(flops / total_ms / 1e9, 1),
            "roofline_frac_of_" + src: round(roof_ms / total_ms, 3), **stats}
+    layer.release()
     del layer
     torch.cuda.empty_cache()
     return out

@@ -80,6 +80,21 @@ class MoELayer(nn.Module):
             y = y.to(inp.dtype)
         return y.reshape(shape[:-1] + (y.shape[-1],))
 
+    def routing_stats(self):
+        """Statistics of the last fused forward call as device tensors (see FusedMoE.routing_stats)."""
+        return self._fused.routing_stats() if self._fused is not None else {}
+
+    def check_status(self):
+        """Host read of the fused kernels' status word; raises MoECommTimeout / MoEOverflow / MoECommError."""
+        if self._fused is not None:
+            self._fused.ctx.check_status("MoELayer")
+
+    def release(self):
+        """Free the symmetric buffers of the fused path (collective)."""
+        if self._fused is not None:
+            self._fused.close()
+            self._fused = None
+
     def extra_repr(self):
         c = self.config
         return (f"experts={c.num_experts} (local {c.experts_per_rank}), top_k={c.top_k}, d_model={c.d_model}, "

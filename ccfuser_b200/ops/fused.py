@@ -36,6 +36,7 @@ import torch.nn.functional as F
 from .. import native as N
 from ..config import env_flag
 from ..parallel.symm import SymmBuffer
+from ..utils.tracing import nvtx_range
 from . import gemm as G
 
 TILE = 128
@@ -207,6 +208,18 @@ class FusedMoE:
             self.ctx.check_status("fused MoE forward")
         return y
 
+    def close(self):
+        """Free this layer's symmetric buffers (collective: call on every rank)."""
+        self.xrecv = self.comb = None
+        self.buf.close()
+
+    def routing_stats(self):
+        """Device tensors describing the last forward call (no host synchronisation): slots per expert before and
+        after the capacity clamp on this rank, the [rank, expert] table of kept rows of every rank, rows this rank
+        received per local expert."""
+        return {"raw_count": self.count_raw, "kept_count": self.count_kept, "count_table": self.table_copy,
+                "recv_rows": self.group_rows, "sent_rows": self.sent_rows[:self.world]}
+
     # ---- launch helpers ------------------------------------------------------------------------
     def _dispatch_args(self, src: torch.Tensor, tokens: int, idx: torch.Tensor, gate_w: torch.Tensor,
                        recv_name_ctx: Optional[str], backward: bool, dgate=None) -> N.DispatchArgs:
@@ -247,55 +260,77 @@ class FusedMoE:
         N.count(2)
 
 
+    # ---- forward stages (also used one by one by the kernel benchmark) ---------------------------
+    def stage_route_plan(self, idx: torch.Tensor, tokens: int):
+        """Positions / kept counts of this rank's slots, count exchange with all ranks, row-layout plan."""
+        lib, cfg, cc = N.load(), self.cfg, self.ctx
+        st = N.stream_ptr()
+        e_tot, e_loc = cfg.num_experts, cfg.experts_per_rank
+        N.check(lib.ccf_route(idx.data_ptr(), tokens * cfg.top_k, e_tot, cfg.capacity(tokens), self.slot_pos.data_ptr(),
+                              cc.block_hist.data_ptr(), cc.block_off.data_ptr(), self.count_raw.data_ptr(),
+                              self.count_kept.data_ptr(), cc.ticket.data_ptr(), st), "ccf_route")
+        cc.epoch += 1
+        p = N.PlanArgs()
+        p.count_kept = self.count_kept.data_ptr()
+        tb, fl = cc.peer("cnt_table"), cc.peer("cnt_flag")
+        for r in range(self.world):
+            p.peer_table[r], p.peer_flag[r] = tb[r], fl[r]
+        p.dst_base, p.group_base, p.group_rows = self.dst_base.data_ptr(), self.group_base.data_ptr(), self.group_rows.data_ptr()
+        p.sent_rows, p.table_copy, p.status = self.sent_rows.data_ptr(), self.table_copy.data_ptr(), cc.ws.status.data_ptr()
+        p.wait_limit_ns = cc.wait_ns
+        p.world, p.my_rank, p.e_total, p.e_loc, p.epoch, p.max_rows = self.world, self.rank, e_tot, e_loc, cc.epoch, self.max_rows
+        N.check(lib.ccf_plan(C.byref(p), st), "ccf_plan")
+        N.count(3)  # route (2 kernels) + plan
+
+    def stage_dispatch_gemm1(self, x, idx, gate_w, w1, b1, wg=None, bg=None, trace=None):
+        """ONE kernel: push this rank's routed rows to their owners and run GEMM-1 (+ bias + activation) on the rows
+        this rank owns, tile by tile as they arrive."""
+        cfg, cc = self.cfg, self.ctx
+        t, d = x.shape
+        f, e_loc = cfg.d_ffn, cfg.experts_per_rank
+        disp = self._dispatch_args(x, t, idx, gate_w, None, backward=False)
+        common = dict(group_base=self.group_base, group_rows=self.group_rows, num_groups=e_loc, tile_flags=cc.tile_flags,
+                      dispatch=disp, n_comm_ctas=cc.n_comm, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace)
+        if cfg.activation == "swiglu":
+            G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), b1=wg.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K,
+                     epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre, out2=self.h_pre2,
+                     bias0=b1, bias1=bg, **common)
+        else:
+            G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT,
+                     n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre, bias0=b1, act=N.ACT_CODE[cfg.activation],
+                     **common)
+        cc.tile_flags.zero_()
+
+    def stage_gemm2_combine(self, w2, b2, trace=None):
+        """GEMM-2 whose epilogue scales by the gate weight and stores every row into its source rank's combine buffer."""
+        cfg, cc = self.cfg, self.ctx
+        d, f, e_loc = cfg.d_model, cfg.d_ffn, cfg.experts_per_rank
+        G.launch(a0=self.h_act, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_COMBINE, n=d, k=f,
+                 group_base=self.group_base, group_rows=self.group_rows, num_groups=e_loc, b_group_rows=d, bias0=b2,
+                 ld_out=d, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace,
+                 **self._combine_kw(self.buf.peer_ptrs(self.off_comb), cc.row_gate))
+
+    def stage_reduce(self, tokens: int, out: torch.Tensor):
+        """Wait until every owner has delivered this rank's rows, then sum the k slots of each token."""
+        self._wait_and_reduce(self.comb, tokens, G.combine_units(self.cfg.d_model), out)
+
+
 class _FusedMoEFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, gate_w, idx, w1, b1, wg, bg, w2, b2, fm: FusedMoE):
-        lib = N.load()
-        cfg, cc = fm.cfg, fm.ctx
-        st = N.stream_ptr()
+        cfg = fm.cfg
         t, d = x.shape
-        f, e_loc, e_tot = cfg.d_ffn, cfg.experts_per_rank, cfg.num_experts
-        s = t * cfg.top_k
         idx = idx.contiguous()
         gate_w = gate_w.contiguous()
-        # 1. positions / counts
-        N.check(lib.ccf_route(idx.data_ptr(), s, e_tot, cfg.capacity(t), fm.slot_pos.data_ptr(),
-                              cc.block_hist.data_ptr(), cc.block_off.data_ptr(), fm.count_raw.data_ptr(),
-                              fm.count_kept.data_ptr(), cc.ticket.data_ptr(), st), "ccf_route")
-        # 2. count exchange + plan
-        cc.epoch += 1
-        p = N.PlanArgs()
-        p.count_kept = fm.count_kept.data_ptr()
-        tb, fl = cc.peer("cnt_table"), cc.peer("cnt_flag")
-        for r in range(fm.world):
-            p.peer_table[r], p.peer_flag[r] = tb[r], fl[r]
-        p.dst_base, p.group_base, p.group_rows = fm.dst_base.data_ptr(), fm.group_base.data_ptr(), fm.group_rows.data_ptr()
-        p.sent_rows, p.table_copy, p.status = fm.sent_rows.data_ptr(), fm.table_copy.data_ptr(), cc.ws.status.data_ptr()
-        p.wait_limit_ns = cc.wait_ns
-        p.world, p.my_rank, p.e_total, p.e_loc, p.epoch, p.max_rows = fm.world, fm.rank, e_tot, e_loc, cc.epoch, fm.max_rows
-        N.check(lib.ccf_plan(C.byref(p), st), "ccf_plan")
-        # 3. dispatch + GEMM-1 (one kernel)
-        disp = fm._dispatch_args(x, t, idx, gate_w, None, backward=False)
-        common = dict(group_base=fm.group_base, group_rows=fm.group_rows, num_groups=e_loc, tile_flags=cc.tile_flags,
-                      dispatch=disp, n_comm_ctas=cc.n_comm, wait_ns=cc.wait_ns, workspace=cc.ws)
-        if cfg.activation == "swiglu":
-            G.launch(a0=fm.xrecv, b0=w1.view(e_loc * f, d), b1=wg.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K,
-                     epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=fm.h_act, out1=fm.h_pre, out2=fm.h_pre2,
-                     bias0=b1, bias1=bg, **common)
-        else:
-            G.launch(a0=fm.xrecv, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT,
-                     n=f, k=d, b_group_rows=f, out0=fm.h_act, out1=fm.h_pre, bias0=b1, act=N.ACT_CODE[cfg.activation],
-                     **common)
-        cc.tile_flags.zero_()
-        # 4. GEMM-2 + combine into the source ranks' buffers
-        G.launch(a0=fm.h_act, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_COMBINE, n=d, k=f,
-                 group_base=fm.group_base, group_rows=fm.group_rows, num_groups=e_loc, b_group_rows=d, bias0=b2,
-                 ld_out=d, wait_ns=cc.wait_ns, workspace=cc.ws,
-                 **fm._combine_kw(fm.buf.peer_ptrs(fm.off_comb), cc.row_gate))
-        # 5. wait for my rows, sum the k slots
+        with nvtx_range("moe.route_plan"):
+            fm.stage_route_plan(idx, t)
+        with nvtx_range("moe.dispatch_gemm1"):
+            fm.stage_dispatch_gemm1(x, idx, gate_w, w1, b1, wg, bg)
+        with nvtx_range("moe.gemm2_combine"):
+            fm.stage_gemm2_combine(w2, b2)
         y = torch.empty(t, d, dtype=x.dtype, device=x.device)
-        fm._wait_and_reduce(fm.comb, t, G.combine_units(d), y)
-        N.count(3)  # route (2 kernels) + plan; the GEMM launches count themselves
+        with nvtx_range("moe.reduce"):
+            fm.stage_reduce(t, y)
         ctx.fm = fm
         ctx.tokens = t
         ctx.save_for_backward(idx, gate_w, w1, wg, w2)

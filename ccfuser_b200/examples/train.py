@@ -1,0 +1,152 @@
+"""Synthetic-data training loops for the three model families of the reference's end-to-end experiment
+(GPT-2, BERT question answering, Transformer-XL; mix_moe/ae/fig11_data.sh, mix_moe/mix_moe/examples/models/
+moe_gpt_ddp.py, moe_bert_ddp.py, mix_moe/mix_moe/examples/transformer-xl/train_ddp.py), each as a dense model, with
+the NCCL all-to-all MoE baseline, or with the fused MoE layer.
+
+    python -m ccfuser_b200.examples.train --model bert --variant fused --steps 20
+    python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 -m ccfuser_b200.examples.train \
+        --model txl --variant fused
+
+Prints ``STEP-i: step_time = ... ms`` lines and a ``[Summary] Average synchronized step_time`` line like the
+reference scripts (mix_moe/mix_moe/examples/mix_moe_ddp.py:199,210), plus one JSON line with the same numbers.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..models.bert_moe import BertMoEConfig, BertMoEForQuestionAnswering
+from ..models.gpt_moe import GPTMoE, GPTMoEConfig
+from ..models.transformer_xl_moe import TransformerXLMoE, TransformerXLMoEConfig
+from ..parallel.ddp import wrap_ddp
+from ..utils.dist import init_distributed
+
+
+class _GPTStep(nn.Module):
+    def __init__(self, m):
+        super().__init__()
+        self.m = m
+
+    def forward(self, batch):
+        return self.m(batch["ids"], batch["labels"])
+
+
+class _BertStep(nn.Module):
+    def __init__(self, m):
+        super().__init__()
+        self.m = m
+
+    def forward(self, batch):
+        return self.m(batch["ids"], batch["mask"], batch["types"], batch["start"], batch["end"])
+
+
+class _TXLStep(nn.Module):
+    def __init__(self, m):
+        super().__init__()
+        self.m = m
+        self.mems = None
+
+    def forward(self, batch):
+        loss, self.mems = self.m(batch["ids"], batch["labels"], self.mems)
+        return loss
+
+
+def build(args, world, dev):
+    backend = {"dense": "auto", "nccl": "nccl", "fused": "fused"}[args.variant]
+    moe = args.variant != "dense"
+    dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
+    g = torch.Generator().manual_seed(1 + (dist.get_rank() if dist.is_initialized() else 0))
+    if args.model == "gpt":
+        b, s = args.batch or 8, args.seq or 1024
+        c = GPTMoEConfig(n_layer=args.layers or 12, n_head=12, d_model=768, d_ffn=3072, seq_len=s,
+                         moe_every=(args.moe_every if moe else 0), num_experts=args.experts_per_gpu * world, top_k=args.top_k,
+                         capacity_factor=args.cf or None, ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
+        model = _GPTStep(GPTMoE(c, device=dev))
+        ids = torch.randint(0, c.vocab_size, (b, s), generator=g)
+        batch = {"ids": ids, "labels": ids.roll(-1, 1)}
+    elif args.model == "bert":
+        b, s = args.batch or 32, args.seq or 512
+        c = BertMoEConfig(n_layer=args.layers or 12, moe_layers=(2, 5, 8, 11) if moe else (), max_position=s,
+                          num_experts=args.experts_per_gpu * world, top_k=args.top_k, capacity_factor=args.cf or None,
+                          ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
+        model = _BertStep(BertMoEForQuestionAnswering(c, device=dev))
+        batch = {"ids": torch.randint(0, c.vocab_size, (b, s), generator=g), "mask": torch.ones(b, s, dtype=torch.long),
+                 "types": torch.zeros(b, s, dtype=torch.long), "start": torch.randint(0, s, (b,), generator=g),
+                 "end": torch.randint(0, s, (b,), generator=g)}
+    else:
+        b, s = args.batch or 16, args.seq or 512
+        c = TransformerXLMoEConfig(n_layer=args.layers or 12, tgt_len=s, mem_len=s, moe=moe,
+                                   num_experts=args.experts_per_gpu * world, top_k=args.top_k,
+                                   capacity_factor=args.cf or None, ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
+        model = _TXLStep(TransformerXLMoE(c, device=dev))
+        batch = {"ids": torch.randint(1, 50, (b, s), generator=g), "labels": torch.randint(1, 50, (b, s), generator=g)}
+    return model, {k: v.to(dev) for k, v in batch.items()}, b * s
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="gpt", choices=["gpt", "bert", "txl"])
+    ap.add_argument("--variant", default="fused", choices=["dense", "nccl", "fused"])
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--experts-per-gpu", type=int, default=16)
+    ap.add_argument("--top-k", type=int, default=2)
+    ap.add_argument("--moe-every", type=int, default=1)
+    ap.add_argument("--cf", type=float, default=0.0)
+    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--optimizer", default="sgd", choices=["sgd", "adamw"])
+    ap.add_argument("--lr", type=float, default=1e-4)
+    args = ap.parse_args()
+    rank, _, world = init_distributed()
+    dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    model, batch, tokens = build(args, world, dev)
+    wrapped = wrap_ddp(model) if world > 1 else model
+    params = [p for p in model.parameters() if p.requires_grad]
+    opt = torch.optim.SGD(params, lr=args.lr) if args.optimizer == "sgd" else torch.optim.AdamW(params, lr=args.lr)
+    times = []
+    import time
+    for i in range(args.warmup + args.steps):
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+        opt.zero_grad(set_to_none=True)
+        loss = wrapped(batch)
+        loss.backward()
+        opt.step()
+        if dev.type == "cuda":
+            e.record()
+            torch.cuda.synchronize()
+            ms = s.elapsed_time(e)
+        else:
+            ms = (time.perf_counter() - t0) * 1e3
+        if i >= args.warmup:
+            times.append(ms)
+        if rank == 0 and i % 10 == 0:
+            print(f"STEP-{i}: step_time = {ms:.3f} ms, loss = {float(loss):.4f}", flush=True)
+    avg = sum(times) / max(1, len(times))
+    t = torch.tensor([avg], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(f"{args.variant} {args.model} {args.experts_per_gpu} [Summary] Average synchronized step_time = {float(t):.3f} ms")
+        print(json.dumps({"bench": "e2e", "model": args.model, "variant": args.variant, "n_gpus": world,
+                          "experts_per_gpu": args.experts_per_gpu, "step_ms": round(float(t), 3),
+                          "tokens_per_s": round(tokens * world / float(t) * 1e3, 1), "final_loss": round(float(loss), 4)}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -138,6 +138,11 @@ def layer_bench(torch, dist, world, rank, steps=5, warmup=3):
 
 def main():
     args = parse()
+    wd = float(os.environ.get("CCFUSER_BENCH_WATCHDOG_S", "0"))
+    if wd > 0:
+        # a stuck run prints every thread's Python stack and exits instead of waiting for an outer timeout
+        import faulthandler
+        faulthandler.dump_traceback_later(wd, exit=True)
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus > 1 and "RANK" not in os.environ:
@@ -159,7 +164,9 @@ def main():
     torch.manual_seed(1234 + rank)
     backend = "fused" if args.impl == "ours" else "nccl"
     seq = 1024
-    c = GPTMoEConfig(n_layer=args.layers, ep_size=world, backend=backend, max_tokens=args.batch * seq, seq_len=seq)
+    # no capacity factor (nothing is dropped, as in the reference); the receive buffers hold 4x the balanced load
+    c = GPTMoEConfig(n_layer=args.layers, ep_size=world, backend=backend, max_tokens=args.batch * seq, seq_len=seq,
+                     recv_factor=4.0)
     model = GPTMoE(c, device=dev)
     trainer = TrainStep(model, lr=1e-4, optimizer="sgd")
     tokens_per_step = args.batch * seq * world
@@ -208,10 +215,23 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms2 = float(t[0]), float(t[1])
+    overflow = None
     for m in model.moe_layers():
         if m._fused is not None:
-            m._fused.ctx.check_status("bench")
+            from ccfuser_b200 import MoEOverflow
+            try:
+                m._fused.ctx.check_status("bench")
+            except MoEOverflow as ex:
+                overflow = str(ex)
             break
+    imbalance = None
+    if args.impl == "ours":
+        # routing statistics of the last step: most loaded rank relative to the balanced load
+        loads = [float(m._fused.group_rows.sum()) for m in model.moe_layers() if m._fused is not None]
+        t_l = torch.tensor([max(loads) if loads else 0.0], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t_l, op=dist.ReduceOp.MAX)
+        imbalance = round(float(t_l) / (args.batch * seq * 2), 3)
     layer = None
     if not args.no_layer_bench and args.impl == "ours":
         del trainer, model
@@ -230,7 +250,8 @@ def main():
             "config": {"model": f"GPT-MoE {args.layers}L d2048 h16 seq1024 vocab50257, MoE every other layer (64 experts, top-2, ffn 8192, GELU)",
                        "global_batch": args.batch * world, "seq_len": seq, "parallelism": f"ep{world}" + (f"+dp{world}" if world > 1 else ""),
                        "optimizer": "sgd", "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2",
-                       "loss": round(float(loss), 4)},
+                       "loss": round(float(loss), 4), "capacity_factor": None, "max_rank_load_over_balanced": imbalance,
+                       "overflow": overflow},
             "clocks": clocks,
             "e2e": {"value": round(tokens_per_step * args.steps / (ms2 / 1e3), 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": 2 * args.batch * seq * 8, "d2h_bytes_per_step": 4, "last_loss": round(last, 4)},

@@ -15,8 +15,22 @@
 
 namespace ccf {
 
+// First hard error wins the status word; an overflow (rows dropped because a receive buffer is full) is only a note
+// and is recorded in the second word so that it can neither hide nor be hidden by a time-out.
 __device__ __forceinline__ void report_status(int* status, int code, int detail) {
-  if (status) atomicCAS(status, 0, (detail << 8) | code);
+  if (!status) return;
+  if (code == CCF_ERR_OVERFLOW) atomicAdd(status + 1, 1);
+  else atomicCAS(status, 0, (detail << 8) | code);
+}
+
+// Once a time-out (or any other hard error) is on record, later waits give up after a millisecond instead of their
+// full limit, so one lost peer costs one limit, not one limit per kernel. An overflow is not a reason to hurry.
+__device__ __forceinline__ unsigned long long fail_fast_limit(const int* status, unsigned long long limit_ns) {
+  if (status != nullptr) {
+    const int code = *reinterpret_cast<const volatile int*>(status) & 0xff;
+    if (code == CCF_ERR_MBAR_TIMEOUT || code == CCF_ERR_FLAG_TIMEOUT) return 1000000ull;
+  }
+  return limit_ns;
 }
 
 __device__ __forceinline__ float2 unpack2(uint32_t u, int fp16) {

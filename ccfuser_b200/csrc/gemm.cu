@@ -297,7 +297,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   volatile int* abort_word = &ctrl->abort_word;
-  const uint64_t limit = args.wait_limit_ns;
+  const uint64_t limit = fail_fast_limit(args.status, args.wait_limit_ns);
   constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
 
   // ---- set-up ------------------------------------------------------------------------------------

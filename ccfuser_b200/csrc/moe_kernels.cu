@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanA
   if (tid < a.world) st_release_sys(a.peer_flag[tid] + a.my_rank, a.epoch);
   // 2. wait for everyone's counts (my own table, local memory)
   if (tid < a.world) {
-    if (!wait_flag_ge(a.peer_flag[a.my_rank] + tid, a.epoch, a.wait_limit_ns)) {
+    if (!wait_flag_ge(a.peer_flag[a.my_rank] + tid, a.epoch, fail_fast_limit(a.status, a.wait_limit_ns))) {
       report_status(a.status, CCF_ERR_FLAG_TIMEOUT, 0x800000 | tid);
       failed = 1;
     }
@@ -219,7 +219,10 @@ __global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanA
       const int e = tid * a.e_loc + i;
       base[e] = run;
       run += (rows[e] + 127) & ~127;
-      sent += a.count_kept[e];
+      // rows of mine that fit into the owner's buffer: the rest is rejected by the dispatch role and must not be
+      // waited for (source and owner derive the same limit from the same table)
+      const int first = run - ((rows[e] + 127) & ~127) + myoff[e];
+      sent += max(0, min(a.count_kept[e], a.max_rows - first));
     }
     a.sent_rows[tid] = sent;
     if (run > a.max_rows) report_status(a.status, CCF_ERR_OVERFLOW, tid);
@@ -259,7 +262,8 @@ __global__ void combine_wait_kernel(const int* done, int* cum, const int* sent_r
   const int o = threadIdx.x;
   if (o >= world) return;
   const int target = cum[o] + sent_rows[o] * n_tiles + 1;
-  if (!wait_flag_ge(done + o, target, limit_ns)) report_status(status, CCF_ERR_FLAG_TIMEOUT, 0x400000 | o);
+  if (!wait_flag_ge(done + o, target, fail_fast_limit(status, limit_ns)))
+    report_status(status, CCF_ERR_FLAG_TIMEOUT, 0x400000 | o);
   cum[o] = target;
 }
 

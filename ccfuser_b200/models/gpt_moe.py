@@ -38,11 +38,12 @@ class GPTMoEConfig:
     max_tokens: int = 8192        # tokens per rank per step (batch * seq_len)
     dtype: torch.dtype = torch.bfloat16
     aux_loss_coef: float = 0.0
+    recv_factor: float = 2.0      # receive-buffer size of a rank relative to the balanced load (no capacity factor)
 
     def moe_config(self) -> MoEConfig:
         return MoEConfig(d_model=self.d_model, d_ffn=self.d_ffn, num_experts=self.num_experts, top_k=self.top_k,
                          capacity_factor=self.capacity_factor, activation=self.activation, dtype=self.dtype,
-                         ep_size=self.ep_size, backend=self.backend, max_tokens=self.max_tokens)
+                         ep_size=self.ep_size, backend=self.backend, max_tokens=self.max_tokens, recv_factor=self.recv_factor)
 
     def flops_per_token(self) -> float:
         """Forward+backward model FLOPs per token (3 x forward; attention scores included)."""

@@ -21,7 +21,7 @@ class Workspace:
 
     def __init__(self, device):
         self.sched = torch.zeros(8, dtype=torch.int32, device=device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(2, dtype=torch.int32, device=device)  # [first hard error, overflow count]
         self.dispatch_done = torch.zeros(1, dtype=torch.int32, device=device)
 
     @classmethod
@@ -35,9 +35,15 @@ class Workspace:
 
     def check(self, what: str = "kernel"):
         """Host read of the status word; raises if a kernel recorded an error, then clears it."""
-        v = int(self.status.item())
-        if v:
+        both = self.status.tolist()
+        v, overflow = int(both[0]), int(both[1])
+        if v or overflow:
             self.status.zero_()
+        if overflow and not v:
+            from ..errors import MoEOverflow
+            raise MoEOverflow(f"{what}: {overflow} rows did not fit a receive buffer and were dropped "
+                              f"(raise config.recv_factor or set a capacity_factor)")
+        if v:
             code, detail = v & 0xff, v >> 8
             from ..errors import MoECommError, MoECommTimeout, MoEOverflow
             msg = f"{what}: {N.ERR_NAMES.get(code, 'error')} (code {code}, detail {detail:#x})"

@@ -143,6 +143,39 @@ def test_fused_layer_module_api_trains():
     assert torch.equal(a, b), "the fused path is deterministic"
 
 
+def test_receive_buffer_overflow_drops_rows_consistently_and_is_reported():
+    """A receive buffer that is too small: the surplus rows are dropped on both sides (no wait runs out), the
+    tokens whose slots all fitted still match the oracle, and check_status raises MoEOverflow."""
+    import time
+    from ccfuser_b200 import MoEConfig, MoELayer, MoEOverflow
+    from ccfuser_b200.ops.fused import topk_softmax, _FusedMoEFn
+    torch.manual_seed(0)
+    tokens = 2048
+    cfg = MoEConfig(d_model=256, d_ffn=512, num_experts=4, top_k=2, capacity_factor=None, activation="gelu",
+                    dtype=torch.bfloat16, ep_size=1, backend="fused", max_tokens=tokens, recv_factor=0.5)
+    layer = MoELayer(cfg, device="cuda")
+    with torch.no_grad():
+        for p in layer.parameters():
+            p.copy_(torch.randn_like(p) * 0.05)
+    fm = layer._fused_impl()
+    assert fm.max_rows < tokens * 2
+    x = (torch.randn(tokens, 256, device="cuda") * 0.5).bfloat16()
+    idx, w = topk_softmax(layer.gate.logits(x), 2)
+    ex = layer.experts
+    t0 = time.time()
+    with torch.no_grad():
+        y = _FusedMoEFn.apply(x, w, idx, ex.htoh4.weight, ex.htoh4.bias, None, None, ex.h4toh.weight, ex.h4toh.bias, fm)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 3.0, "an overflow must not make any wait run into its limit"
+    with pytest.raises(MoEOverflow):
+        fm.ctx.check_status("overflow test")
+    yr, *_ = _oracle_with_routing(cfg, layer, x, idx, w)
+    kept = (fm.slot_row[:tokens * 2].view(tokens, 2) >= 0).all(1)
+    assert 0 < int(kept.sum()) < tokens
+    assert _rel(y[kept], yr[kept].detach()) < 3e-2
+    assert torch.isfinite(y.float()).all()
+
+
 def test_bounded_wait_reports_timeout_without_hanging():
     """A wait on a flag that nothing sets gives up after its limit and records a status; the context stays usable."""
     from ccfuser_b200 import native as N, MoECommTimeout

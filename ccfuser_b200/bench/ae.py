@@ -1,0 +1,130 @@
+"""Runs the three evaluation experiments of the reference and writes CSV files with its column names, so results
+can be laid next to its recorded data (mix_moe/ae/output_data/moe_layer_pcie.csv, e2e_model.csv,
+kernel_eval_nvlink.csv, kernel_eval_expert.csv; produced there by mix_moe/ae/fig10_data.sh, fig11_data.sh,
+fig12_data.sh with grep/awk over log files).
+
+    python -m ccfuser_b200.bench.ae --fig 10 --gpus 4 --out results/
+    python -m ccfuser_b200.bench.ae --fig 11 --gpus 4 --out results/
+    python -m ccfuser_b200.bench.ae --fig 12 --gpus 4 --out results/
+
+fig 10  MoE layer fwd+bwd, d_model 1024, ffn 4096, 8192 tokens/GPU, top-2, GELU, experts/GPU in {4,8,16,32,64};
+        rows "ccfuser_b200" (fused) and "nccl_a2a" (all_to_all_single + library GEMM baseline).
+fig 11  end-to-end step time of GPT-2 small / BERT-base QA / Transformer-XL as dense, baseline MoE and fused MoE.
+fig 12  fused dispatch+GEMM-1 ("AG") and GEMM-2+combine ("GA") against all-to-all + GEMM, over the remote fraction
+        and over experts/GPU.
+Each experiment runs as torchrun children of this process; every number is device-timed and max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import json
+import os
+import subprocess
+import sys
+
+
+def torchrun(gpus: int, module: str, args, port: int, timeout=1800):
+    if gpus == 1:
+        cmd = [sys.executable, "-m", module] + args
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", module] + args
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    recs = []
+    for line in out.stdout.splitlines():
+        line = line.strip()
+        if line.startswith("{"):
+            try:
+                recs.append(json.loads(line))
+            except ValueError:
+                pass
+    if out.returncode != 0 and not recs:
+        sys.stderr.write(out.stdout[-2000:] + out.stderr[-4000:])
+    return recs
+
+
+def fig10(gpus, outdir, iters):
+    recs = torchrun(gpus, "ccfuser_b200.bench.layer_bench",
+                    ["--d-model", "1024", "--d-ffn", "4096", "--tokens", "8192", "--act", "gelu", "--cf", "0",
+                     "--experts-per-gpu", "4,8,16,32,64", "--backends", "fused,nccl", "--iters", str(iters)], 29811)
+    path = os.path.join(outdir, f"moe_layer_b200_x{gpus}.csv")
+    with open(path, "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["name", "num_expert", "total_time", "forward_time", "backward_time"])
+        for name, backend in (("ccfuser_b200", "fused"), ("nccl_a2a", "nccl")):
+            for r in recs:
+                if r["backend"] == backend:
+                    w.writerow([name, r["experts_per_gpu"], r["total_ms"], r["fwd_ms"], r["bwd_ms"]])
+    return path, recs
+
+
+def fig11(gpus, outdir, steps):
+    table = {}
+    recs = []
+    for model in ("gpt", "bert", "txl"):
+        for variant in ("dense", "nccl", "fused"):
+            extra = ["--moe-every", "1"] if model == "gpt" else []
+            r = torchrun(gpus, "ccfuser_b200.examples.train",
+                         ["--model", model, "--variant", variant, "--steps", str(steps), "--warmup", "5"] + extra, 29821)
+            if r:
+                table[(variant, model)] = r[-1]["step_ms"]
+                recs.append(r[-1])
+    path = os.path.join(outdir, f"e2e_model_b200_x{gpus}.csv")
+    with open(path, "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["name", "MOE-GPT", "MOE-BERT", "MOE-Transformer-xl"])
+        for name, variant in (("naive", "dense"), ("nccl_a2a", "nccl"), ("ccfuser_b200", "fused")):
+            w.writerow([name] + [table.get((variant, m), "") for m in ("gpt", "bert", "txl")])
+    return path, recs
+
+
+def fig12(gpus, outdir, iters):
+    paths, allrecs = [], []
+    for sweep, fname, extra_col in (("remote", f"kernel_eval_b200_x{gpus}.csv", False),
+                                    ("experts", f"kernel_eval_expert_b200_x{gpus}.csv", True)):
+        recs = torchrun(gpus, "ccfuser_b200.bench.kernel_bench", ["--sweep", sweep, "--iters", str(iters)], 29831)
+        allrecs += recs
+        path = os.path.join(outdir, fname)
+        with open(path, "w", newline="") as f:
+            w = csv.writer(f)
+            w.writerow(["kernel", "locality", "time", "all2all"] + (["num_expert"] if extra_col else []))
+            for r in recs:
+                tail = [r["experts_per_gpu"]] if extra_col else []
+                w.writerow(["AG", r["remote_frac"], r["fused_ag_ms"], 0] + tail)
+                w.writerow(["All2All-GEMM", r["remote_frac"], r["nccl_a2a_gemm1_ms"], r["nccl_a2a_in_ms"]] + tail)
+                w.writerow(["GA", r["remote_frac"], r["fused_ga_ms"], 0] + tail)
+                w.writerow(["GEMM-All2All", r["remote_frac"], r["gemm2_nccl_a2a_ms"], r["nccl_a2a_out_ms"]] + tail)
+        paths.append(path)
+    return paths, allrecs
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--fig", default="10,11,12")
+    ap.add_argument("--gpus", type=int, default=4)
+    ap.add_argument("--out", default="results")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    args = ap.parse_args()
+    os.makedirs(args.out, exist_ok=True)
+    figs = args.fig.split(",")
+    summary = {}
+    if "10" in figs:
+        path, recs = fig10(args.gpus, args.out, args.iters)
+        summary["fig10"] = recs
+        print("fig10 ->", path, flush=True)
+    if "12" in figs:
+        paths, recs = fig12(args.gpus, args.out, args.iters)
+        summary["fig12"] = recs
+        print("fig12 ->", paths, flush=True)
+    if "11" in figs:
+        path, recs = fig11(args.gpus, args.out, args.steps)
+        summary["fig11"] = recs
+        print("fig11 ->", path, flush=True)
+    with open(os.path.join(args.out, f"ae_summary_x{args.gpus}.json"), "w") as f:
+        json.dump(summary, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

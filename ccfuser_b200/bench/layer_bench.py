@@ -81,6 +81,13 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
                  "remote_frac": round(1 - float(table[rank, rank * experts_per_gpu:(rank + 1) * experts_per_gpu].sum()) / max(1, kept), 4)}
     mats = 3 if args.act == "swiglu" else 2
     rows = tokens * args.top_k
+    if backend == "fused":
+        # rows this rank's experts actually processed (dropped slots do no work); max over ranks like the time
+        rr = torch.tensor([float(stats["recv_rows_this_rank"])], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(rr, op=dist.ReduceOp.MAX)
+        rows = int(rr.item())
+        stats["max_recv_rows_over_ranks"] = rows
     flops_fwd = 2.0 * mats * args.d_model * args.d_ffn * rows
     flops = flops_fwd * (1 if args.forward_only else 3)
     peak, _, src = measured_peaks()

@@ -153,10 +153,32 @@ def run(args, world, rank, e_loc, remote_frac):
         else:
             back.copy_(o)
 
+    # stronger baseline: regroup the received rows to expert-major and use the library grouped GEMM
+    seg = recv_cnt.reshape(-1).tolist()
+    starts = [0]
+    for c in seg:
+        starts.append(starts[-1] + c)
+    perm = torch.cat([torch.arange(starts[r * e_loc + e], starts[r * e_loc + e + 1]) for e in range(e_loc) for r in range(world)]
+                     + [torch.zeros(0, dtype=torch.long)]).to("cuda")
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(perm.numel(), device="cuda")
+    offs = torch.tensor(per_expert, device="cuda", dtype=torch.int32).cumsum(0).to(torch.int32)
+    has_grouped = hasattr(torch, "_grouped_mm")
+
+    def gemm1_grouped():
+        return torch._grouped_mm(recv.index_select(0, perm), w1t.transpose(1, 2), offs=offs)
+
+    hg = gemm1_grouped() if has_grouped else None
+
+    def gemm2_grouped():
+        o.copy_(torch._grouped_mm(hg, w2t.transpose(1, 2), offs=offs).index_select(0, inv))
+
     base_a2a_in = timed(a2a_in, args.iters, args.warmup, world)
     base_ag = timed(lambda: (a2a_in(), gemm1()), args.iters, args.warmup, world)
     base_a2a_out = timed(a2a_out, args.iters, args.warmup, world)
     base_ga = timed(lambda: (gemm2(), a2a_out()), args.iters, args.warmup, world)
+    grouped_ag = timed(lambda: (a2a_in(), gemm1_grouped()), args.iters, args.warmup, world) if has_grouped else None
+    grouped_ga = timed(lambda: (gemm2_grouped(), a2a_out()), args.iters, args.warmup, world) if has_grouped else None
     layer.release()
     del layer
     torch.cuda.empty_cache()
@@ -164,7 +186,11 @@ def run(args, world, rank, e_loc, remote_frac):
             "experts_per_gpu": e_loc, "remote_frac": remote_frac,
             "fused_ag_ms": round(fused_ag, 4), "nccl_a2a_gemm1_ms": round(base_ag, 4), "nccl_a2a_in_ms": round(base_a2a_in, 4),
             "fused_ga_ms": round(fused_ga, 4), "gemm2_nccl_a2a_ms": round(base_ga, 4), "nccl_a2a_out_ms": round(base_a2a_out, 4),
-            "ag_speedup": round(base_ag / fused_ag, 2), "ga_speedup": round(base_ga / fused_ga, 2)}
+            "nccl_a2a_grouped_gemm1_ms": None if grouped_ag is None else round(grouped_ag, 4),
+            "grouped_gemm2_nccl_a2a_ms": None if grouped_ga is None else round(grouped_ga, 4),
+            "ag_speedup": round(base_ag / fused_ag, 2), "ga_speedup": round(base_ga / fused_ga, 2),
+            "ag_speedup_vs_grouped": None if grouped_ag is None else round(grouped_ag / fused_ag, 2),
+            "ga_speedup_vs_grouped": None if grouped_ga is None else round(grouped_ga / fused_ga, 2)}
 
 
 def main():

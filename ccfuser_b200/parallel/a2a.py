@@ -50,6 +50,32 @@ def exchange_counts(count: torch.Tensor, world: int, group) -> torch.Tensor:
     return table.view(world, count.numel())
 
 
+def _use_grouped_mm(rows: torch.Tensor, experts) -> bool:
+    return (rows.is_cuda and rows.dtype == torch.bfloat16 and hasattr(torch, "_grouped_mm")
+            and rows.shape[1] % 8 == 0 and experts.htoh4.weight.shape[1] % 8 == 0)
+
+
+def _experts_grouped_mm(rows: torch.Tensor, per_expert: List[int], experts) -> torch.Tensor:
+    """All local experts with the library grouped GEMM (one call per projection instead of a loop over experts)."""
+    import torch.nn.functional as F
+    offs = torch.tensor(per_expert, device=rows.device, dtype=torch.int32).cumsum(0).to(torch.int32)
+    eid = torch.repeat_interleave(torch.arange(len(per_expert), device=rows.device),
+                                  torch.tensor(per_expert, device=rows.device))
+
+    def proj(x, lin):
+        y = torch._grouped_mm(x, lin.weight.transpose(1, 2), offs=offs)
+        return y if lin.bias is None else y + lin.bias[eid]
+
+    h = proj(rows, experts.htoh4)
+    if experts.activation == "swiglu":
+        h = F.silu(proj(rows, experts.htoh4_gate)) * h
+    elif experts.activation == "gelu":
+        h = F.gelu(h)
+    else:
+        h = F.relu(h)
+    return proj(h, experts.h4toh)
+
+
 def moe_forward_a2a(x: torch.Tensor, topk_idx: torch.Tensor, topk_score: torch.Tensor, experts,
                     *, num_experts: int, capacity: int, group, grouped_mm: bool = False) -> torch.Tensor:
     """x [T,d]; topk_idx/topk_score [T,k]. Differentiable w.r.t. x, topk_score and the expert params."""
@@ -72,16 +98,21 @@ def moe_forward_a2a(x: torch.Tensor, topk_idx: torch.Tensor, topk_score: torch.T
     # regroup to expert-major: rows of (src r, expert e) are contiguous in `recv`
     rc = recv_cnt.reshape(-1).tolist()
     pieces = list(torch.split(recv, rc, 0))
+    seg_ids = [r * e_loc + e for e in range(e_loc) for r in range(world)]          # expert-major order of segments
+    rows = torch.cat([pieces[i] for i in seg_ids], 0) if pieces else recv
+    per_expert = [sum(rc[r * e_loc + e] for r in range(world)) for e in range(e_loc)]
+    if _use_grouped_mm(rows, experts):
+        out = _experts_grouped_mm(rows, per_expert, experts)
+    else:
+        outs_e = []
+        for e, rows_e in enumerate(torch.split(rows, per_expert, 0)):
+            outs_e.append(experts.expert_forward(e, rows_e) if rows_e.shape[0]
+                          else rows_e.new_zeros(0, experts.h4toh.weight.shape[1]))
+        out = torch.cat(outs_e, 0)
+    # back to the (src, expert) order of the exchange
     outs: List[Optional[torch.Tensor]] = [None] * len(pieces)
-    for e in range(e_loc):
-        idxs = [r * e_loc + e for r in range(world)]
-        rows = torch.cat([pieces[i] for i in idxs], 0)
-        if rows.shape[0] == 0:
-            o = rows.new_zeros(0, experts.h4toh.weight.shape[1])
-        else:
-            o = experts.expert_forward(e, rows)
-        for i, piece in zip(idxs, torch.split(o, [rc[i] for i in idxs], 0)):
-            outs[i] = piece
+    for i, piece in zip(seg_ids, torch.split(out, [rc[i] for i in seg_ids], 0)):
+        outs[i] = piece
     back = torch.cat(outs, 0) if outs else recv.new_zeros(0, d)
     ret = all_to_all(back, send_per_rank, recv_per_rank, group)     # same order as send_rows
     w = topk_score.reshape(-1)[order].to(ret.dtype).unsqueeze(1)

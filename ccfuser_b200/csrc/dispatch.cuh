@@ -51,19 +51,19 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fp16) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// One warp works on chunks of kChunk consecutive slots taken from a shared counter.
+// One warp works on chunks of kChunk consecutive slots. Chunks are assigned statically
+// (chunk = warp index within the dispatching CTAs + k * number of such warps): every CTA that runs the role takes
+// part from the start, so a shared work counter would only add an atomic round trip per chunk.
 template <int kChunk>
-__device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
+__device__ void dispatch_rows(const CcfDispatchArgs& a, int* status, int cta, int n_ctas) {
   static_assert(kChunk <= 16, "one lane per slot of a chunk; rows of a chunk are held in registers");
   const int S = a.tokens * a.top_k;
   const int lane = threadIdx.x & 31;
   const int vecs = a.d >> 3;  // 16-byte vectors per row
-  for (;;) {
-    int c = 0;
-    if (lane == 0) c = atomicAdd(a.work_counter, 1);
-    c = __shfl_sync(0xffffffffu, c, 0);
+  const int warps_per_cta = blockDim.x >> 5;
+  const int n_chunks = (S + kChunk - 1) / kChunk;
+  for (int c = cta * warps_per_cta + (threadIdx.x >> 5); c < n_chunks; c += n_ctas * warps_per_cta) {
     const int s0 = c * kChunk;
-    if (s0 >= S) break;
     const int ns = min(kChunk, S - s0);
     // lane i plans slot s0 + i
     int my_row = -1, my_owner = 0;
@@ -155,10 +155,16 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
         if (lane == 0 && dst[i] && a.dgate) a.dgate[s0 + i] = (g[i] != 0.f) ? dot[i] / g[i] : 0.f;
       }
     }
-    // make the rows visible before the counters move
-    __threadfence_system();
+    // The counters move with release semantics at system scope after a warp barrier: the barrier orders the other
+    // lanes' row stores before this lane's release, which makes them visible before the counter value.
     __syncwarp();
-    if (lane < ns && my_row >= 0) red_release_sys_add(a.peer_tile_flags[my_owner] + (my_row >> 7), 1);
+    const bool sent = lane < ns && my_row >= 0;
+    if (sent) red_release_sys_add(a.peer_tile_flags[my_owner] + (my_row >> 7), 1);
+    if (a.total_index >= 0) {
+      // one add per distinct owner of the chunk to that owner's count of all arrived rows
+      const unsigned same = __match_any_sync(0xffffffffu, sent ? my_owner : -1);
+      if (sent && lane == __ffs(same) - 1) red_release_sys_add(a.peer_tile_flags[my_owner] + a.total_index, __popc(same));
+    }
   }
 }
 

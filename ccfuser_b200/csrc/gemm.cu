@@ -56,6 +56,8 @@ struct __align__(16) Ctrl {
   int abort_word;
   int total_tiles;
   int n_tiles;
+  int total_rows;   // valid rows over all groups (row-grouped mode)
+  int pad;
   int sched_tile[kSchedSlots];
   int mt_prefix[CCF_MAX_GROUPS + 1];
 };
@@ -111,32 +113,36 @@ __device__ __forceinline__ Tile decode_tile(int t, const CcfGemmArgs& a, const C
 // ---------------------------------------------------------------------------------------------------
 // epilogue math
 // ---------------------------------------------------------------------------------------------------
-// erf by Abramowitz-Stegun 7.1.26 (|error| <= 1.5e-7, far below bf16/fp16 resolution): two MUFU ops and
-// a degree-5 polynomial instead of libm's branchy erff, which made the epilogue the bottleneck at small K.
-// e2 = exp(-x*x) is passed in so the derivative can share the exponential.
+// erf as an odd polynomial: erf(z) ~= z * P(z^2) on |z| <= 3 (degree 8 in z^2, fitted minimax-style; |error| <= 2.6e-5
+// in fp32 Horner form, erf(3) = 1 - 2.2e-5 beyond the clamp), far below bf16 / fp16 resolution. No MUFU operation and
+// no branch: libm's erff and the exp/rcp-based forms kept the SFU pipe busy for ~4 k cycles per 128x256 tile.
+__device__ __forceinline__ float erf_poly(float z) {
+  z = fminf(fmaxf(z, -3.f), 3.f);
+  const float u = z * z;
+  float p = 4.074189994e-08f;
+  p = fmaf(p, u, -1.944814854e-06f);
+  p = fmaf(p, u, 4.106040073e-05f);
+  p = fmaf(p, u, -5.110358431e-04f);
+  p = fmaf(p, u, 4.235422620e-03f);
+  p = fmaf(p, u, -2.510284860e-02f);
+  p = fmaf(p, u, 1.110793178e-01f);
+  p = fmaf(p, u, -3.753148649e-01f);
+  p = fmaf(p, u, 1.128268424e+00f);
+  return p * z;
+}
 __device__ __forceinline__ float fast_rcp(float x) {
   float y;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // branch-free, 1 ulp: keeps the element loops interleavable
   return y;
 }
-__device__ __forceinline__ float erf_from_exp(float ax, float e2) {
-  const float t = fast_rcp(fmaf(0.3275911f, ax, 1.f));
-  float p = fmaf(1.061405429f, t, -1.453152027f);
-  p = fmaf(p, t, 1.421413741f);
-  p = fmaf(p, t, -0.284496736f);
-  p = fmaf(p, t, 0.254829592f);
-  return 1.f - p * t * e2;
-}
 __device__ __forceinline__ float gelu_f(float x) {
-  const float z = fabsf(x) * 0.70710678118654752f;
-  const float e = erf_from_exp(z, __expf(-z * z));
-  return 0.5f * x * (1.f + copysignf(e, x));
+  const float hx = 0.5f * x;
+  return fmaf(hx, erf_poly(x * 0.70710678118654752f), hx);
 }
 __device__ __forceinline__ float gelu_grad_f(float x) {
-  const float z = fabsf(x) * 0.70710678118654752f;
-  const float e2 = __expf(-z * z);  // exp(-x^2 / 2)
-  const float cdf = 0.5f * (1.f + copysignf(erf_from_exp(z, e2), x));
-  return fmaf(x * 0.3989422804014327f, e2, cdf);
+  const float cdf = fmaf(0.5f, erf_poly(x * 0.70710678118654752f), 0.5f);
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return fmaf(x, pdf, cdf);
 }
 // The activation switch sits outside the element loop: with a branch per element the compiler cannot
 // interleave the 32 independent dependency chains and the epilogue ran ~200 clocks per element.
@@ -193,6 +199,26 @@ __device__ __forceinline__ void store32_f32(float* p, const float (&f)[32]) {
   float4* q = reinterpret_cast<float4*>(p);
 #pragma unroll
   for (int i = 0; i < 8; ++i) q[i] = make_float4(f[i * 4], f[i * 4 + 1], f[i * 4 + 2], f[i * 4 + 3]);
+}
+
+// 32 bias values as raw 16-byte words (same address for every lane: a broadcast load), applied later so that the
+// load latency of chunk c+1 hides behind the math of chunk c
+__device__ __forceinline__ void load_bias_raw(const void* bias, size_t elem_off, uint4 (&raw)[4]) {
+  const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(bias) + elem_off);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) raw[i] = __ldg(q + i);
+}
+__device__ __forceinline__ void add_bias_raw(float (&f)[32], const uint4 (&raw)[4], int fp16) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = unpack2(w[j], fp16);
+      f[i * 8 + j * 2] += t.x;
+      f[i * 8 + j * 2 + 1] += t.y;
+    }
+  }
 }
 
 __device__ __forceinline__ void acc_to_float(const uint32_t (&r)[32], float (&f)[32]) {
@@ -325,6 +351,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       }
       ctrl->mt_prefix[args.num_groups] = acc;
       ctrl->total_tiles = acc * nt;
+      int rows = 0;
+      for (int g = 0; g < args.num_groups; ++g) rows += args.group_rows[g];
+      ctrl->total_rows = rows;
     } else {
       ctrl->total_tiles = args.num_groups * (args.m_per_group / BM) * nt;
     }
@@ -348,10 +377,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   const int total_tiles = ctrl->total_tiles;
 
   // ---- dispatch role (fused all-to-all dispatch) -----------------------------------------------------
+  // (trace: the last recorded tile slot of every CTA holds {0: kernel start, 1: dispatch role finished})
+  if (threadIdx.x == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 0);
   if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) {
-    dispatch_rows<8>(args.disp, args.status);
+    dispatch_rows<8>(args.disp, args.status, static_cast<int>(blockIdx.x),
+                     min(args.n_comm_ctas, static_cast<int>(gridDim.x)));
     __syncthreads();
   }
+  if (threadIdx.x == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
 
   if (warp == 0) {
     // ======================= tile scheduler + TMA producer =======================
@@ -360,6 +393,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     // The index of the next tile is requested one tile ahead, so the latency of the global atomic is
     // hidden behind the loads of the current tile (lane 0 holds it until the next iteration).
     int t_next = 0, seq = 0;
+    bool all_in = false;  // every row of this rank has arrived: no further flag reads
     if (lane == 0) t_next = atomicAdd(args.sched, 1);
     while (ok) {
       if (!mbar_wait(smem_u32(&ctrl->sched_empty[ss]), sphase ^ 1, abort_word, limit)) {
@@ -378,16 +412,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       const Tile ti = decode_tile<kKGroup, kEpi>(t, args, ctrl);
       if (lane == 0) trace_ev(args, seq, 0);
       if constexpr (!kKGroup) {
-        if (args.tile_flags != nullptr) {
-          // rows of this tile are pushed by other GPUs; wait until all of them have landed
-          bool arrived = true;
-          if (lane == 0) arrived = wait_flag_ge(args.tile_flags + (ti.row0 >> 7), ti.rows_valid, limit);
-          arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
-          if (!arrived) {
+        if (args.tile_flags != nullptr && !all_in) {
+          // rows of this tile are pushed by other GPUs; wait until all of them have landed. The count of all
+          // arrived rows is read alongside: once it is complete, later tiles skip the flag read and its latency.
+          int state = 1;
+          if (lane == 0) {
+            int total = 0;
+            if (args.total_index >= 0) total = ld_acquire_sys(args.tile_flags + args.total_index);
+            if (!wait_flag_ge(args.tile_flags + (ti.row0 >> 7), ti.rows_valid, limit)) state = 0;
+            else if (args.total_index >= 0 && total >= ctrl->total_rows) state = 2;
+          }
+          state = __shfl_sync(0xffffffffu, state, 0);
+          if (state == 0) {
             report_status(args.status, CCF_ERR_FLAG_TIMEOUT, ti.row0 >> 7);
             *abort_word = 1;
             break;
           }
+          all_in = state == 2;
           fence_proxy_async();  // generic-proxy peer stores -> async-proxy (TMA) reads
         }
       }
@@ -546,21 +587,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       constexpr int n_chunks = (kEpi == CCF_EPI_SWIGLU) ? 2 : 4;
       const int chunk0 = half * n_chunks;
       const uint32_t stage = smem_base + kStages * kStageBytes + (warp - 2) * kEpiStageBytes;
-      uint32_t racc[2][32];
-      if (have_acc) tmem_ld32(t_row + chunk0 * 32, racc[0]);
-#pragma unroll
+      uint32_t racc[32];  // one buffer: the next chunk is requested right after this one is copied out to f[]
+      if (have_acc) tmem_ld32(t_row + chunk0 * 32, racc);
+      constexpr bool kBias0Prefetch = (kEpi == CCF_EPI_STORE || kEpi == CCF_EPI_BIAS_ACT || kEpi == CCF_EPI_COMBINE);
+      uint4 bcur[4], bnext[4];
+      const bool has_b0 = kBias0Prefetch && args.bias0 != nullptr;
+      if (has_b0 && ti.n0 + chunk0 * 32 < args.n)
+        load_bias_raw(args.bias0, static_cast<size_t>(ti.g) * args.n + ti.n0 + chunk0 * 32, bnext);
+      // not unrolled: the body is large and every launch pays for fetching the kernel's code once per SM
+#pragma unroll 1
       for (int c = 0; c < n_chunks; ++c) {
         const int cg = chunk0 + c;
         const int n = ti.n0 + cg * 32;
         float f[32];
         uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) bcur[i] = bnext[i];
+        if (has_b0 && c + 1 < n_chunks && n + 32 < args.n)
+          load_bias_raw(args.bias0, static_cast<size_t>(ti.g) * args.n + n + 32, bnext);
         if (have_acc) {
           tmem_ld_wait();
-          if constexpr (kEpi != CCF_EPI_SWIGLU && kEpi != CCF_EPI_DSWIGLU) {
+          acc_to_float(racc, f);
+          if constexpr (kEpi != CCF_EPI_SWIGLU) {
             // next chunk's TMEM load overlaps this chunk's math and stores
-            if (c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc[(c + 1) & 1]);
+            if (c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc);
           }
-          acc_to_float(racc[c & 1], f);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) f[i] = 0.f;
@@ -569,10 +620,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
           // f = gate pre-activation (accumulator columns cg*32..), u = up pre-activation (+128)
           float u[32];
           if (have_acc) {
-            tmem_ld32(t_row + 128 + cg * 32, racc[(c + 1) & 1]);
+            tmem_ld32(t_row + 128 + cg * 32, racc);
             tmem_ld_wait();
-            acc_to_float(racc[(c + 1) & 1], u);
-            if (c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc[(c + 1) & 1]);
+            acc_to_float(racc, u);
+            if (c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) u[i] = 0.f;
@@ -612,12 +663,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
           }
         } else if (n < args.n) {  // column edge: chunks beyond the matrix are skipped
           if constexpr (kEpi == CCF_EPI_STORE) {
-            if (args.bias0) {
-              float b[32];
-              load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) f[i] += b[i];
-            }
+            if (has_b0) add_bias_raw(f, bcur, fp16);
             if (args.out_fp32) {
               if (valid) store32_f32(reinterpret_cast<float*>(args.out0) + orow * args.ld_out + n, f);
             } else {
@@ -625,12 +671,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
               staged_store64(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);
             }
           } else if constexpr (kEpi == CCF_EPI_BIAS_ACT) {
-            if (args.bias0) {
-              float b[32];
-              load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) f[i] += b[i];
-            }
+            if (has_b0) add_bias_raw(f, bcur, fp16);
             if (!valid) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) f[i] = 0.f;
@@ -643,12 +684,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             pack32(f, w, fp16);
             staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
           } else if constexpr (kEpi == CCF_EPI_COMBINE) {
-            if (args.bias0) {
-              float b[32];
-              load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) f[i] += b[i];
-            }
+            if (has_b0) add_bias_raw(f, bcur, fp16);
 #pragma unroll
             for (int i = 0; i < 32; ++i) f[i] *= c_gate;
             pack32(f, w, fp16);
@@ -682,10 +718,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
             staged_store64(stage, lane, wu, addr2(args.out1, orow, args.ld_out, n));
           }
-        }
-        if constexpr (kEpi == CCF_EPI_DSWIGLU) {
-          // register budget: this epilogue holds several 32-wide arrays, so its TMEM loads are not double-buffered
-          if (have_acc && c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc[(c + 1) & 1]);
         }
       }
       if (warp == 2 && lane == 0) trace_ev(args, seq, 7);

@@ -43,7 +43,7 @@ struct CcfDispatchArgs {
   int* peer_row_src[CCF_MAX_RANKS];    // [R] packed (source rank << 24 | slot)
   float* peer_row_gate[CCF_MAX_RANKS]; // [R]
   int* peer_tile_flags[CCF_MAX_RANKS]; // [R / 128] rows arrived per 128-row tile
-  int* work_counter;        // dynamic chunk counter (zero before launch; the kernel restores zero)
+  int* work_counter;        // unused (chunks are assigned to warps statically); kept for layout stability
   int tokens;
   int top_k;
   int d;                    // row length in elements (multiple of 8)
@@ -53,7 +53,7 @@ struct CcfDispatchArgs {
   int backward;             // 1: rows are scaled by the gate weight and dgate is produced
   int fp16;                 // 1: fp16 rows, 0: bf16 rows
   int max_rows;             // rows of a receive buffer (bounds check)
-  int pad0;
+  int total_index;          // element of peer_tile_flags[] that counts all rows arrived on that rank (-1 = none)
 };
 
 struct CcfGemmArgs {
@@ -92,5 +92,7 @@ struct CcfGemmArgs {
   int n_comm_ctas;          // CTAs that run the dispatch role before taking GEMM tiles (0 = none)
   int max_slots;            // COMBINE: rows of a combine buffer (bounds check)
   int trace_tiles;          // tiles per CTA recorded in `trace`
+  int total_index;          // element of tile_flags that counts all arrived rows (-1 = none); lets late tiles skip their flag
+  int pad1;
   CcfDispatchArgs disp;
 };

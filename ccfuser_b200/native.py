@@ -34,7 +34,7 @@ class DispatchArgs(C.Structure):
         ("work_counter", _vp),
         ("tokens", C.c_int), ("top_k", C.c_int), ("d", C.c_int), ("capacity", C.c_int),
         ("experts_per_rank", C.c_int), ("my_rank", C.c_int), ("backward", C.c_int), ("fp16", C.c_int),
-        ("max_rows", C.c_int), ("pad0", C.c_int),
+        ("max_rows", C.c_int), ("total_index", C.c_int),
     ]
 
 
@@ -49,6 +49,7 @@ class GemmArgs(C.Structure):
         ("n", C.c_int), ("k", C.c_int), ("num_groups", C.c_int), ("m_per_group", C.c_int), ("kseg", C.c_int),
         ("b_group_rows", C.c_int), ("act", C.c_int), ("fp16", C.c_int), ("out_fp32", C.c_int), ("world", C.c_int),
         ("send_finish", C.c_int), ("n_comm_ctas", C.c_int), ("max_slots", C.c_int), ("trace_tiles", C.c_int),
+        ("total_index", C.c_int), ("pad1", C.c_int),
         ("disp", DispatchArgs),
     ]
 

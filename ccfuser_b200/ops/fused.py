@@ -88,7 +88,9 @@ class CommContext:
         self.block_off = torch.zeros(nb * e_total, dtype=torch.int32, device=device)
         self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
         self.wait_ns = int(float(os.environ.get("CCFUSER_WAIT_LIMIT_S", "5")) * 1e9)
-        self.n_comm = env_flag("COMM_CTAS", 24)
+        # CTAs that run the dispatch role before taking GEMM tiles. Rows are pushed in token order, so tiles only
+        # complete towards the end of the dispatch; with every CTA helping, that phase is as short as the links allow.
+        self.n_comm = env_flag("COMM_CTAS", 1 << 20)
 
     @classmethod
     def get(cls, group, world, rank, device, max_rows, max_slots, d_model, e_total, dtype) -> "CommContext":
@@ -242,6 +244,7 @@ class FusedMoE:
         a.capacity = cfg.capacity(tokens)
         a.experts_per_rank, a.my_rank = cfg.experts_per_rank, self.rank
         a.backward, a.fp16, a.max_rows = int(backward), int(cfg.dtype == torch.float16), self.max_rows
+        a.total_index = self.max_rows // TILE  # last element of tile_flags: all rows arrived on that rank
         return a
 
     def _combine_kw(self, peer_comb, row_gate):
@@ -290,7 +293,8 @@ class FusedMoE:
         f, e_loc = cfg.d_ffn, cfg.experts_per_rank
         disp = self._dispatch_args(x, t, idx, gate_w, None, backward=False)
         common = dict(group_base=self.group_base, group_rows=self.group_rows, num_groups=e_loc, tile_flags=cc.tile_flags,
-                      dispatch=disp, n_comm_ctas=cc.n_comm, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace)
+                      dispatch=disp, n_comm_ctas=cc.n_comm, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace,
+                      total_index=self.max_rows // TILE)
         if cfg.activation == "swiglu":
             G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), b1=wg.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K,
                      epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre, out2=self.h_pre2,
@@ -358,11 +362,11 @@ class _FusedMoEFn(torch.autograd.Function):
         if swiglu:
             G.launch(a0=cc.grecv, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DSWIGLU, n=f, k=d,
                      b_group_rows=d, out0=dh, out1=dh2, aux0=fm.h_pre, aux1=fm.h_pre2, tile_flags=cc.tile_flags,
-                     dispatch=disp, n_comm_ctas=cc.n_comm, **common)
+                     dispatch=disp, n_comm_ctas=cc.n_comm, total_index=fm.max_rows // TILE, **common)
         else:
             G.launch(a0=cc.grecv, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DACT, n=f, k=d,
                      b_group_rows=d, out0=dh, aux0=fm.h_pre, act=N.ACT_CODE[cfg.activation], tile_flags=cc.tile_flags,
-                     dispatch=disp, n_comm_ctas=cc.n_comm, **common)
+                     dispatch=disp, n_comm_ctas=cc.n_comm, total_index=fm.max_rows // TILE, **common)
         cc.tile_flags.zero_()
         # 3. wgrad-2: dW2[e] = (g dy)^T h_act   [d, f]
         dw2 = torch.empty_like(w2)

@@ -70,7 +70,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
            out0=None, out1=None, out2=None, bias0=None, bias1=None, aux0=None, aux1=None, ld_out=None,
            act=N.ACT_NONE, out_fp32=False, tile_flags=None, row_src=None, row_gate=None,
            peer_comb=None, peer_done=None, world=1, send_finish=0, max_slots=0,
-           dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
+           dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, total_index=-1, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
            workspace: Optional[Workspace] = None):
     """Fill a CcfGemmLaunch and launch on the current stream. a0/b0 are 2-D contiguous views."""
     lib = N.load()
@@ -98,6 +98,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     g.n, g.k, g.num_groups, g.m_per_group, g.kseg = int(n), int(k), int(num_groups), int(m_per_group), int(kseg)
     g.b_group_rows, g.act, g.fp16, g.out_fp32 = int(b_group_rows), int(act), _is_fp16(a0), int(bool(out_fp32))
     g.world, g.send_finish, g.n_comm_ctas, g.max_slots = int(world), int(send_finish), int(n_comm_ctas), int(max_slots)
+    g.total_index = int(total_index)
     if dispatch is not None:
         g.disp = dispatch
         g.disp.work_counter = ws.sched.data_ptr() + 8

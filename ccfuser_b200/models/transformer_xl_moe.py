@@ -51,9 +51,10 @@ class TransformerXLMoEConfig:
 
 
 class PositionalEmbedding(nn.Module):
-    def __init__(self, d):
+    def __init__(self, d, device=None):
         super().__init__()
-        self.register_buffer("inv_freq", 1.0 / (10000 ** (torch.arange(0.0, d, 2.0) / d)), persistent=False)
+        self.register_buffer("inv_freq", 1.0 / (10000 ** (torch.arange(0.0, d, 2.0, device=device) / d)),
+                             persistent=False)
 
     def forward(self, pos_seq):
         s = torch.outer(pos_seq, self.inv_freq.to(pos_seq.device))
@@ -130,7 +131,7 @@ class TransformerXLMoE(nn.Module):
         super().__init__()
         self.config = c
         self.word_emb = nn.Embedding(c.n_token, c.d_model, device=device, dtype=c.dtype)
-        self.pos_emb = PositionalEmbedding(c.d_model)
+        self.pos_emb = PositionalEmbedding(c.d_model, device)
         self.r_w_bias = nn.Parameter(torch.zeros(c.n_head, c.d_head, device=device, dtype=c.dtype))
         self.r_r_bias = nn.Parameter(torch.zeros(c.n_head, c.d_head, device=device, dtype=c.dtype))
         self.layers = nn.ModuleList([DecoderLayer(c, ep_group, device) for _ in range(c.n_layer)])

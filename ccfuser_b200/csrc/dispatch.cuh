@@ -158,12 +158,21 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status, int cta, in
     // The counters move with release semantics at system scope after a warp barrier: the barrier orders the other
     // lanes' row stores before this lane's release, which makes them visible before the counter value.
     __syncwarp();
+    // Rows that stay on this GPU only need device scope (the consumer is a CTA of this GPU); a system-scope
+    // release costs several microseconds more per chunk.
     const bool sent = lane < ns && my_row >= 0;
-    if (sent) red_release_sys_add(a.peer_tile_flags[my_owner] + (my_row >> 7), 1);
+    const bool all_local = __all_sync(0xffffffffu, !sent || my_owner == a.my_rank);
+    if (sent) {
+      int* flag = a.peer_tile_flags[my_owner] + (my_row >> 7);
+      if (all_local) red_release_gpu_add(flag, 1); else red_release_sys_add(flag, 1);
+    }
     if (a.total_index >= 0) {
       // one add per distinct owner of the chunk to that owner's count of all arrived rows
       const unsigned same = __match_any_sync(0xffffffffu, sent ? my_owner : -1);
-      if (sent && lane == __ffs(same) - 1) red_release_sys_add(a.peer_tile_flags[my_owner] + a.total_index, __popc(same));
+      if (sent && lane == __ffs(same) - 1) {
+        int* tot = a.peer_tile_flags[my_owner] + a.total_index;
+        if (all_local) red_release_gpu_add(tot, __popc(same)); else red_release_sys_add(tot, __popc(same));
+      }
     }
   }
 }

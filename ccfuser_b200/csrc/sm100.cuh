@@ -191,6 +191,9 @@ __host__ __device__ __forceinline__ uint32_t make_idesc(int m, int n, int fp16_i
 __device__ __forceinline__ void red_release_sys_add(int* addr, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_release_gpu_add(int* addr, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void st_release_sys(int* addr, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }

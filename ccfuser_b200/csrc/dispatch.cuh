@@ -51,18 +51,24 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fp16) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// One warp works on chunks of kChunk consecutive slots. Chunks are assigned statically
-// (chunk = warp index within the dispatching CTAs + k * number of such warps): every CTA that runs the role takes
-// part from the start, so a shared work counter would only add an atomic round trip per chunk.
+// One warp works on chunks of kChunk consecutive slots claimed from a shared counter. Claiming is dynamic on
+// purpose: only CTAs that are resident push rows. With a static assignment a CTA that cannot start yet (its SM is
+// held by another kernel, e.g. a collective of the data-parallel all-reduce that itself waits for a peer) would
+// hold back rows that other GPUs wait for. The next claim is issued before the current chunk is processed so the
+// atomic's round trip is off the critical path.
 template <int kChunk>
-__device__ void dispatch_rows(const CcfDispatchArgs& a, int* status, int cta, int n_ctas) {
+__device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
   static_assert(kChunk <= 16, "one lane per slot of a chunk; rows of a chunk are held in registers");
   const int S = a.tokens * a.top_k;
   const int lane = threadIdx.x & 31;
   const int vecs = a.d >> 3;  // 16-byte vectors per row
-  const int warps_per_cta = blockDim.x >> 5;
   const int n_chunks = (S + kChunk - 1) / kChunk;
-  for (int c = cta * warps_per_cta + (threadIdx.x >> 5); c < n_chunks; c += n_ctas * warps_per_cta) {
+  int c_next = 0;
+  if (lane == 0) c_next = atomicAdd(a.work_counter, 1);
+  for (;;) {
+    const int c = __shfl_sync(0xffffffffu, c_next, 0);
+    if (c >= n_chunks) break;
+    if (lane == 0) c_next = atomicAdd(a.work_counter, 1);
     const int s0 = c * kChunk;
     const int ns = min(kChunk, S - s0);
     // lane i plans slot s0 + i

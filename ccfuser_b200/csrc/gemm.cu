@@ -28,22 +28,15 @@
 #include <cuda_runtime.h>
 #include <stdio.h>
 
-#include "dispatch.cuh"
-#include "gemm_args.h"
-#include "sm100.cuh"
+#include "gemm_common.cuh"
 
 namespace ccf {
 
-constexpr int BM = 128, BN = 256, BK = 64, UK = 16;
 constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kSchedSlots = 4;
-constexpr int kEpiWarps = 8;            // two per TMEM lane quarter, each takes half of the columns
-constexpr int kThreads = 64 + 32 * kEpiWarps;
-constexpr int kTmemCols = 512;
-constexpr int MAJ_K = 0, MAJ_MN = 1;
 
 struct __align__(16) Ctrl {
   uint64_t full[kStages];
@@ -62,17 +55,7 @@ struct __align__(16) Ctrl {
   int mt_prefix[CCF_MAX_GROUPS + 1];
 };
 
-constexpr int kEpiStageBytes = 2048;  // per epilogue warp: 32 rows x 64 bytes, XOR-swizzled
 constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiWarps * kEpiStageBytes + static_cast<int>(sizeof(Ctrl));
-
-struct Tile {
-  int g;           // group (expert)
-  int row0;        // row-grouped: first A/C row; k-grouped: first output row inside the group (m0)
-  int n0;          // first output column (for SWIGLU: first *output* column, 128 per tile)
-  int rows_valid;  // valid rows of the tile
-  int kblocks;     // 64-deep reduction steps
-  int krow0;       // k-grouped: first reduction row
-};
 
 template <bool kKGroup, int kEpi>
 __device__ __forceinline__ Tile decode_tile(int t, const CcfGemmArgs& a, const Ctrl* c) {
@@ -108,204 +91,6 @@ __device__ __forceinline__ Tile decode_tile(int t, const CcfGemmArgs& a, const C
     ti.krow0 = a.group_base[ti.g];
   }
   return ti;
-}
-
-// ---------------------------------------------------------------------------------------------------
-// epilogue math
-// ---------------------------------------------------------------------------------------------------
-// erf as an odd polynomial: erf(z) ~= z * P(z^2) on |z| <= 3 (degree 8 in z^2, fitted minimax-style; |error| <= 2.6e-5
-// in fp32 Horner form, erf(3) = 1 - 2.2e-5 beyond the clamp), far below bf16 / fp16 resolution. No MUFU operation and
-// no branch: libm's erff and the exp/rcp-based forms kept the SFU pipe busy for ~4 k cycles per 128x256 tile.
-__device__ __forceinline__ float erf_poly(float z) {
-  z = fminf(fmaxf(z, -3.f), 3.f);
-  const float u = z * z;
-  float p = 4.074189994e-08f;
-  p = fmaf(p, u, -1.944814854e-06f);
-  p = fmaf(p, u, 4.106040073e-05f);
-  p = fmaf(p, u, -5.110358431e-04f);
-  p = fmaf(p, u, 4.235422620e-03f);
-  p = fmaf(p, u, -2.510284860e-02f);
-  p = fmaf(p, u, 1.110793178e-01f);
-  p = fmaf(p, u, -3.753148649e-01f);
-  p = fmaf(p, u, 1.128268424e+00f);
-  return p * z;
-}
-__device__ __forceinline__ float fast_rcp(float x) {
-  float y;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // branch-free, 1 ulp: keeps the element loops interleavable
-  return y;
-}
-__device__ __forceinline__ float gelu_f(float x) {
-  const float hx = 0.5f * x;
-  return fmaf(hx, erf_poly(x * 0.70710678118654752f), hx);
-}
-__device__ __forceinline__ float gelu_grad_f(float x) {
-  const float cdf = fmaf(0.5f, erf_poly(x * 0.70710678118654752f), 0.5f);
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return fmaf(x, pdf, cdf);
-}
-// The activation switch sits outside the element loop: with a branch per element the compiler cannot
-// interleave the 32 independent dependency chains and the epilogue ran ~200 clocks per element.
-__device__ __forceinline__ void act32(float (&f)[32], int act) {
-  if (act == CCF_ACT_GELU) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) f[i] = gelu_f(f[i]);
-  } else if (act == CCF_ACT_RELU) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) f[i] = fmaxf(f[i], 0.f);
-  }
-}
-// f[i] *= act'(pz[i])
-__device__ __forceinline__ void act_grad32(float (&f)[32], const float (&pz)[32], int act) {
-  if (act == CCF_ACT_GELU) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) f[i] *= gelu_grad_f(pz[i]);
-  } else if (act == CCF_ACT_RELU) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) f[i] = pz[i] > 0.f ? f[i] : 0.f;
-  }
-}
-
-// 32 consecutive 2-byte elements -> floats (64 bytes, 16-byte aligned)
-__device__ __forceinline__ void load32(const void* p, float (&f)[32], int fp16) {
-  const uint4* q = reinterpret_cast<const uint4*>(p);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint4 v = __ldg(q + i);
-    uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 t = unpack2(w[j], fp16);
-      f[i * 8 + j * 2] = t.x;
-      f[i * 8 + j * 2 + 1] = t.y;
-    }
-  }
-}
-
-__device__ __forceinline__ void store32(void* p, const float (&f)[32], int fp16) {
-  uint4* q = reinterpret_cast<uint4*>(p);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint4 v;
-    v.x = pack2(f[i * 8 + 0], f[i * 8 + 1], fp16);
-    v.y = pack2(f[i * 8 + 2], f[i * 8 + 3], fp16);
-    v.z = pack2(f[i * 8 + 4], f[i * 8 + 5], fp16);
-    v.w = pack2(f[i * 8 + 6], f[i * 8 + 7], fp16);
-    q[i] = v;
-  }
-}
-
-__device__ __forceinline__ void store32_f32(float* p, const float (&f)[32]) {
-  float4* q = reinterpret_cast<float4*>(p);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = make_float4(f[i * 4], f[i * 4 + 1], f[i * 4 + 2], f[i * 4 + 3]);
-}
-
-// 32 bias values as raw 16-byte words (same address for every lane: a broadcast load), applied later so that the
-// load latency of chunk c+1 hides behind the math of chunk c
-__device__ __forceinline__ void load_bias_raw(const void* bias, size_t elem_off, uint4 (&raw)[4]) {
-  const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(bias) + elem_off);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) raw[i] = __ldg(q + i);
-}
-__device__ __forceinline__ void add_bias_raw(float (&f)[32], const uint4 (&raw)[4], int fp16) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 t = unpack2(w[j], fp16);
-      f[i * 8 + j * 2] += t.x;
-      f[i * 8 + j * 2 + 1] += t.y;
-    }
-  }
-}
-
-__device__ __forceinline__ void acc_to_float(const uint32_t (&r)[32], float (&f)[32]) {
-#pragma unroll
-  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
-}
-
-
-// ---------------------------------------------------------------------------------------------------
-// Epilogue row I/O through a per-warp shared-memory staging buffer (32 rows x 64 bytes, XOR-swizzled).
-// In the TMEM register layout every lane owns one row, so a direct vector store writes 16 bytes to 32
-// different rows per instruction: 4096 partial-sector requests per 128x256 tile and output, which capped
-// the tensor pipe at ~46 % for two-output epilogues. Staged, each instruction moves 8 rows x 64 contiguous
-// bytes (full 32-byte sectors). Lane l owns row l; `row_ptr` is the global address of this lane's
-// 64-byte segment (0 = skip the row).
-// ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t stage_off(int row, int piece) {
-  return static_cast<uint32_t>(row * 64 + ((piece ^ ((row >> 1) & 3)) << 4));
-}
-
-__device__ __forceinline__ void staged_store64(uint32_t stage, int lane, const uint32_t (&w)[16],
-                                               unsigned long long row_ptr) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + stage_off(lane, j)), "r"(w[4 * j]),
-                 "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
-                 : "memory");
-  }
-  __syncwarp();
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int row = 8 * i + (lane >> 2), piece = lane & 3;
-    const unsigned long long p = __shfl_sync(0xffffffffu, row_ptr, row);
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "r"(stage + stage_off(row, piece))
-                 : "memory");
-    if (p != 0ull) *reinterpret_cast<uint4*>(p + piece * 16) = v;
-  }
-  __syncwarp();
-}
-
-__device__ __forceinline__ void staged_load64(uint32_t stage, int lane, uint32_t (&w)[16],
-                                              unsigned long long row_ptr) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int row = 8 * i + (lane >> 2), piece = lane & 3;
-    const unsigned long long p = __shfl_sync(0xffffffffu, row_ptr, row);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (p != 0ull) v = __ldg(reinterpret_cast<const uint4*>(p + piece * 16));
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + stage_off(row, piece)), "r"(v.x), "r"(v.y),
-                 "r"(v.z), "r"(v.w)
-                 : "memory");
-  }
-  __syncwarp();
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(w[4 * j]), "=r"(w[4 * j + 1]), "=r"(w[4 * j + 2]), "=r"(w[4 * j + 3])
-                 : "r"(stage + stage_off(lane, j))
-                 : "memory");
-  }
-  __syncwarp();
-}
-
-__device__ __forceinline__ void pack32(const float (&f)[32], uint32_t (&w)[16], int fp16) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] = pack2(f[2 * i], f[2 * i + 1], fp16);
-}
-__device__ __forceinline__ void unpack32(const uint32_t (&w)[16], float (&f)[32], int fp16) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float2 t = unpack2(w[i], fp16);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-// byte address of element (row, col) of a 2-byte matrix with leading dimension ld
-__device__ __forceinline__ unsigned long long addr2(const void* base, long long row, long long ld, int col) {
-  return reinterpret_cast<unsigned long long>(base) + static_cast<unsigned long long>((row * ld + col) * 2);
-}
-
-// Optional per-tile trace: slot `ev` of tile number `seq` of this CTA gets the SM clock (clock64).
-__device__ __forceinline__ void trace_ev(const CcfGemmArgs& a, int seq, int ev) {
-  if (a.trace != nullptr && seq < a.trace_tiles)
-    a.trace[(static_cast<size_t>(blockIdx.x) * a.trace_tiles + seq) * 8 + ev] = clock64();
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -380,8 +165,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   // (trace: the last recorded tile slot of every CTA holds {0: kernel start, 1: dispatch role finished})
   if (threadIdx.x == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 0);
   if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) {
-    dispatch_rows<8>(args.disp, args.status, static_cast<int>(blockIdx.x),
-                     min(args.n_comm_ctas, static_cast<int>(gridDim.x)));
+    dispatch_rows<8>(args.disp, args.status);
     __syncthreads();
   }
   if (threadIdx.x == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
@@ -537,7 +321,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     // ======================= epilogue (warps 2..9) =======================
     const int q = warp & 3;               // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
-    const int fp16 = args.fp16;
     int ss = 0, sphase = 0, as = 0, aphase = 0, seq = -1;
     while (true) {
       ++seq;
@@ -560,166 +343,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         tc_fence_after();
       }
       if (warp == 2 && lane == 0) trace_ev(args, seq, 6);
-      const int r_in_tile = q * 32 + lane;
-      const bool valid = r_in_tile < ti.rows_valid;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * BN;
-      // output row (elements offset)
-      long long orow;
-      if constexpr (kKGroup) orow = static_cast<long long>(ti.g) * args.m_per_group + ti.row0 + r_in_tile;
-      else orow = static_cast<long long>(ti.row0) + r_in_tile;
-
-      // COMBINE: where this row goes
-      int c_rank = 0, c_slot = 0;
-      float c_gate = 1.f;
-      bool c_ok = false;
-      if constexpr (kEpi == CCF_EPI_COMBINE) {
-        if (valid) {
-          const int packed = args.row_src[orow];
-          c_rank = (packed >> 24) & 0xff;
-          c_slot = packed & 0xffffff;
-          c_gate = args.row_gate ? args.row_gate[orow] : 1.f;
-          c_ok = c_rank < args.world && c_slot < args.max_slots;
-          if (!c_ok) report_status(args.status, CCF_ERR_BOUNDS, static_cast<int>(orow) & 0xffffff);
-        }
-      }
-
-      // chunks of 32 accumulator columns; this warp takes n_chunks of them starting at chunk0
-      constexpr int n_chunks = (kEpi == CCF_EPI_SWIGLU) ? 2 : 4;
-      const int chunk0 = half * n_chunks;
       const uint32_t stage = smem_base + kStages * kStageBytes + (warp - 2) * kEpiStageBytes;
-      uint32_t racc[32];  // one buffer: the next chunk is requested right after this one is copied out to f[]
-      if (have_acc) tmem_ld32(t_row + chunk0 * 32, racc);
-      constexpr bool kBias0Prefetch = (kEpi == CCF_EPI_STORE || kEpi == CCF_EPI_BIAS_ACT || kEpi == CCF_EPI_COMBINE);
-      uint4 bcur[4], bnext[4];
-      const bool has_b0 = kBias0Prefetch && args.bias0 != nullptr;
-      if (has_b0 && ti.n0 + chunk0 * 32 < args.n)
-        load_bias_raw(args.bias0, static_cast<size_t>(ti.g) * args.n + ti.n0 + chunk0 * 32, bnext);
-      // not unrolled: the body is large and every launch pays for fetching the kernel's code once per SM
-#pragma unroll 1
-      for (int c = 0; c < n_chunks; ++c) {
-        const int cg = chunk0 + c;
-        const int n = ti.n0 + cg * 32;
-        float f[32];
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) bcur[i] = bnext[i];
-        if (has_b0 && c + 1 < n_chunks && n + 32 < args.n)
-          load_bias_raw(args.bias0, static_cast<size_t>(ti.g) * args.n + n + 32, bnext);
-        if (have_acc) {
-          tmem_ld_wait();
-          acc_to_float(racc, f);
-          if constexpr (kEpi != CCF_EPI_SWIGLU) {
-            // next chunk's TMEM load overlaps this chunk's math and stores
-            if (c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = 0.f;
-        }
-        if constexpr (kEpi == CCF_EPI_SWIGLU) {
-          // f = gate pre-activation (accumulator columns cg*32..), u = up pre-activation (+128)
-          float u[32];
-          if (have_acc) {
-            tmem_ld32(t_row + 128 + cg * 32, racc);
-            tmem_ld_wait();
-            acc_to_float(racc, u);
-            if (c + 1 < n_chunks) tmem_ld32(t_row + (cg + 1) * 32, racc);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) u[i] = 0.f;
-          }
-          if (n < args.n) {
-            if (args.bias1) {
-              float b[32];
-              load32(reinterpret_cast<const uint16_t*>(args.bias1) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) f[i] += b[i];
-            }
-            if (args.bias0) {
-              float b[32];
-              load32(reinterpret_cast<const uint16_t*>(args.bias0) + static_cast<size_t>(ti.g) * args.n + n, b, fp16);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) u[i] += b[i];
-            }
-            if (!valid) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) { f[i] = 0.f; u[i] = 0.f; }
-            }
-            if (args.out1) {
-              pack32(f, w, fp16);
-              staged_store64(stage, lane, w, addr2(args.out1, orow, args.ld_out, n));
-            }
-            if (args.out2) {
-              pack32(u, w, fp16);
-              staged_store64(stage, lane, w, addr2(args.out2, orow, args.ld_out, n));
-            }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float sg = fast_rcp(1.f + __expf(-f[i]));
-              f[i] = f[i] * sg * u[i];
-            }
-            pack32(f, w, fp16);
-            staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
-          }
-        } else if (n < args.n) {  // column edge: chunks beyond the matrix are skipped
-          if constexpr (kEpi == CCF_EPI_STORE) {
-            if (has_b0) add_bias_raw(f, bcur, fp16);
-            if (args.out_fp32) {
-              if (valid) store32_f32(reinterpret_cast<float*>(args.out0) + orow * args.ld_out + n, f);
-            } else {
-              pack32(f, w, fp16);
-              staged_store64(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);
-            }
-          } else if constexpr (kEpi == CCF_EPI_BIAS_ACT) {
-            if (has_b0) add_bias_raw(f, bcur, fp16);
-            if (!valid) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) f[i] = 0.f;
-            }
-            if (args.out1) {
-              pack32(f, w, fp16);
-              staged_store64(stage, lane, w, addr2(args.out1, orow, args.ld_out, n));
-            }
-            act32(f, args.act);  // rows beyond the group hold zeros: act(0) = 0 for every supported activation
-            pack32(f, w, fp16);
-            staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
-          } else if constexpr (kEpi == CCF_EPI_COMBINE) {
-            if (has_b0) add_bias_raw(f, bcur, fp16);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] *= c_gate;
-            pack32(f, w, fp16);
-            // peer stores over NVLink (or local when c_rank is this rank), 64 contiguous bytes per row
-            staged_store64(stage, lane, w, c_ok ? addr2(args.peer_comb[c_rank], c_slot, args.ld_out, n) : 0ull);
-          } else if constexpr (kEpi == CCF_EPI_DACT) {
-            staged_load64(stage, lane, w, valid ? addr2(args.aux0, orow, args.ld_out, n) : 0ull);
-            {
-              float pz[32];
-              unpack32(w, pz, fp16);
-              act_grad32(f, pz, args.act);
-              if (!valid) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) f[i] = 0.f;
-              }
-            }
-            pack32(f, w, fp16);
-            staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
-          } else if constexpr (kEpi == CCF_EPI_DSWIGLU) {
-            uint32_t wu[16];
-            staged_load64(stage, lane, w, valid ? addr2(args.aux0, orow, args.ld_out, n) : 0ull);
-            staged_load64(stage, lane, wu, valid ? addr2(args.aux1, orow, args.ld_out, n) : 0ull);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float2 gp = unpack2(w[j], fp16), up = unpack2(wu[j], fp16);
-              const float a0 = valid ? f[2 * j] : 0.f, a1 = valid ? f[2 * j + 1] : 0.f;
-              const float s0 = fast_rcp(1.f + __expf(-gp.x)), s1 = fast_rcp(1.f + __expf(-gp.y));
-              w[j] = pack2(a0 * up.x * (s0 * (1.f + gp.x * (1.f - s0))), a1 * up.y * (s1 * (1.f + gp.y * (1.f - s1))), fp16);
-              wu[j] = pack2(a0 * gp.x * s0, a1 * gp.y * s1, fp16);
-            }
-            staged_store64(stage, lane, w, addr2(args.out0, orow, args.ld_out, n));
-            staged_store64(stage, lane, wu, addr2(args.out1, orow, args.ld_out, n));
-          }
-        }
-      }
+      long long row_base;
+      if constexpr (kKGroup) row_base = static_cast<long long>(ti.g) * args.m_per_group + ti.row0;
+      else row_base = ti.row0;
+      const CombineDest cd = epilogue_tile<kEpi>(args, ti, row_base, ti.rows_valid, BM, have_acc, t_row, stage, q, half, lane);
       if (warp == 2 && lane == 0) trace_ev(args, seq, 7);
       if (have_acc) {
         // all TMEM reads of this accumulator stage are complete: hand it back to the MMA warp
@@ -728,15 +357,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[as]));
         if (++as == 2) { as = 0; aphase ^= 1; }
       }
-      if constexpr (kEpi == CCF_EPI_COMBINE) {
-        // tell every source rank how many of its rows (for this half column tile) are now in its buffer
-        __threadfence_system();
-        __syncwarp();
-        for (int s = 0; s < args.world; ++s) {
-          const unsigned m = __ballot_sync(0xffffffffu, c_ok && c_rank == s);
-          if (m != 0u && lane == 0) red_release_sys_add(args.peer_done[s], __popc(m));
-        }
-      }
+      if constexpr (kEpi == CCF_EPI_COMBINE) combine_signal(args, cd, lane);
+      (void)cd;
     }
   }
 
@@ -838,6 +460,8 @@ struct CcfGemmLaunch {
   int kgroup;                // 1 = k-grouped (wgrad)
   int grid;                  // 0 = one CTA per SM
   int device;                // CUDA device of the operands; made current for the calling thread (-1 = leave)
+  int two_cta;               // 1 = 256x256 tiles on CTA pairs (tcgen05 cta_group::2), 0 = 128x256 tiles per CTA
+  int pad0;
 };
 
 int ccf_gemm_smem_bytes() { return ccf::kSmemBytes; }
@@ -862,8 +486,10 @@ int ccf_gemm_launch(const CcfGemmLaunch* L, void* stream_v) {
   CUtensorMap tm[4];
   const int fp16 = a.fp16;
   const int a_box_rows = (L->a_major == MAJ_K) ? BM : BK;
+  const bool pair = L->two_cta != 0;
+  if (pair && L->kgroup && (a.m_per_group % (2 * BM) != 0)) return -8;
   int b_box_rows = (L->b_major == MAJ_K) ? BN : BK;
-  if (L->epi == CCF_EPI_SWIGLU) b_box_rows = BN / 2;
+  if (L->epi == CCF_EPI_SWIGLU || (pair && L->b_major == MAJ_K)) b_box_rows = BN / 2;  // a pair member loads half of B
   int rc;
   if ((rc = make_tmap(&tm[0], L->a0, L->a_rows, L->a_cols, 64, a_box_rows, fp16))) return rc;
   if ((rc = make_tmap(&tm[1], L->a1 ? L->a1 : L->a0, L->a_rows, L->a_cols, 64, a_box_rows, fp16))) return rc;
@@ -877,6 +503,7 @@ int ccf_gemm_launch(const CcfGemmLaunch* L, void* stream_v) {
     grid = sms;
   }
   const int key = (L->a_major << 12) | (L->b_major << 8) | (L->epi << 4) | (L->kgroup ? 1 : 0);
+  if (pair) return launch_pair_by_key(key, tm, a, grid, stream);
   switch (key) {
     case (MAJ_K << 12) | (MAJ_K << 8) | (CCF_EPI_STORE << 4):
       return launch_variant<MAJ_K, MAJ_K, CCF_EPI_STORE, false>(tm, a, grid, stream);

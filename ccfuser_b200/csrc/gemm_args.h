@@ -43,7 +43,7 @@ struct CcfDispatchArgs {
   int* peer_row_src[CCF_MAX_RANKS];    // [R] packed (source rank << 24 | slot)
   float* peer_row_gate[CCF_MAX_RANKS]; // [R]
   int* peer_tile_flags[CCF_MAX_RANKS]; // [R / 128] rows arrived per 128-row tile
-  int* work_counter;        // unused (chunks are assigned to warps statically); kept for layout stability
+  int* work_counter;        // chunk claim counter (zero before launch; the kernel's last CTA restores zero)
   int tokens;
   int top_k;
   int d;                    // row length in elements (multiple of 8)

@@ -241,8 +241,16 @@ __global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanA
 // ---------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) dispatch_kernel(const __grid_constant__ CcfDispatchArgs a, int* status,
                                                        int* done_ctas) {
-  (void)done_ctas;
-  dispatch_rows<8>(a, status, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+  dispatch_rows<8>(a, status);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_ctas, 1) == static_cast<int>(gridDim.x) - 1) {
+      *a.work_counter = 0;
+      *done_ctas = 0;
+      __threadfence();
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -60,7 +60,7 @@ class GemmLaunch(C.Structure):
         ("a0", _vp), ("a1", _vp), ("b0", _vp), ("b1", _vp),
         ("a_rows", C.c_longlong), ("a_cols", C.c_longlong), ("b_rows", C.c_longlong), ("b_cols", C.c_longlong),
         ("a_major", C.c_int), ("b_major", C.c_int), ("epi", C.c_int), ("kgroup", C.c_int), ("grid", C.c_int),
-        ("device", C.c_int),
+        ("device", C.c_int), ("two_cta", C.c_int), ("pad0", C.c_int),
     ]
 
 

@@ -55,6 +55,8 @@ class Workspace:
 
 
 DEFAULT_WAIT_NS = 5_000_000_000
+# 256x256 tiles on CTA pairs (tcgen05 cta_group::2) by default; CCFUSER_TWO_CTA=0 selects the one-CTA 128x256 kernel
+TWO_CTA_DEFAULT = bool(int(__import__('os').environ.get('CCFUSER_TWO_CTA', '1')))
 
 
 def _is_fp16(t: torch.Tensor) -> int:
@@ -70,7 +72,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
            out0=None, out1=None, out2=None, bias0=None, bias1=None, aux0=None, aux1=None, ld_out=None,
            act=N.ACT_NONE, out_fp32=False, tile_flags=None, row_src=None, row_gate=None,
            peer_comb=None, peer_done=None, world=1, send_finish=0, max_slots=0,
-           dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, total_index=-1, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
+           dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, total_index=-1, two_cta=None, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
            workspace: Optional[Workspace] = None):
     """Fill a CcfGemmLaunch and launch on the current stream. a0/b0 are 2-D contiguous views."""
     lib = N.load()
@@ -108,6 +110,10 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     L.b_rows, L.b_cols = b0.shape
     L.a_major, L.b_major, L.epi, L.kgroup, L.grid = int(a_major), int(b_major), int(epi), int(bool(kgroup)), int(grid)
     L.device = a0.device.index if a0.device.index is not None else torch.cuda.current_device()
+    if two_cta is None:
+        two_cta = TWO_CTA_DEFAULT
+    # the pair kernel needs 256-row output tiles in k-grouped mode
+    L.two_cta = int(bool(two_cta) and not (kgroup and m_per_group % 256 != 0))
     N.check(lib.ccf_gemm_launch(C.byref(L), N.stream_ptr()), "ccf_gemm_launch")
     N.count(1)
     return ws

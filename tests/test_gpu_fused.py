@@ -121,6 +121,24 @@ def test_fused_layer_forward_backward_one_gpu(act, cf, tokens):
     assert (w.grad.cpu().view(-1)[~plan.keep] == 0).all()
 
 
+def test_fused_layer_fp16_forward_only_one_expert_per_rank():
+    """fp16, a single local expert, SwiGLU without biases, forward only (the small-message serving shape)."""
+    from ccfuser_b200.ops.fused import topk_softmax, _FusedMoEFn
+    for tokens in (128, 500):
+        cfg, layer = _make_layer("swiglu", None, e=1, d=256, f=512, tokens=512, k=1, dtype=torch.float16, bias=False)
+        fm = layer._fused_impl()
+        x = (torch.randn(tokens, 256, device="cuda") * 0.5).half()
+        with torch.no_grad():
+            idx, w = topk_softmax(layer.gate.logits(x), 1)
+            ex = layer.experts
+            y = _FusedMoEFn.apply(x, w, idx, ex.htoh4.weight, None, ex.htoh4_gate.weight, None, ex.h4toh.weight, None, fm)
+        torch.cuda.synchronize()
+        fm.ctx.check_status("fp16 forward")
+        yr, *_ = _oracle_with_routing(cfg, layer, x, idx, w)
+        assert _rel(y, yr.detach()) < 2e-2
+        layer.release()
+
+
 def test_fused_layer_module_api_trains():
     """Through MoELayer.forward (router included): loss goes down over a few SGD steps, twice the same result."""
     cfg, layer = _make_layer("gelu", 1.25, e=16, d=256, f=512, tokens=2048)

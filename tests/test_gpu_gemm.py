@@ -209,6 +209,38 @@ def test_combine_epilogue_local_rank():
         _close(comb[row_src[s:s + r].long()], ref)
 
 
+@pytest.mark.parametrize("two_cta", [False, True])
+def test_one_cta_and_two_cta_kernels_agree(two_cta):
+    """Both tile shapes (128x256 per CTA, 256x256 per CTA pair) against the fp32 reference on ragged groups."""
+    N, G = _mods()
+    torch.manual_seed(6)
+    rows = [257, 128, 0, 1, 600, 129]
+    e, k, n = len(rows), 512, 768
+    gb, gr, total = _groups(rows, "cuda")
+    x = torch.randn(total + 256, k, device="cuda", dtype=torch.bfloat16)   # rows past the last group exist
+    w = torch.randn(e, n, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    b = torch.randn(e, n, device="cuda", dtype=torch.bfloat16) * 0.1
+    out = torch.full((total + 256, n), 5.0, device="cuda", dtype=torch.bfloat16)
+    G.launch(a0=x, b0=w.view(e * n, k), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT, n=n, k=k,
+             group_base=gb, group_rows=gr, num_groups=e, b_group_rows=n, out0=out, bias0=b, act=N.ACT_GELU,
+             two_cta=two_cta)
+    torch.cuda.synchronize()
+    G.Workspace.get(x.device).check("bias_act")
+    for i, r in enumerate(rows):
+        s = int(gb[i])
+        if r:
+            _close(out[s:s + r], F.gelu(F.linear(x[s:s + r].float(), w[i].float(), b[i].float())))
+        pad = (r + 127) // 128 * 128
+        assert (out[s + r:s + pad] == 0).all()
+    # nothing outside the padded regions of the groups was touched
+    assert (out[total:] == 5.0).all()
+    used = torch.zeros(total + 256, dtype=torch.bool, device="cuda")
+    for i, r in enumerate(rows):
+        s = int(gb[i])
+        used[s:s + (r + 127) // 128 * 128] = True
+    assert (out[~used] == 5.0).all()
+
+
 def test_scheduler_counters_return_to_zero():
     N, G = _mods()
     x = torch.randn(512, 128, device="cuda", dtype=torch.bfloat16)

@@ -332,6 +332,43 @@ __global__ void __launch_bounds__(256) colsum_grouped_kernel(const void* x, long
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// SGD step on 2-byte parameters: p -= lr * (g + wd * p), 16-byte vectors, fp32 arithmetic. With 64 experts per GPU
+// the optimizer streams ~150 GB per step; one pass with full-width accesses keeps it at the HBM rate.
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) sgd_step_kernel(void* p, const void* g, long long n, float lr, float wd, int fp16) {
+  const long long nvec = n >> 3;
+  uint4* pv = reinterpret_cast<uint4*>(p);
+  const uint4* gv = reinterpret_cast<const uint4*>(g);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 a = pv[i];
+    const uint4 b = __ldg(gv + i);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 pf = unpack2(aw[q], fp16), gf = unpack2(bw[q], fp16);
+      o[q] = pack2(pf.x - lr * (gf.x + wd * pf.x), pf.y - lr * (gf.y + wd * pf.y), fp16);
+    }
+    pv[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  // tail (n not a multiple of 8)
+  const long long tail0 = nvec << 3;
+  const long long t = tail0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t < n) {
+    if (fp16) {
+      __half* ph = reinterpret_cast<__half*>(p);
+      const float pf = __half2float(ph[t]), gf = __half2float(reinterpret_cast<const __half*>(g)[t]);
+      ph[t] = __float2half(pf - lr * (gf + wd * pf));
+    } else {
+      __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(p);
+      const float pf = __bfloat162float(pb[t]), gf = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g)[t]);
+      pb[t] = __float2bfloat16(pf - lr * (gf + wd * pf));
+    }
+  }
+}
+
 // A wait that nothing satisfies unless `flag` already holds `target`: used to exercise the timeout path.
 __global__ void wait_probe_kernel(const int* flag, int target, unsigned long long limit_ns, int* status) {
   if (!wait_flag_ge(flag, target, limit_ns)) report_status(status, CCF_ERR_FLAG_TIMEOUT, 0x123);
@@ -423,6 +460,16 @@ int ccf_colsum_grouped(const void* x, long long ld, int n, int groups, const int
   dim3 grid((n + 127) / 128, groups);
   ccf::colsum_grouped_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, ld, n, group_base,
                                                                                         group_rows, out, fp16);
+  return last_err();
+}
+
+int ccf_sgd_step(void* p, const void* g, long long n, float lr, float wd, int fp16, void* stream) {
+  if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15) return -2;
+  long long blocks = ((n >> 3) + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  ccf::sgd_step_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p, g, n, lr, wd, fp16);
   return last_err();
 }
 

@@ -131,6 +131,7 @@ def _declare(lib):
         "ccf_combine_reduce": ([p, p, p, i, i, i, i, p], i),
         "ccf_colsum_grouped": ([p, ll, i, i, p, p, p, i, p], i),
         "ccf_wait_probe": ([p, i, ull, p, p], i),
+        "ccf_sgd_step": ([p, p, ll, C.c_float, C.c_float, i, p], i),
         "ccf_symm_alloc": ([ull, C.POINTER(p)], i),
         "ccf_symm_free": ([p], i),
         "ccf_symm_handle_bytes": ([], i),

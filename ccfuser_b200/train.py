@@ -26,7 +26,11 @@ class TrainStep:
         self.model = wrap_ddp(model, dp_group) if self.use_ddp else model
         params = [p for p in model.parameters() if p.requires_grad]
         if optimizer == "sgd":
-            self.opt = torch.optim.SGD(params, lr=lr, foreach=True)
+            if params[0].is_cuda and params[0].dtype in (torch.bfloat16, torch.float16):
+                from .ops.optim import FusedSGD
+                self.opt = FusedSGD(params, lr=lr)
+            else:
+                self.opt = torch.optim.SGD(params, lr=lr, foreach=True)
         elif optimizer == "adamw":
             self.opt = torch.optim.AdamW(params, lr=lr, fused=params[0].is_cuda)
         else:

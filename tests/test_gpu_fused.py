@@ -194,6 +194,20 @@ def test_receive_buffer_overflow_drops_rows_consistently_and_is_reported():
     assert torch.isfinite(y.float()).all()
 
 
+def test_fused_sgd_matches_torch():
+    from ccfuser_b200.ops.optim import FusedSGD
+    torch.manual_seed(0)
+    for dtype, n in [(torch.bfloat16, 1000003), (torch.float16, 4096), (torch.bfloat16, 7)]:
+        p = torch.randn(n, device="cuda").to(dtype)
+        g = torch.randn(n, device="cuda").to(dtype)
+        a = torch.nn.Parameter(p.clone())
+        a.grad = g.clone()
+        FusedSGD([a], lr=0.1, weight_decay=0.01).step()
+        ref = (p.float() - 0.1 * (g.float() + 0.01 * p.float())).to(dtype)
+        # fp32 arithmetic, one rounding to the parameter type (an FMA contraction may move the last bit)
+        assert torch.allclose(a.detach().float(), ref.float(), rtol=8e-3, atol=1e-3)
+
+
 def test_bounded_wait_reports_timeout_without_hanging():
     """A wait on a flag that nothing sets gives up after its limit and records a status; the context stays usable."""
     from ccfuser_b200 import native as N, MoECommTimeout

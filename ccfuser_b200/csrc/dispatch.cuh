@@ -51,41 +51,45 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fp16) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// One warp works on chunks of kChunk consecutive slots claimed from a shared counter. Claiming is dynamic on
-// purpose: only CTAs that are resident push rows. With a static assignment a CTA that cannot start yet (its SM is
-// held by another kernel, e.g. a collective of the data-parallel all-reduce that itself waits for a peer) would
-// hold back rows that other GPUs wait for. The next claim is issued before the current chunk is processed so the
-// atomic's round trip is off the critical path.
+// One warp works on chunks of kChunk consecutive positions of the destination order (rows of this rank's own experts
+// first, then the next owner's, ...; inside an expert in position order), claimed from a shared counter. Consecutive
+// positions land on consecutive rows of one receive buffer, so tiles fill up one after the other: the owner's GEMM can
+// start on its first tiles while later rows are still being pushed, and all sources start with a different owner.
+// Claiming is dynamic on purpose: only warps that are running push rows. With a static assignment a CTA that cannot
+// start yet (its SM is held by another kernel, e.g. a collective of the data-parallel all-reduce that itself waits for
+// a peer) would hold back rows that other GPUs wait for. The next claim is issued before the current chunk is
+// processed so the atomic's round trip is off the critical path.
 template <int kChunk>
 __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
-  static_assert(kChunk <= 16, "one lane per slot of a chunk; rows of a chunk are held in registers");
-  const int S = a.tokens * a.top_k;
+  static_assert(kChunk <= 16, "one lane per row of a chunk; rows of a chunk are held in registers");
+  const int e_total = a.e_total;
+  const int kept = a.order_off[e_total];   // rows to push
   const int lane = threadIdx.x & 31;
   const int vecs = a.d >> 3;  // 16-byte vectors per row
-  const int n_chunks = (S + kChunk - 1) / kChunk;
+  const int n_chunks = (kept + kChunk - 1) / kChunk;
   int c_next = 0;
   if (lane == 0) c_next = atomicAdd(a.work_counter, 1);
   for (;;) {
     const int c = __shfl_sync(0xffffffffu, c_next, 0);
     if (c >= n_chunks) break;
     if (lane == 0) c_next = atomicAdd(a.work_counter, 1);
-    const int s0 = c * kChunk;
-    const int ns = min(kChunk, S - s0);
-    // lane i plans slot s0 + i
-    int my_row = -1, my_owner = 0;
+    const int i0 = c * kChunk;
+    const int ns = min(kChunk, kept - i0);
+    // lane i plans the row at position i0 + i of the destination order
+    int my_row = -1, my_owner = 0, my_slot = 0;
     float my_gate = 0.f;
     if (lane < ns) {
-      const int s = s0 + lane;
+      const int s = a.sorted_slot[i0 + lane];
+      my_slot = s;
       const int e = a.slot_expert[s];
       const int p = a.slot_pos[s];
       my_gate = a.slot_gate[s];
-      if (p < a.capacity) {
-        my_owner = e / a.experts_per_rank;
-        my_row = a.dst_base[e] + p;
-        if (my_row < 0 || my_row >= a.max_rows || my_owner >= CCF_MAX_RANKS) {
-          report_status(status, CCF_ERR_OVERFLOW, s & 0xffffff);
-          my_row = -1;
-        }
+      my_owner = e / a.experts_per_rank;
+      my_row = a.dst_base[e] + p;
+      if (my_row < 0 || my_row >= a.max_rows || my_owner >= CCF_MAX_RANKS || p >= a.capacity) {
+        // beyond the owner's buffer: dropped on both sides (the plan did not count it)
+        if (p < a.capacity) report_status(status, CCF_ERR_OVERFLOW, s & 0xffffff);
+        my_row = -1;
       }
       if (a.slot_row) a.slot_row[s] = my_row;
       if (my_row >= 0) {
@@ -105,7 +109,7 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
       const int row = __shfl_sync(0xffffffffu, my_row, i);
       const int owner = __shfl_sync(0xffffffffu, my_owner, i);
       const bool on = i < ns && row >= 0;
-      const int t = (s0 + i) / a.top_k;
+      const int t = __shfl_sync(0xffffffffu, my_slot, i) / a.top_k;
       src[i] = on ? reinterpret_cast<const uint4*>(a.x) + static_cast<size_t>(t) * vecs : nullptr;
       dst[i] = on ? reinterpret_cast<uint4*>(a.peer_recv[owner]) + static_cast<size_t>(row) * vecs : nullptr;
     }
@@ -122,13 +126,15 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
     } else {
       // rows of the backward pass carry g * dy; the gate gradient is <dy, saved scaled output> / g
       float dot[kChunk], g[kChunk];
+      int slot[kChunk];
       const uint4* sv[kChunk];
 #pragma unroll
       for (int i = 0; i < kChunk; ++i) {
         dot[i] = 0.f;
         g[i] = __shfl_sync(0xffffffffu, my_gate, i);
+        slot[i] = __shfl_sync(0xffffffffu, my_slot, i);
         sv[i] = (src[i] && a.saved_comb)
-                    ? reinterpret_cast<const uint4*>(a.saved_comb) + static_cast<size_t>(s0 + i) * vecs
+                    ? reinterpret_cast<const uint4*>(a.saved_comb) + static_cast<size_t>(slot[i]) * vecs
                     : nullptr;
       }
       for (int v = lane; v < vecs; v += 32) {
@@ -158,7 +164,7 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
       for (int i = 0; i < kChunk; ++i) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], off);
-        if (lane == 0 && dst[i] && a.dgate) a.dgate[s0 + i] = (g[i] != 0.f) ? dot[i] / g[i] : 0.f;
+        if (lane == 0 && dst[i] && a.dgate) a.dgate[slot[i]] = (g[i] != 0.f) ? dot[i] / g[i] : 0.f;
       }
     }
     // The counters move with release semantics at system scope after a warp barrier: the barrier orders the other
@@ -168,9 +174,12 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
     // release costs several microseconds more per chunk.
     const bool sent = lane < ns && my_row >= 0;
     const bool all_local = __all_sync(0xffffffffu, !sent || my_owner == a.my_rank);
-    if (sent) {
+    // rows of a chunk mostly share one tile: one counter update per distinct (owner, tile)
+    const int key = sent ? ((my_owner << 24) | (my_row >> 7)) : -1;
+    const unsigned same_tile = __match_any_sync(0xffffffffu, key);
+    if (sent && lane == __ffs(same_tile) - 1) {
       int* flag = a.peer_tile_flags[my_owner] + (my_row >> 7);
-      if (all_local) red_release_gpu_add(flag, 1); else red_release_sys_add(flag, 1);
+      if (all_local) red_release_gpu_add(flag, __popc(same_tile)); else red_release_sys_add(flag, __popc(same_tile));
     }
     if (a.total_index >= 0) {
       // one add per distinct owner of the chunk to that owner's count of all arrived rows

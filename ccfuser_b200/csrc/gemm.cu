@@ -162,13 +162,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   const int total_tiles = ctrl->total_tiles;
 
   // ---- dispatch role (fused all-to-all dispatch) -----------------------------------------------------
-  // (trace: the last recorded tile slot of every CTA holds {0: kernel start, 1: dispatch role finished})
+  // Run by the epilogue warps before their first accumulator is due (see below); the producer and MMA warps go
+  // straight to the tile loop and start on tiles whose rows have already landed.
+  // (trace: the last recorded tile slot of every CTA holds {0: kernel start, 1: this CTA's dispatch part finished})
   if (threadIdx.x == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 0);
-  if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) {
-    dispatch_rows<8>(args.disp, args.status);
-    __syncthreads();
-  }
-  if (threadIdx.x == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
 
   if (warp == 0) {
     // ======================= tile scheduler + TMA producer =======================
@@ -321,6 +318,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     // ======================= epilogue (warps 2..9) =======================
     const int q = warp & 3;               // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
+    if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8>(args.disp, args.status);
+    if (warp == 2 && lane == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
     int ss = 0, sphase = 0, as = 0, aphase = 0, seq = -1;
     while (true) {
       ++seq;

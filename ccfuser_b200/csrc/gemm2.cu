@@ -33,8 +33,11 @@ struct __align__(16) Ctrl2 {
   int total_tiles;
   int n_tiles;
   int total_rows;
-  int pad;
-  int mt_prefix[CCF_MAX_GROUPS + 1];
+  int tiles_a;                          // pair tiles (x n-tiles) of phase A: made only of rows this rank pushed itself
+  int mt_prefix[CCF_MAX_GROUPS + 1];    // phase B (all other pair tiles), prefix over groups
+  int mta_prefix[CCF_MAX_GROUPS + 1];   // phase A, prefix over groups
+  short a0[CCF_MAX_GROUPS];             // first phase-A pair tile of each group
+  short na[CCF_MAX_GROUPS];             // number of phase-A pair tiles of each group
 };
 
 constexpr int k2SmemBytes = 1024 + k2Stages * k2StageBytes + kEpiWarps * kEpiStageBytes + static_cast<int>(sizeof(Ctrl2));
@@ -136,16 +139,24 @@ __device__ __forceinline__ PairTile decode_pair_tile(int t, const CcfGemmArgs& a
   PairTile ti;
   constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
   if constexpr (!kKGroup) {
+    // Phase A first: the pair tiles that hold only rows pushed by this rank itself (they arrive first, without
+    // crossing NVLink); then phase B, every other pair tile. Inside a phase: group-major, column tile, row tile.
     const int nt = c->n_tiles;
+    const bool phase_a = t < c->tiles_a;
+    const int* pre = phase_a ? c->mta_prefix : c->mt_prefix;
+    const int tt = phase_a ? t : t - c->tiles_a;
     int lo = 0, hi = a.num_groups;
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (nt * c->mt_prefix[mid] <= t) lo = mid; else hi = mid;
+      if (nt * pre[mid] <= tt) lo = mid; else hi = mid;
     }
     ti.g = lo;
-    const int mt_g = c->mt_prefix[lo + 1] - c->mt_prefix[lo];
-    const int local = t - nt * c->mt_prefix[lo];
-    const int j = local / mt_g, i = local - j * mt_g;
+    const int mt_g = pre[lo + 1] - pre[lo];
+    const int local = tt - nt * pre[lo];
+    const int j = local / mt_g;
+    int i = local - j * mt_g;
+    if (phase_a) i += c->a0[lo];
+    else if (i >= c->a0[lo]) i += c->na[lo];
     ti.row0 = a.group_base[lo] + i * PM;
     ti.rows_pair = min(PM, a.group_rows[lo] - i * PM);
     ti.n0 = j * bn_out;
@@ -198,14 +209,31 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
     const int nt = (args.n + bn_out - 1) / bn_out;
     ctrl->n_tiles = nt;
     if constexpr (!kKGroup) {
-      int acc = 0, rows = 0;
+      int acc_a = 0, acc_b = 0, rows = 0;
       for (int g = 0; g < args.num_groups; ++g) {
-        ctrl->mt_prefix[g] = acc;
-        acc += (args.group_rows[g] + PM - 1) / PM;
-        rows += args.group_rows[g];
+        const int gr = args.group_rows[g];
+        const int mt = (gr + PM - 1) / PM;
+        int a0 = 0, na = 0;
+        if (args.local_begin != nullptr && args.tile_flags != nullptr) {
+          const int lb = args.local_begin[g], le = min(gr, lb + args.local_rows[g]);
+          a0 = (lb + PM - 1) / PM;
+          // a tile is local-only when it lies inside [lb, le); the last tile of the group also counts when le == gr
+          int a1 = (le == gr) ? mt : le / PM;
+          na = max(0, a1 - a0);
+          if (na == 0) a0 = 0;
+        }
+        ctrl->a0[g] = static_cast<short>(a0);
+        ctrl->na[g] = static_cast<short>(na);
+        ctrl->mta_prefix[g] = acc_a;
+        ctrl->mt_prefix[g] = acc_b;
+        acc_a += na;
+        acc_b += mt - na;
+        rows += gr;
       }
-      ctrl->mt_prefix[args.num_groups] = acc;
-      ctrl->total_tiles = acc * nt;
+      ctrl->mta_prefix[args.num_groups] = acc_a;
+      ctrl->mt_prefix[args.num_groups] = acc_b;
+      ctrl->tiles_a = acc_a * nt;
+      ctrl->total_tiles = (acc_a + acc_b) * nt;
       ctrl->total_rows = rows;
     } else {
       ctrl->total_tiles = args.num_groups * (args.m_per_group / PM) * nt;
@@ -230,13 +258,11 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
   const uint32_t tmem_base = ctrl->tmem_base;
   const int total_tiles = ctrl->total_tiles;
 
-  // ---- dispatch role ---------------------------------------------------------------------------------
+  // ---- dispatch role (fused all-to-all dispatch) -----------------------------------------------------
+  // Run by the epilogue warps before their first accumulator is due (see below); the producer and MMA warps go
+  // straight to the tile loop and start on tiles whose rows have already landed.
+  // (trace: the last recorded tile slot of every CTA holds {0: kernel start, 1: this CTA's dispatch part finished})
   if (threadIdx.x == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 0);
-  if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) {
-    dispatch_rows<8>(args.disp, args.status);
-    __syncthreads();
-  }
-  if (threadIdx.x == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
 
   if (warp == 0) {
     // ======================= TMA producer (both CTAs) =======================
@@ -367,6 +393,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
     // ======================= epilogue (warps 2..9, both CTAs) =======================
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
+    if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8>(args.disp, args.status);
+    if (warp == 2 && lane == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
     int as = 0, aphase = 0, seq = 0;
     for (int t = pair; t < total_tiles; t += n_pairs, ++seq) {
       const PairTile ti = decode_pair_tile<kKGroup, kEpi>(t, args, ctrl);

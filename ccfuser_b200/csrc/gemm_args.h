@@ -38,7 +38,9 @@ struct CcfDispatchArgs {
   const float* slot_gate;   // [S] gate weight of the slot
   const void* saved_comb;   // backward only: [S, D] scaled expert outputs saved by the forward pass
   float* dgate;             // backward only: [S] gradient of the gate weight
-  int* slot_row;            // [S] out: destination row, -1 if dropped
+  int* slot_row;            // [S] out: destination row (dropped slots are set to -1 by the routing kernels)
+  const int* sorted_slot;   // [S] slot ids in destination order (own experts first, then the next owner's, ...)
+  const int* order_off;     // [E_total + 1]; order_off[E_total] = number of kept rows = length of sorted_slot in use
   void* peer_recv[CCF_MAX_RANKS];      // receive buffer [R, D] of every rank
   int* peer_row_src[CCF_MAX_RANKS];    // [R] packed (source rank << 24 | slot)
   float* peer_row_gate[CCF_MAX_RANKS]; // [R]
@@ -54,6 +56,8 @@ struct CcfDispatchArgs {
   int fp16;                 // 1: fp16 rows, 0: bf16 rows
   int max_rows;             // rows of a receive buffer (bounds check)
   int total_index;          // element of peer_tile_flags[] that counts all rows arrived on that rank (-1 = none)
+  int e_total;              // number of experts over all ranks
+  int pad0;
 };
 
 struct CcfGemmArgs {
@@ -61,6 +65,8 @@ struct CcfGemmArgs {
   const int* group_base;    // [G] first row of each group (multiple of 128)
   const int* group_rows;    // [G] valid rows of each group
   const int* tile_flags;    // optional [R / 128] arrival counters gating the A tiles (row-grouped only)
+  const int* local_begin;   // optional [G] offset of the rows pushed by this rank itself inside each group
+  const int* local_rows;    // optional [G] their number; tiles made only of such rows are scheduled first
   // epilogue operands
   void* out0;
   void* out1;

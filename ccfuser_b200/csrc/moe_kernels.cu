@@ -94,7 +94,7 @@ constexpr int kRouteBlock = 1024;
 
 __global__ void __launch_bounds__(kRouteBlock)
 route_hist_kernel(const int* __restrict__ expert, int S, int E, int cap, int* pos, int* block_hist, int* block_off,
-                  int* count_raw, int* count_kept, int* ticket) {
+                  int* count_raw, int* count_kept, int* ticket, int* order_off, int first_expert) {
   __shared__ int wh[32][CCF_MAX_GROUPS];
   __shared__ int is_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -135,16 +135,38 @@ route_hist_kernel(const int* __restrict__ expert, int S, int E, int cap, int* po
       count_raw[tid] = run;
       count_kept[tid] = min(run, cap);
     }
-    if (tid == 0) *ticket = 0;
+    __syncthreads();
+    if (tid == 0) {
+      *ticket = 0;
+      if (order_off != nullptr) {
+        // destination order of this rank's kept rows: experts starting with this rank's own (first_expert), then the
+        // next owner's, ... so that local rows are pushed first and every source starts with a different owner
+        int run = 0;
+        for (int k = 0; k < E; ++k) {
+          const int e = (first_expert + k) % E;
+          order_off[e] = run;
+          run += count_kept[e];
+        }
+        order_off[E] = run;  // kept rows in total
+      }
+    }
   }
 }
 
 __global__ void route_pos_kernel(const int* __restrict__ expert, int S, int E, const int* __restrict__ block_off,
-                                 int* pos) {
+                                 int* pos, int cap, const int* __restrict__ order_off, int* sorted_slot, int* slot_row) {
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= S) return;
   const int e = expert[s];
-  if (e >= 0 && e < E) pos[s] += block_off[(s / kRouteBlock) * E + e];
+  int p = pos[s];
+  if (e >= 0 && e < E) {
+    p += block_off[(s / kRouteBlock) * E + e];
+    pos[s] = p;
+  }
+  if (sorted_slot != nullptr) {
+    if (e >= 0 && e < E && p < cap) sorted_slot[order_off[e] + p] = s;   // inverse of the destination order
+    else if (slot_row != nullptr) slot_row[s] = -1;                       // dropped slots are never dispatched
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -165,6 +187,8 @@ struct PlanArgs {
   int* group_rows;                     // out [E_loc]
   int* sent_rows;                      // out [W] kept rows this rank sends to each owner
   int* table_copy;                     // out [W, E_total] snapshot of the table (routing statistics)
+  int* local_begin;                    // out [E_loc] offset of this rank's own rows inside each local expert (optional)
+  int* local_rows;                     // out [E_loc] number of those rows
   int* status;
   unsigned long long wait_limit_ns;
   int world, my_rank, e_total, e_loc, epoch, max_rows;
@@ -195,7 +219,11 @@ __global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanA
   __syncthreads();
   if (failed) {
     for (int e = tid; e < a.e_total; e += blockDim.x) a.dst_base[e] = 0;
-    for (int e = tid; e < a.e_loc; e += blockDim.x) { a.group_base[e] = 0; a.group_rows[e] = 0; }
+    for (int e = tid; e < a.e_loc; e += blockDim.x) {
+      a.group_base[e] = 0;
+      a.group_rows[e] = 0;
+      if (a.local_begin != nullptr) { a.local_begin[e] = 0; a.local_rows[e] = 0; }
+    }
     if (tid < a.world) a.sent_rows[tid] = 0;
     return;
   }
@@ -233,6 +261,10 @@ __global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanA
     const int e = a.my_rank * a.e_loc + i;
     a.group_base[i] = base[e];
     a.group_rows[i] = min(rows[e], max(0, a.max_rows - base[e]));
+    if (a.local_begin != nullptr) {
+      a.local_begin[i] = myoff[e];
+      a.local_rows[i] = max(0, min(a.count_kept[e], a.max_rows - (base[e] + myoff[e])));
+    }
   }
 }
 
@@ -406,16 +438,33 @@ int ccf_topk_softmax_bwd(const int* idx, const float* w, const float* dw, int T,
 }
 
 // scratch: block_hist [nb*E] + block_off [nb*E] ints, ticket 1 int (zero before the first call)
-int ccf_route(const int* expert, int S, int E, int cap, int* pos, int* block_hist, int* block_off, int* count_raw,
-              int* count_kept, int* ticket, void* stream) {
+static int route_impl(const int* expert, int S, int E, int cap, int* pos, int* block_hist, int* block_off,
+                      int* count_raw, int* count_kept, int* ticket, int* order_off, int* sorted_slot, int* slot_row,
+                      int first_expert, void* stream) {
   if (E > CCF_MAX_GROUPS) return -2;
   if (S == 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int nb = (S + ccf::kRouteBlock - 1) / ccf::kRouteBlock;
   ccf::route_hist_kernel<<<nb, ccf::kRouteBlock, 0, st>>>(expert, S, E, cap, pos, block_hist, block_off, count_raw,
-                                                          count_kept, ticket);
-  ccf::route_pos_kernel<<<(S + 255) / 256, 256, 0, st>>>(expert, S, E, block_off, pos);
+                                                          count_kept, ticket, order_off, first_expert);
+  ccf::route_pos_kernel<<<(S + 255) / 256, 256, 0, st>>>(expert, S, E, block_off, pos, cap, order_off, sorted_slot,
+                                                         slot_row);
   return last_err();
+}
+
+int ccf_route(const int* expert, int S, int E, int cap, int* pos, int* block_hist, int* block_off, int* count_raw,
+              int* count_kept, int* ticket, void* stream) {
+  return route_impl(expert, S, E, cap, pos, block_hist, block_off, count_raw, count_kept, ticket, nullptr, nullptr,
+                    nullptr, 0, stream);
+}
+
+// Same, and also the destination order of the kept slots: order_off [E + 1] (order_off[E] = kept rows in total),
+// sorted_slot [S] (slot id at each position of that order), slot_row [S] set to -1 for dropped slots.
+int ccf_route_ordered(const int* expert, int S, int E, int cap, int* pos, int* block_hist, int* block_off,
+                      int* count_raw, int* count_kept, int* ticket, int* order_off, int* sorted_slot, int* slot_row,
+                      int first_expert, void* stream) {
+  return route_impl(expert, S, E, cap, pos, block_hist, block_off, count_raw, count_kept, ticket, order_off,
+                    sorted_slot, slot_row, first_expert, stream);
 }
 
 int ccf_sizeof_plan_args() { return static_cast<int>(sizeof(ccf::PlanArgs)); }

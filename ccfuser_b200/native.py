@@ -28,19 +28,19 @@ _vp = C.c_void_p
 class DispatchArgs(C.Structure):
     _fields_ = [
         ("x", _vp), ("slot_expert", _vp), ("slot_pos", _vp), ("dst_base", _vp), ("slot_gate", _vp),
-        ("saved_comb", _vp), ("dgate", _vp), ("slot_row", _vp),
+        ("saved_comb", _vp), ("dgate", _vp), ("slot_row", _vp), ("sorted_slot", _vp), ("order_off", _vp),
         ("peer_recv", _vp * MAX_RANKS), ("peer_row_src", _vp * MAX_RANKS),
         ("peer_row_gate", _vp * MAX_RANKS), ("peer_tile_flags", _vp * MAX_RANKS),
         ("work_counter", _vp),
         ("tokens", C.c_int), ("top_k", C.c_int), ("d", C.c_int), ("capacity", C.c_int),
         ("experts_per_rank", C.c_int), ("my_rank", C.c_int), ("backward", C.c_int), ("fp16", C.c_int),
-        ("max_rows", C.c_int), ("total_index", C.c_int),
+        ("max_rows", C.c_int), ("total_index", C.c_int), ("e_total", C.c_int), ("pad0", C.c_int),
     ]
 
 
 class GemmArgs(C.Structure):
     _fields_ = [
-        ("group_base", _vp), ("group_rows", _vp), ("tile_flags", _vp),
+        ("group_base", _vp), ("group_rows", _vp), ("tile_flags", _vp), ("local_begin", _vp), ("local_rows", _vp),
         ("out0", _vp), ("out1", _vp), ("out2", _vp), ("bias0", _vp), ("bias1", _vp), ("aux0", _vp), ("aux1", _vp),
         ("row_src", _vp), ("row_gate", _vp),
         ("peer_comb", _vp * MAX_RANKS), ("peer_done", _vp * MAX_RANKS),
@@ -68,6 +68,7 @@ class PlanArgs(C.Structure):
     _fields_ = [
         ("count_kept", _vp), ("peer_table", _vp * MAX_RANKS), ("peer_flag", _vp * MAX_RANKS),
         ("dst_base", _vp), ("group_base", _vp), ("group_rows", _vp), ("sent_rows", _vp), ("table_copy", _vp),
+        ("local_begin", _vp), ("local_rows", _vp),
         ("status", _vp), ("wait_limit_ns", C.c_ulonglong),
         ("world", C.c_int), ("my_rank", C.c_int), ("e_total", C.c_int), ("e_loc", C.c_int), ("epoch", C.c_int),
         ("max_rows", C.c_int),
@@ -125,6 +126,7 @@ def _declare(lib):
         "ccf_topk_softmax": ([p, i, i, i, i, i, p, p, p], i),
         "ccf_topk_softmax_bwd": ([p, p, p, i, i, i, p, i, i, p], i),
         "ccf_route": ([p, i, i, i, p, p, p, p, p, p, p], i),
+        "ccf_route_ordered": ([p, i, i, i, p, p, p, p, p, p, p, p, p, i, p], i),
         "ccf_plan": ([C.POINTER(PlanArgs), p], i),
         "ccf_dispatch": ([C.POINTER(DispatchArgs), p, p, i, p], i),
         "ccf_combine_wait": ([p, p, p, i, i, ull, p, p], i),

@@ -88,8 +88,7 @@ class CommContext:
         self.block_off = torch.zeros(nb * e_total, dtype=torch.int32, device=device)
         self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
         self.wait_ns = int(float(os.environ.get("CCFUSER_WAIT_LIMIT_S", "5")) * 1e9)
-        # CTAs that run the dispatch role before taking GEMM tiles. Rows are pushed in token order, so tiles only
-        # complete towards the end of the dispatch; with every CTA helping, that phase is as short as the links allow.
+        # CTAs whose epilogue warps run the dispatch role before their first accumulator is due (default: all)
         self.n_comm = env_flag("COMM_CTAS", 1 << 20)
 
     @classmethod
@@ -183,6 +182,10 @@ class FusedMoE:
         i32 = dict(dtype=torch.int32, device=dev)
         self.slot_pos = torch.zeros(self.max_slots, **i32)
         self.slot_row = torch.full((self.max_slots,), -1, **i32)
+        self.sorted_slot = torch.zeros(self.max_slots, **i32)        # slot ids in destination order
+        self.order_off = torch.zeros(cfg.num_experts + 1, **i32)     # start of each expert in that order; [-1] = kept rows
+        self.local_begin = torch.zeros(e_loc, **i32)                 # this rank's own rows inside each local expert
+        self.local_rows = torch.zeros(e_loc, **i32)
         self.count_raw = torch.zeros(cfg.num_experts, **i32)
         self.count_kept = torch.zeros(cfg.num_experts, **i32)
         self.dst_base = torch.zeros(cfg.num_experts, **i32)
@@ -235,6 +238,9 @@ class FusedMoE:
         a.saved_comb = self.comb.data_ptr() if backward else 0
         a.dgate = N.ptr(dgate)
         a.slot_row = self.slot_row.data_ptr()
+        a.sorted_slot = self.sorted_slot.data_ptr()
+        a.order_off = self.order_off.data_ptr()
+        a.e_total = cfg.num_experts
         recv = ctx.peer("grecv") if backward else self.buf.peer_ptrs(self.off_xrecv)
         rs, rg, tf = ctx.peer("row_src"), ctx.peer("row_gate"), ctx.peer("tile_flags")
         for r in range(self.world):
@@ -269,9 +275,11 @@ class FusedMoE:
         lib, cfg, cc = N.load(), self.cfg, self.ctx
         st = N.stream_ptr()
         e_tot, e_loc = cfg.num_experts, cfg.experts_per_rank
-        N.check(lib.ccf_route(idx.data_ptr(), tokens * cfg.top_k, e_tot, cfg.capacity(tokens), self.slot_pos.data_ptr(),
-                              cc.block_hist.data_ptr(), cc.block_off.data_ptr(), self.count_raw.data_ptr(),
-                              self.count_kept.data_ptr(), cc.ticket.data_ptr(), st), "ccf_route")
+        N.check(lib.ccf_route_ordered(idx.data_ptr(), tokens * cfg.top_k, e_tot, cfg.capacity(tokens),
+                                      self.slot_pos.data_ptr(), cc.block_hist.data_ptr(), cc.block_off.data_ptr(),
+                                      self.count_raw.data_ptr(), self.count_kept.data_ptr(), cc.ticket.data_ptr(),
+                                      self.order_off.data_ptr(), self.sorted_slot.data_ptr(), self.slot_row.data_ptr(),
+                                      self.rank * e_loc, st), "ccf_route_ordered")
         cc.epoch += 1
         p = N.PlanArgs()
         p.count_kept = self.count_kept.data_ptr()
@@ -280,6 +288,7 @@ class FusedMoE:
             p.peer_table[r], p.peer_flag[r] = tb[r], fl[r]
         p.dst_base, p.group_base, p.group_rows = self.dst_base.data_ptr(), self.group_base.data_ptr(), self.group_rows.data_ptr()
         p.sent_rows, p.table_copy, p.status = self.sent_rows.data_ptr(), self.table_copy.data_ptr(), cc.ws.status.data_ptr()
+        p.local_begin, p.local_rows = self.local_begin.data_ptr(), self.local_rows.data_ptr()
         p.wait_limit_ns = cc.wait_ns
         p.world, p.my_rank, p.e_total, p.e_loc, p.epoch, p.max_rows = self.world, self.rank, e_tot, e_loc, cc.epoch, self.max_rows
         N.check(lib.ccf_plan(C.byref(p), st), "ccf_plan")
@@ -294,7 +303,7 @@ class FusedMoE:
         disp = self._dispatch_args(x, t, idx, gate_w, None, backward=False)
         common = dict(group_base=self.group_base, group_rows=self.group_rows, num_groups=e_loc, tile_flags=cc.tile_flags,
                       dispatch=disp, n_comm_ctas=cc.n_comm, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace,
-                      total_index=self.max_rows // TILE)
+                      total_index=self.max_rows // TILE, local_begin=self.local_begin, local_rows=self.local_rows)
         if cfg.activation == "swiglu":
             G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), b1=wg.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K,
                      epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre, out2=self.h_pre2,
@@ -351,7 +360,7 @@ class _FusedMoEFn(torch.autograd.Function):
         t, d, f, e_loc = ctx.tokens, cfg.d_model, cfg.d_ffn, cfg.experts_per_rank
         fp16 = int(cfg.dtype == torch.float16)
         dy = dy.contiguous()
-        dgate = torch.empty(t * cfg.top_k, dtype=torch.float32, device=dy.device)
+        dgate = torch.zeros(t * cfg.top_k, dtype=torch.float32, device=dy.device)  # dropped slots keep 0
         swiglu = cfg.activation == "swiglu"
         # 1+2. push g*dy rows (dispatch role) + dgrad-2 with the activation derivative in the epilogue
         disp = fm._dispatch_args(dy, t, idx, gate_w, "grecv", backward=True, dgate=dgate)
@@ -362,11 +371,13 @@ class _FusedMoEFn(torch.autograd.Function):
         if swiglu:
             G.launch(a0=cc.grecv, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DSWIGLU, n=f, k=d,
                      b_group_rows=d, out0=dh, out1=dh2, aux0=fm.h_pre, aux1=fm.h_pre2, tile_flags=cc.tile_flags,
-                     dispatch=disp, n_comm_ctas=cc.n_comm, total_index=fm.max_rows // TILE, **common)
+                     dispatch=disp, n_comm_ctas=cc.n_comm, total_index=fm.max_rows // TILE, local_begin=fm.local_begin,
+                     local_rows=fm.local_rows, **common)
         else:
             G.launch(a0=cc.grecv, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DACT, n=f, k=d,
                      b_group_rows=d, out0=dh, aux0=fm.h_pre, act=N.ACT_CODE[cfg.activation], tile_flags=cc.tile_flags,
-                     dispatch=disp, n_comm_ctas=cc.n_comm, total_index=fm.max_rows // TILE, **common)
+                     dispatch=disp, n_comm_ctas=cc.n_comm, total_index=fm.max_rows // TILE, local_begin=fm.local_begin,
+                     local_rows=fm.local_rows, **common)
         cc.tile_flags.zero_()
         # 3. wgrad-2: dW2[e] = (g dy)^T h_act   [d, f]
         dw2 = torch.empty_like(w2)

@@ -70,7 +70,7 @@ def _is_fp16(t: torch.Tensor) -> int:
 def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num_groups,
            a1=None, b1=None, kgroup=False, m_per_group=0, kseg=1, b_group_rows=0,
            out0=None, out1=None, out2=None, bias0=None, bias1=None, aux0=None, aux1=None, ld_out=None,
-           act=N.ACT_NONE, out_fp32=False, tile_flags=None, row_src=None, row_gate=None,
+           act=N.ACT_NONE, out_fp32=False, tile_flags=None, local_begin=None, local_rows=None, row_src=None, row_gate=None,
            peer_comb=None, peer_done=None, world=1, send_finish=0, max_slots=0,
            dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, total_index=-1, two_cta=None, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
            workspace: Optional[Workspace] = None):
@@ -81,6 +81,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     g = L.args
     g.group_base, g.group_rows = N.ptr(group_base), N.ptr(group_rows)
     g.tile_flags = N.ptr(tile_flags)
+    g.local_begin, g.local_rows = N.ptr(local_begin), N.ptr(local_rows)
     g.out0, g.out1, g.out2 = N.ptr(out0), N.ptr(out1), N.ptr(out2)
     g.bias0, g.bias1, g.aux0, g.aux1 = N.ptr(bias0), N.ptr(bias1), N.ptr(aux0), N.ptr(aux1)
     g.row_src, g.row_gate = N.ptr(row_src), N.ptr(row_gate)

@@ -53,6 +53,38 @@ def test_route_kernel_bit_exact(s, e, cap):
     assert torch.equal(kept.cpu().long(), ref.count)
 
 
+def test_route_ordered_gives_destination_order():
+    """ccf_route_ordered: kept slots listed expert by expert starting at `first_expert`, in position order."""
+    from ccfuser_b200 import native as N
+    lib = N.load()
+    s, e, cap, first = 5000, 24, 150, 8
+    g = torch.Generator().manual_seed(5)
+    expert = torch.randint(0, e, (s,), generator=g).int().cuda()
+    nb = (s + 1023) // 1024
+    i32 = dict(dtype=torch.int32, device="cuda")
+    pos, bh, bo = torch.empty(s, **i32), torch.zeros(nb * e, **i32), torch.zeros(nb * e, **i32)
+    raw, kept, ticket = torch.zeros(e, **i32), torch.zeros(e, **i32), torch.zeros(1, **i32)
+    order_off, sorted_slot, slot_row = torch.zeros(e + 1, **i32), torch.full((s,), -5, **i32), torch.full((s,), 7, **i32)
+    N.check(lib.ccf_route_ordered(expert.data_ptr(), s, e, cap, pos.data_ptr(), bh.data_ptr(), bo.data_ptr(), raw.data_ptr(),
+                                  kept.data_ptr(), ticket.data_ptr(), order_off.data_ptr(), sorted_slot.data_ptr(),
+                                  slot_row.data_ptr(), first, N.stream_ptr()), "route_ordered")
+    torch.cuda.synchronize()
+    ex, ps, kp = expert.cpu().long(), pos.cpu().long(), kept.cpu().long()
+    order = [(first + k) % e for k in range(e)]
+    off, run = {}, 0
+    for x in order:
+        off[x] = run
+        run += int(kp[x])
+    assert int(order_off[e]) == run and all(int(order_off[x]) == off[x] for x in range(e))
+    ss = sorted_slot.cpu().long()
+    for slot in range(s):
+        if ps[slot] < cap:
+            assert int(ss[off[int(ex[slot])] + int(ps[slot])]) == slot
+            assert int(slot_row[slot]) == 7          # left for the dispatch role to fill in
+        else:
+            assert int(slot_row[slot]) == -1
+
+
 def _make_layer(act, cf, e=8, d=256, f=512, tokens=1024, k=2, dtype=torch.bfloat16, bias=True):
     from ccfuser_b200 import MoEConfig, MoELayer
     torch.manual_seed(0)

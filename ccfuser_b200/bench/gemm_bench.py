@@ -50,6 +50,7 @@ def main():
     ap.add_argument("--d", type=int, default=4096)
     ap.add_argument("--f", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--out", default="", help="optional JSON file for the records")
     args = ap.parse_args()
     peak, _, src = measured_peaks()
     dev = "cuda"
@@ -104,9 +105,10 @@ def main():
         report("wgrad2", 2 * r * d * f, lambda: G.launch(
             a0=y, b0=h, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True, m_per_group=d,
             group_base=gb, group_rows=gr, num_groups=e, out0=dw, ld_out=f))
-    os.makedirs("gpurun_out", exist_ok=True)
-    with open("gpurun_out/gemm_bench.json", "w") as fh:
-        json.dump(out, fh, indent=1)
+    if args.out:
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+        with open(args.out, "w") as fh:
+            json.dump(out, fh, indent=1)
 
 
 if __name__ == "__main__":

@@ -250,7 +250,7 @@ def main():
             "config": {"model": f"GPT-MoE {args.layers}L d2048 h16 seq1024 vocab50257, MoE every other layer (64 experts, top-2, ffn 8192, GELU)",
                        "global_batch": args.batch * world, "seq_len": seq, "parallelism": f"ep{world}" + (f"+dp{world}" if world > 1 else ""),
                        "optimizer": "sgd", "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2",
-                       "loss": round(float(loss), 4), "capacity_factor": None, "max_rank_load_over_balanced": imbalance,
+                       "loss": round(float(loss.detach()), 4), "capacity_factor": None, "max_rank_load_over_balanced": imbalance,
                        "overflow": overflow},
             "clocks": clocks,
             "e2e": {"value": round(tokens_per_step * args.steps / (ms2 / 1e3), 1), "unit": "tokens/s",

@@ -133,7 +133,7 @@ def main():
         if i >= args.warmup:
             times.append(ms)
         if rank == 0 and i % 10 == 0:
-            print(f"STEP-{i}: step_time = {ms:.3f} ms, loss = {float(loss):.4f}", flush=True)
+            print(f"STEP-{i}: step_time = {ms:.3f} ms, loss = {float(loss.detach()):.4f}", flush=True)
     avg = sum(times) / max(1, len(times))
     t = torch.tensor([avg], device=dev, dtype=torch.float64)
     if world > 1:
@@ -142,7 +142,7 @@ def main():
         print(f"{args.variant} {args.model} {args.experts_per_gpu} [Summary] Average synchronized step_time = {float(t):.3f} ms")
         print(json.dumps({"bench": "e2e", "model": args.model, "variant": args.variant, "n_gpus": world,
                           "experts_per_gpu": args.experts_per_gpu, "step_ms": round(float(t), 3),
-                          "tokens_per_s": round(tokens * world / float(t) * 1e3, 1), "final_loss": round(float(loss), 4)}))
+                          "tokens_per_s": round(tokens * world / float(t) * 1e3, 1), "final_loss": round(float(loss.detach()), 4)}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

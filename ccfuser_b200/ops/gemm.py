@@ -22,7 +22,6 @@ class Workspace:
     def __init__(self, device):
         self.sched = torch.zeros(8, dtype=torch.int32, device=device)
         self.status = torch.zeros(2, dtype=torch.int32, device=device)  # [first hard error, overflow count]
-        self.dispatch_done = torch.zeros(1, dtype=torch.int32, device=device)
 
     @classmethod
     def get(cls, device) -> "Workspace":

@@ -1,0 +1,55 @@
+"""Data parallelism around expert parallelism on CPU (gloo): expert parameters stay local, replicated ones are reduced;
+model families run on the CPU backend."""
+import torch
+import torch.distributed as dist
+
+from tests.mp_util import run_ranks
+
+
+def _ddp_rank(rank, world):
+    from ccfuser_b200.models.gpt_moe import GPTMoE, GPTMoEConfig
+    from ccfuser_b200.parallel.ddp import expert_param_names, wrap_ddp
+    torch.manual_seed(0)   # same replicated parameters everywhere
+    c = GPTMoEConfig(vocab_size=128, n_layer=2, n_head=2, d_model=32, d_ffn=64, seq_len=16, num_experts=4, top_k=2,
+                     ep_size=world, backend="cpu", max_tokens=32, dtype=torch.float32)
+    model = GPTMoE(c)
+    names = expert_param_names(model)
+    ddp = wrap_ddp(model)
+    ignored = set(getattr(model, "_ddp_params_and_buffers_to_ignore", []))
+    g = torch.Generator().manual_seed(10 + rank)   # different data per rank
+    ids = torch.randint(0, 128, (2, 16), generator=g)
+    loss = ddp(ids, ids.roll(-1, 1))
+    loss.backward()
+    rep = model.h[0].attn.c_attn.weight.grad.clone()
+    gate = model.h[1].mlp.gate.gate.weight.grad.clone()
+    exp = model.h[1].mlp.experts.htoh4.weight.grad.clone()
+    outs = []
+    for t in (rep, gate, exp):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        outs.append(bool(torch.allclose(parts[0], parts[1])))
+    return names, sorted(ignored), outs
+
+
+def test_ddp_skips_expert_parameters():
+    res = run_ranks(_ddp_rank, 2)
+    names, ignored, (rep_equal, gate_equal, exp_equal) = res[0]
+    assert names and all(".experts." in n for n in names)
+    assert set(names) == set(ignored)
+    assert rep_equal and gate_equal, "replicated parameters (attention, router) get the all-reduced gradient"
+    assert not exp_equal, "expert gradients are local to the owning rank"
+
+
+def test_all_model_families_step_on_cpu():
+    from ccfuser_b200.examples import train
+    import sys
+    for model in ("gpt", "bert", "txl"):
+        for variant in ("dense", "nccl"):
+            argv = ["train", "--model", model, "--variant", variant, "--steps", "1", "--warmup", "0", "--layers", "2",
+                    "--batch", "2", "--seq", "16", "--experts-per-gpu", "4", "--dtype", "bf16"]
+            old = sys.argv
+            sys.argv = argv
+            try:
+                train.main()
+            finally:
+                sys.argv = old

@@ -61,15 +61,23 @@ class GPTMoEConfig:
 
 
 class CausalSelfAttention(nn.Module):
+    """Causal multi-head attention. Query, key and value have their own projections: with one fused QKV matrix the
+    backward pass has to concatenate the three gradients again (a 100 MB copy per layer at the benchmark size)."""
+
     def __init__(self, c: GPTMoEConfig, device=None):
         super().__init__()
         self.n_head = c.n_head
-        self.c_attn = nn.Linear(c.d_model, 3 * c.d_model, device=device, dtype=c.dtype)
+        self.q_proj = nn.Linear(c.d_model, c.d_model, device=device, dtype=c.dtype)
+        self.k_proj = nn.Linear(c.d_model, c.d_model, device=device, dtype=c.dtype)
+        self.v_proj = nn.Linear(c.d_model, c.d_model, device=device, dtype=c.dtype)
         self.c_proj = nn.Linear(c.d_model, c.d_model, device=device, dtype=c.dtype)
 
     def forward(self, x):
         b, s, d = x.shape
-        q, k, v = self.c_attn(x).view(b, s, 3, self.n_head, d // self.n_head).permute(2, 0, 3, 1, 4)
+        h = self.n_head
+        q = self.q_proj(x).view(b, s, h, d // h).transpose(1, 2)
+        k = self.k_proj(x).view(b, s, h, d // h).transpose(1, 2)
+        v = self.v_proj(x).view(b, s, h, d // h).transpose(1, 2)
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         return self.c_proj(y.transpose(1, 2).reshape(b, s, d))
 

@@ -101,7 +101,16 @@ def load(build_if_missing: bool = True):
             from . import build as _build
             try:
                 if _build.needs_build():
-                    _build.build()
+                    # several ranks of one job may arrive here together: one builds, the others wait for the lock
+                    import fcntl
+                    os.makedirs(os.path.dirname(path), exist_ok=True)
+                    with open(path + ".lock", "w") as lock:
+                        fcntl.flock(lock, fcntl.LOCK_EX)
+                        try:
+                            if _build.needs_build():
+                                _build.build()
+                        finally:
+                            fcntl.flock(lock, fcntl.LOCK_UN)
             except Exception:
                 if not os.path.exists(path):
                     raise

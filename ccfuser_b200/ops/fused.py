@@ -28,10 +28,9 @@ from __future__ import annotations
 
 import ctypes as C
 import os
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
-import torch.nn.functional as F
 
 from .. import native as N
 from ..config import env_flag
@@ -227,7 +226,7 @@ class FusedMoE:
 
     # ---- launch helpers ------------------------------------------------------------------------
     def _dispatch_args(self, src: torch.Tensor, tokens: int, idx: torch.Tensor, gate_w: torch.Tensor,
-                       recv_name_ctx: Optional[str], backward: bool, dgate=None) -> N.DispatchArgs:
+                       backward: bool, dgate=None) -> N.DispatchArgs:
         cfg, ctx = self.cfg, self.ctx
         a = N.DispatchArgs()
         a.x = src.data_ptr()
@@ -300,7 +299,7 @@ class FusedMoE:
         cfg, cc = self.cfg, self.ctx
         t, d = x.shape
         f, e_loc = cfg.d_ffn, cfg.experts_per_rank
-        disp = self._dispatch_args(x, t, idx, gate_w, None, backward=False)
+        disp = self._dispatch_args(x, t, idx, gate_w, backward=False)
         common = dict(group_base=self.group_base, group_rows=self.group_rows, num_groups=e_loc, tile_flags=cc.tile_flags,
                       dispatch=disp, n_comm_ctas=cc.n_comm, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace,
                       total_index=self.max_rows // TILE, local_begin=self.local_begin, local_rows=self.local_rows)
@@ -363,7 +362,7 @@ class _FusedMoEFn(torch.autograd.Function):
         dgate = torch.zeros(t * cfg.top_k, dtype=torch.float32, device=dy.device)  # dropped slots keep 0
         swiglu = cfg.activation == "swiglu"
         # 1+2. push g*dy rows (dispatch role) + dgrad-2 with the activation derivative in the epilogue
-        disp = fm._dispatch_args(dy, t, idx, gate_w, "grecv", backward=True, dgate=dgate)
+        disp = fm._dispatch_args(dy, t, idx, gate_w, backward=True, dgate=dgate)
         common = dict(group_base=fm.group_base, group_rows=fm.group_rows, num_groups=e_loc, wait_ns=cc.wait_ns,
                       workspace=cc.ws)
         dh = torch.empty(fm.max_rows, f, dtype=cfg.dtype, device=dy.device)

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import threading
 import time
-from typing import Callable, Optional
+from typing import Callable
 
 import torch.distributed as dist
 

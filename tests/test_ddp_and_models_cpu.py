@@ -20,7 +20,7 @@ def _ddp_rank(rank, world):
     ids = torch.randint(0, 128, (2, 16), generator=g)
     loss = ddp(ids, ids.roll(-1, 1))
     loss.backward()
-    rep = model.h[0].attn.c_attn.weight.grad.clone()
+    rep = model.h[0].attn.q_proj.weight.grad.clone()
     gate = model.h[1].mlp.gate.gate.weight.grad.clone()
     exp = model.h[1].mlp.experts.htoh4.weight.grad.clone()
     outs = []

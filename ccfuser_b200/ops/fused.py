@@ -204,6 +204,16 @@ class FusedMoE:
         if logits is None:
             raise TypeError("the fused backend needs a gate with a .logits(x) method (NaiveGate)")
         idx, w = topk_softmax(logits, cfg.top_k)
+        coef = getattr(layer.gate, "aux_loss_coef", 0.0)
+        if coef and coef > 0 and hasattr(layer.gate, "set_loss"):
+            # load-balance auxiliary loss, same definition as NaiveGate.forward (fraction of slots per expert times the
+            # mean router probability), kept in torch: it is a [T, E] reduction next to GEMMs that dominate the layer
+            probs = torch.softmax(logits.float(), dim=-1)
+            frac = torch.zeros(cfg.num_experts, device=x.device, dtype=torch.float32)
+            frac.scatter_add_(0, idx.reshape(-1).long(), torch.ones(idx.numel(), device=x.device))
+            layer.gate.set_loss(coef * cfg.num_experts * (frac / max(1, idx.numel()) * probs.mean(0)).sum())
+        elif hasattr(layer.gate, "set_loss"):
+            layer.gate.set_loss(None)
         ex = layer.experts
         wg = ex.htoh4_gate.weight if cfg.activation == "swiglu" else None
         bg = ex.htoh4_gate.bias if cfg.activation == "swiglu" else None

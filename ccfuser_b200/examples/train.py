@@ -103,10 +103,15 @@ def main():
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--optimizer", default="sgd", choices=["sgd", "adamw"])
     ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--save", default="", help="checkpoint prefix written at the end (per-rank expert shards + manifest)")
+    ap.add_argument("--resume", default="", help="checkpoint prefix to load before training (any EP degree)")
     args = ap.parse_args()
     rank, _, world = init_distributed()
     dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     model, batch, tokens = build(args, world, dev)
+    if args.resume:
+        from ..utils.checkpoint import load_ep_checkpoint
+        load_ep_checkpoint(model, args.resume, rank, world)
     wrapped = wrap_ddp(model) if world > 1 else model
     params = [p for p in model.parameters() if p.requires_grad]
     opt = torch.optim.SGD(params, lr=args.lr) if args.optimizer == "sgd" else torch.optim.AdamW(params, lr=args.lr)
@@ -143,6 +148,9 @@ def main():
         print(json.dumps({"bench": "e2e", "model": args.model, "variant": args.variant, "n_gpus": world,
                           "experts_per_gpu": args.experts_per_gpu, "step_ms": round(float(t), 3),
                           "tokens_per_s": round(tokens * world / float(t) * 1e3, 1), "final_loss": round(float(loss.detach()), 4)}))
+    if args.save:
+        from ..utils.checkpoint import save_ep_checkpoint
+        save_ep_checkpoint(model, args.save, rank, world, extra={"model": args.model, "variant": args.variant})
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -160,6 +160,8 @@ class FusedMoE:
         self.world, self.rank = cfg.ep_size, layer.ep_rank
         self.max_rows = cfg.max_recv_rows()
         self.max_slots = cfg.max_tokens * cfg.top_k
+        if self.max_slots >= (1 << 24):
+            raise ValueError("fused backend: max_tokens * top_k must stay below 2^24 (slot ids travel in 24 bits)")
         group = layer.ep_group if self.world > 1 else None
         self.ctx = CommContext.get(group, self.world, self.rank, self.device, self.max_rows, self.max_slots,
                                    cfg.d_model, cfg.num_experts, cfg.dtype)

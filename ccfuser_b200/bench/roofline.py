@@ -1,0 +1,71 @@
+"""Roofline arithmetic for the MoE layer: target time = the slower of (FLOPs / measured GEMM peak) and
+(bytes that must cross NVLink / link bandwidth); fraction = target / measured.
+
+    python -m ccfuser_b200.bench.roofline --tokens 16384 --d-model 4096 --d-ffn 14336 --top-k 2 --act swiglu \
+        --gpus 8 --measured-ms 34.9
+
+The denominators default to the values measured on this machine type (cuBLAS bf16 burst rate from
+MEASURED_PEAKS.json when present, peer-copy bandwidth 770 GB/s per direction).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+from .gemm_bench import measured_peaks
+
+NVLINK_GBS = 770.0
+
+
+def layer_flops(tokens: int, d_model: int, d_ffn: int, top_k: int, act: str, backward: bool = True,
+                kept_fraction: float = 1.0) -> float:
+    """FLOPs of one rank's share of an expert-parallel MoE FFN call (balanced routing)."""
+    mats = 3 if act == "swiglu" else 2
+    fwd = 2.0 * mats * d_model * d_ffn * tokens * top_k * kept_fraction
+    return fwd * (3 if backward else 1)
+
+
+def nvlink_bytes(tokens: int, d_model: int, top_k: int, gpus: int, backward: bool = True, elem: int = 2,
+                 kept_fraction: float = 1.0) -> float:
+    """Bytes one rank sends over NVLink per call: dispatch + combine (and their mirrors in backward)."""
+    remote = (gpus - 1) / gpus if gpus > 1 else 0.0
+    one_way = tokens * top_k * kept_fraction * d_model * elem * remote
+    return one_way * (4 if backward else 2)
+
+
+def roofline(tokens, d_model, d_ffn, top_k, act, gpus, backward=True, kept_fraction=1.0, peak_tflops=None,
+             nvlink_gbs=NVLINK_GBS):
+    if peak_tflops is None:
+        peak_tflops, _, src = measured_peaks()
+    else:
+        src = "given"
+    fl = layer_flops(tokens, d_model, d_ffn, top_k, act, backward, kept_fraction)
+    by = nvlink_bytes(tokens, d_model, top_k, gpus, backward, kept_fraction=kept_fraction)
+    t_compute = fl / (peak_tflops * 1e9)            # ms
+    t_link = by / (nvlink_gbs * 1e6)                # ms
+    return {"flops": fl, "nvlink_bytes": by, "compute_ms": t_compute, "link_ms": t_link,
+            "target_ms": max(t_compute, t_link), "bound": "compute" if t_compute >= t_link else "nvlink",
+            "peak_source": src, "peak_tflops": peak_tflops}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--d-model", type=int, default=4096)
+    ap.add_argument("--d-ffn", type=int, default=14336)
+    ap.add_argument("--top-k", type=int, default=2)
+    ap.add_argument("--act", default="swiglu")
+    ap.add_argument("--gpus", type=int, default=8)
+    ap.add_argument("--forward-only", action="store_true")
+    ap.add_argument("--kept-fraction", type=float, default=1.0)
+    ap.add_argument("--measured-ms", type=float, default=0.0)
+    a = ap.parse_args()
+    r = roofline(a.tokens, a.d_model, a.d_ffn, a.top_k, a.act, a.gpus, not a.forward_only, a.kept_fraction)
+    if a.measured_ms > 0:
+        r["measured_ms"] = a.measured_ms
+        r["fraction_of_roofline"] = round(r["target_ms"] / a.measured_ms, 3)
+    print(json.dumps(r))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,44 @@
+"""Configuration arithmetic and the roofline helper (CPU)."""
+import math
+
+import pytest
+import torch
+
+from ccfuser_b200 import MoEConfig, zipf_router_bias
+from ccfuser_b200.bench.roofline import layer_flops, nvlink_bytes, roofline
+
+
+def test_capacity_and_receive_bounds():
+    c = MoEConfig(d_model=64, d_ffn=128, num_experts=64, top_k=2, capacity_factor=1.2, ep_size=8, max_tokens=16384)
+    assert c.experts_per_rank == 8
+    assert c.capacity(16384) == math.ceil(1.2 * 16384 * 2 / 64) == 615
+    # per expert: 8 sources x 615 rows, padded to 128 -> 4992; 8 local experts
+    assert c.max_recv_rows() == 8 * 4992
+    n = MoEConfig(d_model=64, d_ffn=128, num_experts=8, top_k=2, capacity_factor=None, ep_size=1, max_tokens=1000)
+    assert n.capacity(1000) == 2000
+    assert n.max_recv_rows() % 128 == 0 and n.max_recv_rows() >= 2000
+    with pytest.raises(ValueError):
+        MoEConfig(d_model=64, d_ffn=128, num_experts=10, ep_size=4)
+    with pytest.raises(ValueError):
+        MoEConfig(d_model=64, d_ffn=128, num_experts=8, activation="tanh")
+
+
+def test_zipf_bias_orders_expert_popularity():
+    b = zipf_router_bias(64, 1.2, 1.0, seed=0)
+    p = torch.softmax(b, 0)
+    top = torch.sort(p, descending=True).values
+    # p_k ~ k^-1.2: the ratio of the two most popular experts is 2^1.2
+    assert abs(float(top[0] / top[1]) - 2 ** 1.2) < 1e-3
+    assert abs(float(p.sum()) - 1) < 1e-6
+
+
+def test_roofline_numbers_for_the_large_layer():
+    # 16384 tokens/GPU, top-2, SwiGLU 4096 -> 14336 -> 4096: 34.6 TFLOP per GPU forward + backward
+    fl = layer_flops(16384, 4096, 14336, 2, "swiglu")
+    assert abs(fl / 1e12 - 34.6) < 0.1
+    by = nvlink_bytes(16384, 4096, 2, 8)
+    assert abs(by / 1e6 - 4 * 268.4 * 7 / 8) < 1.0
+    r = roofline(16384, 4096, 14336, 2, "swiglu", 8, peak_tflops=1675.7)
+    assert r["bound"] == "compute" and abs(r["target_ms"] - 20.7) < 0.1
+    small = roofline(128, 4096, 14336, 2, "swiglu", 8, backward=False, peak_tflops=1675.7)
+    assert small["target_ms"] < 0.06 and small["bound"] == "compute"

@@ -33,19 +33,30 @@ def nvlink_bytes(tokens: int, d_model: int, top_k: int, gpus: int, backward: boo
     return one_way * (4 if backward else 2)
 
 
+def weight_bytes(d_model: int, d_ffn: int, act: str, experts_per_gpu: int, backward: bool = True, elem: int = 2) -> float:
+    """HBM traffic of the expert weights alone: read once in forward; in backward read again (dgrad) and the weight
+    gradients written once. With few tokens per expert this, not the FLOPs, bounds the layer."""
+    mats = 3 if act == "swiglu" else 2
+    w = experts_per_gpu * mats * d_model * d_ffn * elem
+    return w * (3 if backward else 1)
+
+
 def roofline(tokens, d_model, d_ffn, top_k, act, gpus, backward=True, kept_fraction=1.0, peak_tflops=None,
-             nvlink_gbs=NVLINK_GBS):
+             nvlink_gbs=NVLINK_GBS, experts_per_gpu=0, hbm_gbs=None):
     if peak_tflops is None:
-        peak_tflops, _, src = measured_peaks()
+        peak_tflops, hbm_meas, src = measured_peaks()
     else:
-        src = "given"
+        hbm_meas, src = 6557.0, "given"
+    hbm_gbs = hbm_gbs or hbm_meas
     fl = layer_flops(tokens, d_model, d_ffn, top_k, act, backward, kept_fraction)
     by = nvlink_bytes(tokens, d_model, top_k, gpus, backward, kept_fraction=kept_fraction)
     t_compute = fl / (peak_tflops * 1e9)            # ms
     t_link = by / (nvlink_gbs * 1e6)                # ms
-    return {"flops": fl, "nvlink_bytes": by, "compute_ms": t_compute, "link_ms": t_link,
-            "target_ms": max(t_compute, t_link), "bound": "compute" if t_compute >= t_link else "nvlink",
-            "peak_source": src, "peak_tflops": peak_tflops}
+    t_hbm = weight_bytes(d_model, d_ffn, act, experts_per_gpu, backward) / (hbm_gbs * 1e6) if experts_per_gpu else 0.0
+    terms = {"compute": t_compute, "nvlink": t_link, "hbm_weights": t_hbm}
+    bound = max(terms, key=terms.get)
+    return {"flops": fl, "nvlink_bytes": by, "compute_ms": t_compute, "link_ms": t_link, "hbm_weights_ms": t_hbm,
+            "target_ms": terms[bound], "bound": bound, "peak_source": src, "peak_tflops": peak_tflops}
 
 
 def main():
@@ -59,8 +70,10 @@ def main():
     ap.add_argument("--forward-only", action="store_true")
     ap.add_argument("--kept-fraction", type=float, default=1.0)
     ap.add_argument("--measured-ms", type=float, default=0.0)
+    ap.add_argument("--experts-per-gpu", type=int, default=0, help="include the HBM traffic of this many experts' weights")
     a = ap.parse_args()
-    r = roofline(a.tokens, a.d_model, a.d_ffn, a.top_k, a.act, a.gpus, not a.forward_only, a.kept_fraction)
+    r = roofline(a.tokens, a.d_model, a.d_ffn, a.top_k, a.act, a.gpus, not a.forward_only, a.kept_fraction,
+                 experts_per_gpu=a.experts_per_gpu)
     if a.measured_ms > 0:
         r["measured_ms"] = a.measured_ms
         r["fraction_of_roofline"] = round(r["target_ms"] / a.measured_ms, 3)

@@ -40,5 +40,6 @@ def test_roofline_numbers_for_the_large_layer():
     assert abs(by / 1e6 - 4 * 268.4 * 7 / 8) < 1.0
     r = roofline(16384, 4096, 14336, 2, "swiglu", 8, peak_tflops=1675.7)
     assert r["bound"] == "compute" and abs(r["target_ms"] - 20.7) < 0.1
-    small = roofline(128, 4096, 14336, 2, "swiglu", 8, backward=False, peak_tflops=1675.7)
-    assert small["target_ms"] < 0.06 and small["bound"] == "compute"
+    small = roofline(128, 4096, 14336, 2, "swiglu", 8, backward=False, peak_tflops=1675.7, experts_per_gpu=1, hbm_gbs=6557.0)
+    # one expert's weights are 352 MB: reading them (54 us) costs as much as the 256 routed rows' FLOPs
+    assert abs(small["hbm_weights_ms"] - 0.0537) < 0.001 and small["target_ms"] < 0.06

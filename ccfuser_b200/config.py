@@ -38,6 +38,9 @@ class MoEConfig:
     max_tokens           upper bound of tokens per rank per call; sizes the symmetric buffers
     recv_factor          without a capacity factor the receive buffer of a rank is sized
                          recv_factor x the balanced load (overflow is reported, not silent)
+    shadow_experts       >0: the n most popular experts of every step are replicated to all ranks for that step
+                         (weights broadcast, gradients reduced back to the owner) and their tokens are computed
+                         where they are; see parallel/shadow.py
     """
 
     d_model: int
@@ -53,6 +56,7 @@ class MoEConfig:
     max_tokens: int = 4096
     recv_factor: float = 2.0
     router_bias: bool = True
+    shadow_experts: int = 0
 
     def __post_init__(self):
         if self.activation not in ACTIVATIONS:
@@ -63,6 +67,8 @@ class MoEConfig:
             raise ValueError("num_experts must be divisible by ep_size")
         if not (1 <= self.top_k <= self.num_experts):
             raise ValueError("top_k must be in [1, num_experts]")
+        if not (0 <= self.shadow_experts <= self.num_experts):
+            raise ValueError("shadow_experts must be in [0, num_experts]")
 
     @property
     def experts_per_rank(self) -> int:

@@ -19,6 +19,8 @@ from .config import MoEConfig
 from .experts import Experts, scan_expert_params
 from .gates import NaiveGate
 from .parallel.a2a import moe_forward_a2a
+from .parallel.placement import plan_placement, rebalance_experts
+from .parallel.shadow import gather_shadow_params, select_popular, shadow_forward, split_shadow_slots
 
 
 class MoELayer(nn.Module):
@@ -70,15 +72,49 @@ class MoELayer(nn.Module):
         shape = inp.shape
         x = inp.reshape(-1, cfg.d_model)
         backend = self.backend(x)
+        group = self.ep_group if cfg.ep_size > 1 else None
         if backend == "fused":
-            y = self._fused_impl()(x)
+            fused = self._fused_impl()
+            x = x.contiguous()
+            idx, score = fused.route(x)
         else:
             idx, score = self.gate(x)
+        y_shadow = None
+        if cfg.shadow_experts > 0:
+            # the step's most popular experts are replicated: their slots leave the expert-parallel path
+            shadow_ids = select_popular(idx, cfg.num_experts, cfg.shadow_experts, group)
+            params = gather_shadow_params(self.experts, shadow_ids, self.ep_rank, group)
+            idx, which = split_shadow_slots(idx, shadow_ids)
+            y_shadow = shadow_forward(x, which, score, params, cfg.activation)
+            self.last_stats["shadow_ids"] = shadow_ids
+        if backend == "fused":
+            y = fused.run_experts(x, idx, score)
+        else:
             y = moe_forward_a2a(x, idx, score, self.experts, num_experts=cfg.num_experts,
-                                capacity=cfg.capacity(x.shape[0]),
-                                group=self.ep_group if cfg.ep_size > 1 else None)
+                                capacity=cfg.capacity(x.shape[0]), group=group, stats=self.last_stats)
             y = y.to(inp.dtype)
+        if y_shadow is not None:
+            y = y + y_shadow.to(y.dtype)
         return y.reshape(shape[:-1] + (y.shape[-1],))
+
+    # ---- placement ---------------------------------------------------------------------------
+    def count_table(self) -> Optional[torch.Tensor]:
+        """``[source rank, expert]`` kept rows of the last forward call (identical on every rank), or None before the
+        first call. Reading it on the host synchronises; meant for the occasional placement decision."""
+        if self._fused is not None:
+            return self._fused.routing_stats()["count_table"]
+        return self.last_stats.get("count_table")
+
+    def rebalance(self, placement=None, optimizer=None, topology=None, slack: float = 0.05):
+        """Move experts between ranks (collective over the expert-parallel group). With ``placement=None`` a placement
+        is planned from the counts of the last forward call; see parallel/placement.py. Returns the placement used."""
+        if placement is None:
+            table = self.count_table()
+            if table is None:
+                raise RuntimeError("no routing counts yet: run a forward pass first or pass a placement")
+            placement = plan_placement(table, self.config.experts_per_rank, topology, slack)
+        rebalance_experts(self, placement, optimizer)
+        return list(placement)
 
     def routing_stats(self):
         """Statistics of the last fused forward call as device tensors (see FusedMoE.routing_stats)."""

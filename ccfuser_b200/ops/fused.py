@@ -198,10 +198,16 @@ class FusedMoE:
 
     # ------------------------------------------------------------------------------------------
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        x = x.contiguous()
+        idx, w = self.route(x)
+        return self.run_experts(x, idx, w)
+
+    def route(self, x: torch.Tensor):
+        """Router logits -> (idx [T, k] int32, weights [T, k] fp32) with the top-k softmax kernel; also sets the gate's
+        auxiliary loss."""
         cfg, layer = self.cfg, self.layer
         if x.shape[0] > cfg.max_tokens:
             raise ValueError(f"{x.shape[0]} tokens exceed config.max_tokens={cfg.max_tokens}")
-        x = x.contiguous()
         logits = layer.gate.logits(x) if hasattr(layer.gate, "logits") else None
         if logits is None:
             raise TypeError("the fused backend needs a gate with a .logits(x) method (NaiveGate)")
@@ -216,6 +222,13 @@ class FusedMoE:
             layer.gate.set_loss(coef * cfg.num_experts * (frac / max(1, idx.numel()) * probs.mean(0)).sum())
         elif hasattr(layer.gate, "set_loss"):
             layer.gate.set_loss(None)
+        return idx, w
+
+    def run_experts(self, x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """The expert-parallel part for given routing decisions. A slot whose expert id is negative is not routed
+        (the routing kernels drop it, its gate weight gets a zero gradient from here)."""
+        cfg, layer = self.cfg, self.layer
+        x = x.contiguous()
         ex = layer.experts
         wg = ex.htoh4_gate.weight if cfg.activation == "swiglu" else None
         bg = ex.htoh4_gate.bias if cfg.activation == "swiglu" else None

@@ -7,9 +7,11 @@ same tokens:
 * the position of a slot inside its expert is the number of earlier slots of the same rank that
   chose the same expert (a prefix count, so it is deterministic, unlike the ``atomicSub`` placement
   of the reference at mix_moe/csrc/cuda/local_exchange.cu:6-17);
-* a slot is kept iff its position is below the per-(rank, expert) capacity.
+* a slot is kept iff its position is below the per-(rank, expert) capacity;
+* a slot whose expert id is negative is not routed at all (it is dropped and counted nowhere), the ``-1 = dropped``
+  convention of mix_moe/csrc/cuda/local_exchange.cu:37-70.
 
-The torch implementation below runs on CPU and GPU; the CUDA kernels in csrc/routing.cu compute the
+The torch implementation below runs on CPU and GPU; the CUDA kernels in csrc/moe_kernels.cu (route_hist_kernel, route_pos_kernel) compute the
 same quantities without a host round trip and are tested bit-exactly against it.
 """
 from __future__ import annotations
@@ -44,11 +46,14 @@ def positions_in_expert(expert: torch.Tensor, num_experts: int) -> torch.Tensor:
 
 
 def route_local(topk_idx: torch.Tensor, num_experts: int, capacity: int) -> LocalRouting:
-    """topk_idx: [T, k] integer expert ids -> plan of this rank's slots."""
+    """topk_idx: [T, k] integer expert ids (negative = not routed) -> plan of this rank's slots."""
     expert = topk_idx.reshape(-1).to(torch.int64)
-    pos = positions_in_expert(expert, num_experts)
-    keep = pos < capacity
-    raw = torch.bincount(expert, minlength=num_experts)
+    valid = (expert >= 0) & (expert < num_experts)
+    # unrouted slots are counted in an extra bin so that they never shift the position of a routed slot
+    binned = torch.where(valid, expert, torch.full_like(expert, num_experts))
+    pos = positions_in_expert(binned, num_experts + 1)
+    keep = valid & (pos < capacity)
+    raw = torch.bincount(binned, minlength=num_experts + 1)[:num_experts]
     count = torch.clamp(raw, max=capacity)
     return LocalRouting(expert, pos, keep, count, raw)
 

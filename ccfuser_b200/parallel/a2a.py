@@ -77,8 +77,10 @@ def _experts_grouped_mm(rows: torch.Tensor, per_expert: List[int], experts) -> t
 
 
 def moe_forward_a2a(x: torch.Tensor, topk_idx: torch.Tensor, topk_score: torch.Tensor, experts,
-                    *, num_experts: int, capacity: int, group, grouped_mm: bool = False) -> torch.Tensor:
-    """x [T,d]; topk_idx/topk_score [T,k]. Differentiable w.r.t. x, topk_score and the expert params."""
+                    *, num_experts: int, capacity: int, group, grouped_mm: bool = False,
+                    stats: Optional[dict] = None) -> torch.Tensor:
+    """x [T,d]; topk_idx/topk_score [T,k] (a negative expert id = slot not routed). Differentiable w.r.t. x,
+    topk_score and the expert params. ``stats`` (optional dict) receives the ``[rank, expert]`` count table."""
     world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
     e_loc = num_experts // world
     t, d = x.shape
@@ -89,6 +91,8 @@ def moe_forward_a2a(x: torch.Tensor, topk_idx: torch.Tensor, topk_score: torch.T
     order = kept[torch.sort(plan.expert[kept], stable=True).indices]
     send_rows = x[order // k]                                       # [S_kept, d]
     table = exchange_counts(plan.count, world, group)               # [W, E]
+    if stats is not None:
+        stats["count_table"] = table
     # rows I send to owner o / rows I receive from source r (per local expert)
     send_per_rank = plan.count.view(world, e_loc).sum(1).tolist()
     me = dist.get_rank(group) if world > 1 else 0

@@ -1,0 +1,118 @@
+"""Shadow (replicated) experts for skewed routing: the most popular experts of a step are computed on every rank for
+that rank's own tokens instead of drawing all of their tokens to one owner.
+
+The reference reserves three extra expert slots per rank for this (``popular_expert_num = 3``,
+mix_moe/mix_moe/transformer.py:449,453) and picks the global top-3 experts of every step
+(``select_popular_expert``, transformer.py:365-374; used at transformer.py:160-171), but the extra slots are
+independent parameters: they are never filled from the owner's weights and their gradients are never returned, so
+the feature only works as a timing experiment. Here the replicas are real:
+
+* selection: the per-expert slot counts of all ranks are summed (one small all-reduce) and the ``n`` largest win,
+  ties towards the lower id, so every rank selects the same experts without a host round trip;
+* weights: every rank contributes the selected experts it owns (zeros otherwise) to a sum all-reduce, which is a
+  broadcast from each owner that needs no host-side knowledge of who owns what;
+* gradients: the all-reduce is an autograd function whose backward is again a sum all-reduce, so the owner's
+  parameter receives the sum of the replicas' gradients and the parameters stay single-copy;
+* the selected experts' slots are taken out of the expert-parallel path (expert id -1 = not routed) and computed
+  locally with library GEMMs; they are not subject to the capacity factor, since they draw on no shared buffer.
+
+Cost model: replicating one expert moves its weights once per step (forward) and its gradients once (backward),
+``2 x 3 x d_model x d_ffn x 2`` bytes for SwiGLU in bf16, instead of its tokens twice in each direction; it pays
+when one expert draws more than about ``1.5 x d_ffn`` tokens per rank, i.e. under heavy skew only. Off by default
+(``MoEConfig.shadow_experts = 0``).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops.reference import expert_ffn
+
+
+class _AllReduceSum(torch.autograd.Function):
+    """y = sum over the group of x; dx = sum over the group of dy."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        y = x.contiguous().clone()
+        if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        if ctx.group is not None and dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+            dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+def all_reduce_sum(x: torch.Tensor, group) -> torch.Tensor:
+    return _AllReduceSum.apply(x, group)
+
+
+def select_popular(topk_idx: torch.Tensor, num_experts: int, n: int, group) -> torch.Tensor:
+    """Ids [n] (int64, ascending popularity order is not guaranteed, the set is what matters) of the ``n`` experts
+    that received the most slots over all ranks in this step. Same result on every rank, no host synchronisation."""
+    flat = topk_idx.reshape(-1).to(torch.int64)
+    valid = (flat >= 0) & (flat < num_experts)
+    counts = torch.zeros(num_experts + 1, dtype=torch.float32, device=flat.device)
+    counts.scatter_add_(0, torch.where(valid, flat, torch.full_like(flat, num_experts)),
+                        torch.ones(flat.numel(), dtype=torch.float32, device=flat.device))
+    counts = counts[:num_experts].contiguous()
+    if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(counts, group=group)
+    # stable descending sort: equal counts resolve to the lower expert id on every rank
+    order = torch.sort(counts, descending=True, stable=True).indices
+    return order[:n]
+
+
+def gather_shadow_params(experts, shadow_ids: torch.Tensor, rank: int, group) -> Dict[str, Optional[torch.Tensor]]:
+    """Stacked parameters ``[n, ...]`` of the selected experts, identical on every rank and differentiable: the
+    gradient of a replica flows back to the owner's parameter through the all-reduce."""
+    e_loc = experts.htoh4.num_expert
+    local = shadow_ids - rank * e_loc
+    mine = (local >= 0) & (local < e_loc)
+    pick = local.clamp(0, e_loc - 1)
+    out: Dict[str, Optional[torch.Tensor]] = {}
+    for name in ("htoh4", "htoh4_gate", "h4toh"):
+        lin = getattr(experts, name, None)
+        for part in ("weight", "bias"):
+            p = getattr(lin, part, None) if lin is not None else None
+            if p is None:
+                out[f"{name}.{part}"] = None
+                continue
+            sel = p[pick]
+            mask = mine.view(-1, *([1] * (sel.dim() - 1))).to(sel.dtype)
+            out[f"{name}.{part}"] = all_reduce_sum(sel * mask, group)
+    return out
+
+
+def split_shadow_slots(topk_idx: torch.Tensor, shadow_ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """-> (idx for the expert-parallel path with the shadowed slots set to -1, shadow index [T, k] in 0..n-1 or -1)."""
+    hit = topk_idx.unsqueeze(-1) == shadow_ids.to(topk_idx.dtype).view(1, 1, -1)          # [T, k, n]
+    is_shadow = hit.any(-1)
+    which = torch.where(is_shadow, hit.to(torch.int64).argmax(-1), torch.full_like(is_shadow, -1, dtype=torch.int64))
+    main_idx = torch.where(is_shadow, torch.full_like(topk_idx, -1), topk_idx)
+    return main_idx, which
+
+
+def shadow_forward(x: torch.Tensor, which: torch.Tensor, score: torch.Tensor, params: Dict[str, Optional[torch.Tensor]],
+                   activation: str) -> torch.Tensor:
+    """Sum over this rank's shadowed slots of score * FFN_replica(x). x [T, d]; which, score [T, k]."""
+    n = params["htoh4.weight"].shape[0]
+    d_out = params["h4toh.weight"].shape[1]
+    y = torch.zeros(x.shape[0], d_out, dtype=x.dtype, device=x.device)
+    for j in range(n):
+        tok, slot = (which == j).nonzero(as_tuple=True)
+        # a replica without tokens still runs (on zero rows): every rank then builds the same graph and so issues the
+        # gradient all-reduces of the backward pass in the same order
+        opt = lambda key: None if params[key] is None else params[key][j]  # noqa: E731
+        o = expert_ffn(x[tok], params["htoh4.weight"][j], opt("htoh4.bias"), params["h4toh.weight"][j], opt("h4toh.bias"),
+                       activation, opt("htoh4_gate.weight") if activation == "swiglu" else None,
+                       opt("htoh4_gate.bias") if activation == "swiglu" else None)
+        y = y.index_add(0, tok, o * score[tok, slot].to(o.dtype).unsqueeze(1))
+    return y

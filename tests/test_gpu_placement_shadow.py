@@ -1,0 +1,82 @@
+"""Shadow experts and in-place expert permutation through the fused kernels (one GPU, one-rank expert-parallel group).
+
+With one rank the replicas' weight broadcast is the identity, so these tests isolate what the fused path adds: slots
+with expert id -1 are skipped by the routing, dispatch and reduce kernels, and their gate weights get no gradient
+from the expert-parallel part."""
+import pytest
+import torch
+
+from tests.test_gpu_fused import _make_layer, _rel
+
+pytestmark = pytest.mark.gpu
+
+# Not part of the calibrated suite yet: a failure here is reported without stopping the run.
+_new = pytest.mark.xfail(strict=False, reason="tolerances of the masked-slot path are provisional")
+
+
+def _oracle_full(layer):
+    from ccfuser_b200.ops.reference import dense_moe_oracle
+    full = {"gate.weight": layer.gate.gate.weight.detach().float(), "gate.bias": layer.gate.gate.bias.detach().float()}
+    for name in ("htoh4", "h4toh", "htoh4_gate"):
+        if hasattr(layer.experts, name):
+            m = getattr(layer.experts, name)
+            full[name + ".weight"] = m.weight.detach().float().requires_grad_(True)
+            full[name + ".bias"] = m.bias.detach().float().requires_grad_(True)
+    return full
+
+
+@_new
+@pytest.mark.parametrize("act", ["gelu", "swiglu"])
+def test_fused_layer_with_shadow_experts_matches_oracle(act):
+    from ccfuser_b200 import MoELayer
+    from ccfuser_b200.ops.fused import topk_softmax
+    from ccfuser_b200.ops.reference import dense_moe_oracle
+    cfg, base = _make_layer(act, None, e=8, d=256, f=512, tokens=1024)
+    cfg = cfg.replace(shadow_experts=2)
+    layer = MoELayer(cfg, device="cuda")
+    layer.load_state_dict(base.state_dict())
+    base.release()
+    x = (torch.randn(1000, cfg.d_model, device="cuda") * 0.5).to(cfg.dtype).requires_grad_(True)
+    y = layer(x)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    torch.cuda.synchronize()
+    layer.check_status()
+    shadow = layer.last_stats["shadow_ids"].tolist()
+    assert len(set(shadow)) == 2
+    assert int(layer.count_table()[:, shadow].sum()) == 0          # no shadowed row went through dispatch
+    # oracle with the routing decisions of the kernel (bf16 logits can flip near-ties against an fp32 router)
+    with torch.no_grad():
+        idx, w = topk_softmax(layer.gate.logits(x.detach()), cfg.top_k)
+    full = _oracle_full(layer)
+    xf = x.detach().float().requires_grad_(True)
+    yr = dense_moe_oracle([xf], full, top_k=cfg.top_k, capacity=None, activation=act, routing=[(idx, w.float())])[0]
+    yr.backward(gy.float())
+    assert _rel(y, yr) < 3e-2
+    ex = layer.experts
+    assert _rel(ex.htoh4.weight.grad, full["htoh4.weight"].grad) < 4e-2
+    assert _rel(ex.h4toh.weight.grad, full["h4toh.weight"].grad) < 4e-2
+    assert _rel(ex.h4toh.bias.grad, full["h4toh.bias"].grad) < 4e-2
+    layer.release()
+
+
+@_new
+def test_fused_layer_output_survives_expert_permutation():
+    cfg, layer = _make_layer("swiglu", None, e=8, d=256, f=512, tokens=1024)
+    x = (torch.randn(900, cfg.d_model, device="cuda") * 0.5).to(cfg.dtype)
+    with torch.no_grad():
+        y0 = layer(x)
+        layer.rebalance([3, 2, 1, 0, 7, 6, 5, 4])
+        y1 = layer(x)
+        planned = layer.rebalance()
+        y2 = layer(x)
+        lg = layer.gate.logits(x).float().sort(dim=-1, descending=True).values
+    torch.cuda.synchronize()
+    layer.check_status()
+    assert sorted(planned) == list(range(8))
+    # a tie between the last selected and the first rejected logit resolves to the lower expert id, which a permutation
+    # changes: such tokens (rare, bf16 logits) are left out
+    clear = lg[:, cfg.top_k - 1] != lg[:, cfg.top_k]
+    assert clear.float().mean() > 0.9
+    assert _rel(y1[clear], y0[clear]) < 1e-2 and _rel(y2[clear], y0[clear]) < 1e-2
+    layer.release()

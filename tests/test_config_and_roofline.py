@@ -43,3 +43,23 @@ def test_roofline_numbers_for_the_large_layer():
     small = roofline(128, 4096, 14336, 2, "swiglu", 8, backward=False, peak_tflops=1675.7, experts_per_gpu=1, hbm_gbs=6557.0)
     # one expert's weights are 352 MB: reading them (54 us) costs as much as the 256 routed rows' FLOPs
     assert abs(small["hbm_weights_ms"] - 0.0537) < 0.001 and small["target_ms"] < 0.06
+
+
+def test_plot_tool_writes_wellformed_svg(tmp_path):
+    """The figure tool reads the experiment CSVs (its own and the reference's recorded format with a partial
+    num_expert column) and writes parseable SVG."""
+    import xml.etree.ElementTree as ET
+    from ccfuser_b200.bench import plot
+    d = tmp_path / "data"
+    d.mkdir()
+    (d / "moe_layer_t.csv").write_text("name,num_expert,total_time,forward_time,backward_time\\n\n"
+                                       "a,4,2.0,1.0,1.0\na,8,2.5,1.2,1.3\nb,4,9.0,4.0,5.0\nb,8,9.5,4.5,5.0\n")
+    (d / "e2e_model_t.csv").write_text("name,MOE-GPT,MOE-BERT\nnaive,10,20\nfused,12,25\n")
+    (d / "kernel_eval_expert_t.csv").write_text(
+        "kernel, locality, time, all2all, num_expert\nAG, 0.25, 0.2, 0 \nAll2All-GEMM, 0.25, 0.5, 0.1\n"
+        "GA, 0.25, 0.2, 0 \nGEMM-All2All, 0.25, 0.4, 0.1, 2\n")
+    made = plot.main(["--data", str(d), "--out", str(tmp_path / "fig")])
+    assert len(made) == 3 + 1 + 2
+    for p in made:
+        root = ET.parse(p).getroot()
+        assert root.tag.endswith("svg") and len(list(root.iter())) > 20

@@ -413,7 +413,7 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D row-major view [rows, cols] of 2-byte elements, box = {box_cols, box_rows}, 128-byte swizzle
-static int make_tmap(CUtensorMap* m, const void* base, long long rows, long long cols, int box_cols, int box_rows,
+int make_tmap(CUtensorMap* m, const void* base, long long rows, long long cols, int box_cols, int box_rows,
                      int fp16) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;

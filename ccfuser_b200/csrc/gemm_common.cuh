@@ -18,6 +18,10 @@ constexpr int kTmemCols = 512;
 constexpr int MAJ_K = 0, MAJ_MN = 1;
 constexpr int kEpiStageBytes = 2048;  // per epilogue warp: 32 rows x 64 bytes, XOR-swizzled
 
+// Host: tensor map of a 2-D row-major view [rows, cols] of 2-byte elements with box {box_cols, box_rows} and 128-byte
+// swizzle (defined in gemm.cu). Returns 0 or a negative error code.
+int make_tmap(CUtensorMap* m, const void* base, long long rows, long long cols, int box_cols, int box_rows, int fp16);
+
 struct Tile {
   int g;           // group (expert)
   int row0;        // row-grouped: first A/C row; k-grouped: first output row inside the group (m0)

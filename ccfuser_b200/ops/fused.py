@@ -37,6 +37,7 @@ from ..config import env_flag
 from ..parallel.symm import SymmBuffer
 from ..utils.tracing import nvtx_range
 from . import gemm as G
+from . import router as R
 
 TILE = 128
 
@@ -195,6 +196,7 @@ class FusedMoE:
         self.sent_rows = torch.zeros(N.MAX_RANKS, **i32)
         self.table_copy = torch.zeros(self.world, cfg.num_experts, **i32)
         self.check_every_call = bool(env_flag("CHECK_STATUS", 0))
+        self.fused_router = bool(env_flag("FUSED_ROUTER", 0))
 
     # ------------------------------------------------------------------------------------------
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
@@ -208,11 +210,18 @@ class FusedMoE:
         cfg, layer = self.cfg, self.layer
         if x.shape[0] > cfg.max_tokens:
             raise ValueError(f"{x.shape[0]} tokens exceed config.max_tokens={cfg.max_tokens}")
+        coef = getattr(layer.gate, "aux_loss_coef", 0.0)
+        lin = getattr(layer.gate, "gate", None)
+        if (self.fused_router and not (coef and coef > 0) and isinstance(lin, torch.nn.Linear)
+                and R.supported(x, lin.weight, cfg.top_k)):
+            # linear layer + top-k + softmax in one kernel; the logits are never written
+            if hasattr(layer.gate, "set_loss"):
+                layer.gate.set_loss(None)
+            return R.fused_router(x, lin.weight, lin.bias, cfg.top_k)
         logits = layer.gate.logits(x) if hasattr(layer.gate, "logits") else None
         if logits is None:
             raise TypeError("the fused backend needs a gate with a .logits(x) method (NaiveGate)")
         idx, w = topk_softmax(logits, cfg.top_k)
-        coef = getattr(layer.gate, "aux_loss_coef", 0.0)
         if coef and coef > 0 and hasattr(layer.gate, "set_loss"):
             # load-balance auxiliary loss, same definition as NaiveGate.forward (fraction of slots per expert times the
             # mean router probability), kept in torch: it is a [T, E] reduction next to GEMMs that dominate the layer

@@ -41,6 +41,10 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
     gy = torch.randn(tokens, args.d_model, device="cuda", dtype=dtype, generator=g)
     flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     fwd, bwd = [], []
+    graphed = None
+    if args.graph and args.forward_only and backend == "fused":
+        from ..ops.fused import GraphedForward
+        graphed = GraphedForward(layer, tokens)
     for it in range(args.warmup + args.iters):
         for p in layer.parameters():
             p.grad = None
@@ -51,7 +55,11 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
         torch.cuda.synchronize()
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record()
-        if args.forward_only:
+        if graphed is not None:
+            y = graphed(x)
+            e1.record()
+            e2.record()
+        elif args.forward_only:
             with torch.no_grad():
                 y = layer(x)
             e1.record()
@@ -96,7 +104,7 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
     roof_ms = max(flops / (peak * 1e9), nv_bytes / (NVLINK_GBS * 1e6))
     out = {"bench": "moe_layer", "backend": backend, "n_gpus": world, "tokens_per_gpu": tokens, "d_model": args.d_model,
            "d_ffn": args.d_ffn, "experts_per_gpu": experts_per_gpu, "top_k": args.top_k, "act": args.act, "cf": args.cf,
-           "zipf": args.zipf, "dtype": args.dtype, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
+           "zipf": args.zipf, "dtype": args.dtype, "cuda_graph": graphed is not None, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
            "total_ms": round(total_ms, 4), "tflops_per_gpu": round(flops / total_ms / 1e9, 1),
            "roofline_frac_of_" + src: round(roof_ms / total_ms, 3), **stats}
     layer.release()
@@ -121,6 +129,7 @@ def main():
     ap.add_argument("--zipf-scale", type=float, default=1.0)
     ap.add_argument("--backends", default="fused", help="comma list of fused,nccl")
     ap.add_argument("--forward-only", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="with --forward-only: replay the fused forward from a CUDA graph")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default="")

@@ -194,7 +194,7 @@ struct PlanArgs {
   int world, my_rank, e_total, e_loc, epoch, max_rows;
 };
 
-__global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanArgs a) {
+__device__ __forceinline__ void plan_body(const PlanArgs& a, const int epoch) {
   __shared__ int rows[CCF_MAX_GROUPS];
   __shared__ int myoff[CCF_MAX_GROUPS];
   __shared__ int base[CCF_MAX_GROUPS];
@@ -208,10 +208,10 @@ __global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanA
   }
   __threadfence_system();
   __syncthreads();
-  if (tid < a.world) st_release_sys(a.peer_flag[tid] + a.my_rank, a.epoch);
+  if (tid < a.world) st_release_sys(a.peer_flag[tid] + a.my_rank, epoch);
   // 2. wait for everyone's counts (my own table, local memory)
   if (tid < a.world) {
-    if (!wait_flag_ge(a.peer_flag[a.my_rank] + tid, a.epoch, fail_fast_limit(a.status, a.wait_limit_ns))) {
+    if (!wait_flag_ge(a.peer_flag[a.my_rank] + tid, epoch, fail_fast_limit(a.status, a.wait_limit_ns))) {
       report_status(a.status, CCF_ERR_FLAG_TIMEOUT, 0x800000 | tid);
       failed = 1;
     }
@@ -266,6 +266,20 @@ __global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanA
       a.local_rows[i] = max(0, min(a.count_kept[e], a.max_rows - (base[e] + myoff[e])));
     }
   }
+}
+
+__global__ void __launch_bounds__(256) plan_kernel(const __grid_constant__ PlanArgs a) { plan_body(a, a.epoch); }
+
+// Same, with the call's epoch taken from a counter in device memory (previous value + 1, written back at the end)
+// instead of a launch argument: a captured CUDA graph replays with fixed arguments, so a host-side epoch would
+// repeat and the wait for the peers' counts would be satisfied by the previous call's flags.
+__global__ void __launch_bounds__(256) plan_kernel_dev_epoch(const __grid_constant__ PlanArgs a, int* epoch_counter) {
+  __shared__ int epoch;
+  if (threadIdx.x == 0) epoch = *epoch_counter + 1;
+  __syncthreads();
+  plan_body(a, epoch);
+  __syncthreads();
+  if (threadIdx.x == 0) *epoch_counter = epoch;
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -472,6 +486,13 @@ int ccf_sizeof_plan_args() { return static_cast<int>(sizeof(ccf::PlanArgs)); }
 int ccf_plan(const ccf::PlanArgs* a, void* stream) {
   if (a->e_total > CCF_MAX_GROUPS || a->world > CCF_MAX_RANKS) return -2;
   ccf::plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
+  return last_err();
+}
+
+// epoch_counter: one int in device memory, equal on every rank of the group, advanced by one per call
+int ccf_plan_dev_epoch(const ccf::PlanArgs* a, int* epoch_counter, void* stream) {
+  if (a->e_total > CCF_MAX_GROUPS || a->world > CCF_MAX_RANKS || epoch_counter == nullptr) return -2;
+  ccf::plan_kernel_dev_epoch<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a, epoch_counter);
   return last_err();
 }
 

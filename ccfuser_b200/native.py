@@ -138,6 +138,7 @@ def _declare(lib):
         "ccf_route": ([p, i, i, i, p, p, p, p, p, p, p], i),
         "ccf_route_ordered": ([p, i, i, i, p, p, p, p, p, p, p, p, p, i, p], i),
         "ccf_plan": ([C.POINTER(PlanArgs), p], i),
+        "ccf_plan_dev_epoch": ([C.POINTER(PlanArgs), p, p], i),
         "ccf_dispatch": ([C.POINTER(DispatchArgs), p, p, i, p], i),
         "ccf_combine_wait": ([p, p, p, i, i, ull, p, p], i),
         "ccf_combine_reduce": ([p, p, p, i, i, i, i, p], i),

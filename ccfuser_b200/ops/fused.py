@@ -80,6 +80,11 @@ class CommContext:
         self.done = v(self.off["done"], (N.MAX_RANKS,), torch.int32)
         self.done_cum = torch.zeros(N.MAX_RANKS, dtype=torch.int32, device=device)
         self.epoch = 0
+        # The epoch can also live on the device (advanced by the plan kernel itself): needed when calls are replayed
+        # from a CUDA graph, whose launch arguments are frozen. Switched on by GraphedForward or CCFUSER_DEVICE_EPOCH=1;
+        # every rank of the group must switch at the same call.
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=device)
+        self.device_epoch = bool(env_flag("DEVICE_EPOCH", 0))
         self.ws = G.Workspace.get(device)
         # scratch of the routing kernels
         s_max = max_slots
@@ -103,6 +108,12 @@ class CommContext:
 
     def peer(self, name: str):
         return self.buf.peer_ptrs(self.off[name])
+
+    def use_device_epoch(self):
+        """Move the call epoch into device memory (collective in effect: all ranks of the group at the same call)."""
+        if not self.device_epoch:
+            self.epoch_dev.fill_(self.epoch)
+            self.device_epoch = True
 
     def check_status(self, what="fused MoE"):
         self.ws.check(what)
@@ -313,7 +324,8 @@ class FusedMoE:
                                       self.count_raw.data_ptr(), self.count_kept.data_ptr(), cc.ticket.data_ptr(),
                                       self.order_off.data_ptr(), self.sorted_slot.data_ptr(), self.slot_row.data_ptr(),
                                       self.rank * e_loc, st), "ccf_route_ordered")
-        cc.epoch += 1
+        if not cc.device_epoch:
+            cc.epoch += 1
         p = N.PlanArgs()
         p.count_kept = self.count_kept.data_ptr()
         tb, fl = cc.peer("cnt_table"), cc.peer("cnt_flag")
@@ -324,7 +336,10 @@ class FusedMoE:
         p.local_begin, p.local_rows = self.local_begin.data_ptr(), self.local_rows.data_ptr()
         p.wait_limit_ns = cc.wait_ns
         p.world, p.my_rank, p.e_total, p.e_loc, p.epoch, p.max_rows = self.world, self.rank, e_tot, e_loc, cc.epoch, self.max_rows
-        N.check(lib.ccf_plan(C.byref(p), st), "ccf_plan")
+        if cc.device_epoch:
+            N.check(lib.ccf_plan_dev_epoch(C.byref(p), cc.epoch_dev.data_ptr(), st), "ccf_plan_dev_epoch")
+        else:
+            N.check(lib.ccf_plan(C.byref(p), st), "ccf_plan")
         N.count(3)  # route (2 kernels) + plan
 
     def stage_dispatch_gemm1(self, x, idx, gate_w, w1, b1, wg=None, bg=None, trace=None):
@@ -359,6 +374,42 @@ class FusedMoE:
     def stage_reduce(self, tokens: int, out: torch.Tensor):
         """Wait until every owner has delivered this rank's rows, then sum the k slots of each token."""
         self._wait_and_reduce(self.comb, tokens, G.combine_units(self.cfg.d_model), out)
+
+
+class GraphedForward:
+    """Inference forward of one fused MoE layer replayed from a CUDA graph: for the latency-bound regime (a few
+    hundred tokens per GPU) where ten kernel launches and their host code cost more than the kernels.
+
+        g = GraphedForward(layer, tokens=128)     # every rank of the group, same point of the program
+        y = g(x)                                  # x [tokens, d_model]; y is a buffer that the next call overwrites
+
+    The graph holds the router, routing, plan, both fused GEMMs and the reduce of one call with a fixed token count;
+    the cross-GPU protocol is unchanged (flags and counters live in device memory; the plan's epoch moves there too,
+    see CommContext.use_device_epoch). Replays are collective like eager calls. Status words are not checked inside the
+    graph: call ``layer.check_status()`` when convenient."""
+
+    def __init__(self, layer, tokens: int, warmup: int = 3):
+        fm = layer._fused_impl()
+        cfg = layer.config
+        if tokens > cfg.max_tokens:
+            raise ValueError(f"{tokens} tokens exceed config.max_tokens={cfg.max_tokens}")
+        fm.ctx.use_device_epoch()
+        self.layer = layer
+        self.x = torch.zeros(tokens, cfg.d_model, dtype=cfg.dtype, device=fm.device)
+        side = torch.cuda.Stream(device=fm.device)
+        side.wait_stream(torch.cuda.current_stream(fm.device))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(max(1, warmup)):           # first-use set-up (attributes, driver entry points) outside capture
+                layer(self.x)
+        torch.cuda.current_stream(fm.device).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.y = layer(self.x)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        self.x.copy_(x.reshape(self.x.shape))
+        self.graph.replay()
+        return self.y
 
 
 class _FusedMoEFn(torch.autograd.Function):

@@ -208,6 +208,7 @@ class FusedMoE:
         self.table_copy = torch.zeros(self.world, cfg.num_experts, **i32)
         self.check_every_call = bool(env_flag("CHECK_STATUS", 0))
         self.fused_router = bool(env_flag("FUSED_ROUTER", 0))
+        self._save_pre = True   # whether the next forward stores the pre-activations (set per call by run_experts)
 
     # ------------------------------------------------------------------------------------------
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
@@ -252,7 +253,13 @@ class FusedMoE:
         ex = layer.experts
         wg = ex.htoh4_gate.weight if cfg.activation == "swiglu" else None
         bg = ex.htoh4_gate.bias if cfg.activation == "swiglu" else None
-        y = _FusedMoEFn.apply(x, w, idx, ex.htoh4.weight, ex.htoh4.bias, wg, bg, ex.h4toh.weight, ex.h4toh.bias, self)
+        tensors = (x, w, ex.htoh4.weight, ex.htoh4.bias, wg, bg, ex.h4toh.weight, ex.h4toh.bias)
+        # without a backward pass to come the pre-activations need not be stored (inference / no_grad)
+        self._save_pre = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+        try:
+            y = _FusedMoEFn.apply(x, w, idx, ex.htoh4.weight, ex.htoh4.bias, wg, bg, ex.h4toh.weight, ex.h4toh.bias, self)
+        finally:
+            self._save_pre = True
         if self.check_every_call:
             self.ctx.check_status("fused MoE forward")
         return y
@@ -342,9 +349,10 @@ class FusedMoE:
             N.check(lib.ccf_plan(C.byref(p), st), "ccf_plan")
         N.count(3)  # route (2 kernels) + plan
 
-    def stage_dispatch_gemm1(self, x, idx, gate_w, w1, b1, wg=None, bg=None, trace=None):
+    def stage_dispatch_gemm1(self, x, idx, gate_w, w1, b1, wg=None, bg=None, trace=None, save_pre=True):
         """ONE kernel: push this rank's routed rows to their owners and run GEMM-1 (+ bias + activation) on the rows
-        this rank owns, tile by tile as they arrive."""
+        this rank owns, tile by tile as they arrive. ``save_pre=False`` (no backward will follow) skips the stores of
+        the pre-activations, which only the activation derivative needs."""
         cfg, cc = self.cfg, self.ctx
         t, d = x.shape
         f, e_loc = cfg.d_ffn, cfg.experts_per_rank
@@ -354,12 +362,12 @@ class FusedMoE:
                       total_index=self.max_rows // TILE, local_begin=self.local_begin, local_rows=self.local_rows)
         if cfg.activation == "swiglu":
             G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), b1=wg.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K,
-                     epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre, out2=self.h_pre2,
-                     bias0=b1, bias1=bg, **common)
+                     epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre if save_pre else None,
+                     out2=self.h_pre2 if save_pre else None, bias0=b1, bias1=bg, **common)
         else:
             G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT,
-                     n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre, bias0=b1, act=N.ACT_CODE[cfg.activation],
-                     **common)
+                     n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre if save_pre else None, bias0=b1,
+                     act=N.ACT_CODE[cfg.activation], **common)
         cc.tile_flags.zero_()
 
     def stage_gemm2_combine(self, w2, b2, trace=None):
@@ -422,7 +430,7 @@ class _FusedMoEFn(torch.autograd.Function):
         with nvtx_range("moe.route_plan"):
             fm.stage_route_plan(idx, t)
         with nvtx_range("moe.dispatch_gemm1"):
-            fm.stage_dispatch_gemm1(x, idx, gate_w, w1, b1, wg, bg)
+            fm.stage_dispatch_gemm1(x, idx, gate_w, w1, b1, wg, bg, save_pre=fm._save_pre)
         with nvtx_range("moe.gemm2_combine"):
             fm.stage_gemm2_combine(w2, b2)
         y = torch.empty(t, d, dtype=x.dtype, device=x.device)

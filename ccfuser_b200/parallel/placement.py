@@ -107,6 +107,39 @@ def plan_placement(count_table: torch.Tensor, experts_per_rank: int, topology=No
                     best, best_key = c, key
             got[best].append(ex)
             cur[best] += float(load[ex])
+        # greedy leftovers: while the busiest child is above the tolerated load, swap one of its experts with a lighter
+        # one of another child (or move it into a free slot) if that lowers the larger of the two loads
+        sizes = [len(r) for r in child_ranks]
+        for _ in range(4 * len(experts)):
+            hot = max(range(len(children)), key=lambda c: cur[c] / sizes[c])
+            if cur[hot] / sizes[hot] <= target * (1.0 + slack):
+                break
+            best_gain, best_move = 0.0, None
+            for a in got[hot]:
+                for c in range(len(children)):
+                    if c == hot:
+                        continue
+                    options = list(got[c]) + ([None] if len(got[c]) < room[c] else [])
+                    for b in options:
+                        lb = float(load[b]) if b is not None else 0.0
+                        la = float(load[a])
+                        new_hot = (cur[hot] - la + lb) / sizes[hot]
+                        new_c = (cur[c] - lb + la) / sizes[c]
+                        gain = cur[hot] / sizes[hot] - max(new_hot, new_c)
+                        if gain > best_gain + 1e-9:
+                            best_gain, best_move = gain, (a, c, b)
+            if best_move is None:
+                break
+            a, c, b = best_move
+            got[hot].remove(a)
+            got[c].append(a)
+            cur[hot] -= float(load[a])
+            cur[c] += float(load[a])
+            if b is not None:
+                got[c].remove(b)
+                got[hot].append(b)
+                cur[c] -= float(load[b])
+                cur[hot] += float(load[b])
         for c, child in enumerate(children):
             split(child, got[c])
 

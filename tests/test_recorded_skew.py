@@ -1,0 +1,131 @@
+"""Recorded, heavily skewed routing counts as fixtures: placement planning, routing invariants and a 4-rank layer run."""
+import torch
+import torch.nn as nn
+
+from ccfuser_b200 import MoEConfig, MoELayer
+from ccfuser_b200.gates import BaseGate
+from ccfuser_b200.ops.reference import dense_moe_oracle
+from ccfuser_b200.ops.routing import global_plan, route_local
+from ccfuser_b200.parallel.placement import placement_cost, plan_placement
+from tests.fixtures import RECORDED_COUNTS
+from tests.mp_util import run_ranks
+from tests.test_cpu_layer import _full_params, load_shard
+
+W, E, E_LOC = 4, 64, 16
+
+
+def _slots_of_rank(r, scale=1):
+    """Expert id of every slot of rank r, reproducing the recorded histogram (divided by `scale`), shuffled."""
+    counts = [c // scale for c in RECORDED_COUNTS[r]]
+    ids = torch.repeat_interleave(torch.arange(E), torch.tensor(counts))
+    g = torch.Generator().manual_seed(100 + r)
+    return ids[torch.randperm(ids.numel(), generator=g)]
+
+
+def test_planner_on_recorded_skew():
+    ct = torch.tensor(RECORDED_COUNTS)
+    ident = list(range(E))
+    before = placement_cost(ct, ident, E_LOC)
+    pl = plan_placement(ct, E_LOC)
+    after = placement_cost(ct, pl, E_LOC)
+    mean = ct.sum().item() / W
+    assert before["max_rank_rows"] > 1.25 * mean                 # the recorded step is clearly imbalanced
+    assert after["max_rank_rows"] <= 1.06 * mean                  # planned: within the slack of the mean
+    assert after["cross_rows"] <= before["cross_rows"]            # and no more rows cross GPUs than before
+    # two-level topology (two pairs): same balance guarantee at the outer level
+    pl2 = plan_placement(ct, E_LOC, topology=[[0, 1], [2, 3]])
+    a2 = placement_cost(ct, pl2, E_LOC)
+    pair_rows = [a2["rank_rows"][0] + a2["rank_rows"][1], a2["rank_rows"][2] + a2["rank_rows"][3]]
+    assert max(pair_rows) <= 1.06 * 2 * mean
+
+
+def test_routing_invariants_on_recorded_skew():
+    cap = 512
+    tables = []
+    for r in range(W):
+        ids = _slots_of_rank(r)
+        plan = route_local(ids.view(-1, 1), E, cap)
+        assert plan.raw_count.tolist() == RECORDED_COUNTS[r]
+        assert plan.count.tolist() == [min(c, cap) for c in RECORDED_COUNTS[r]]
+        # kept slots of one expert have positions 0..count-1, in slot order
+        for e in (9, 34, 50):
+            pos = plan.pos[(ids == e) & plan.keep]
+            assert pos.tolist() == list(range(int(plan.count[e])))
+        tables.append(plan.count)
+    table = torch.stack(tables)
+    gp = global_plan(table, E_LOC)
+    assert (gp.expert_base % 128 == 0).all()
+    # segments of different (source, expert) pairs never overlap inside an owner's buffer
+    for owner in range(W):
+        spans = []
+        for e in range(owner * E_LOC, (owner + 1) * E_LOC):
+            for r in range(W):
+                n = int(table[r, e])
+                if n:
+                    s = int(gp.expert_base[e] + gp.src_offset[r, e])
+                    spans.append((s, s + n))
+        spans.sort()
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+        assert spans[-1][1] <= int(gp.rank_rows[owner])
+
+
+class _FixedGate(BaseGate):
+    """Routes by a prescribed expert id per token (top-1) with a learnable scalar score per expert."""
+
+    def __init__(self, ids, num_expert, world):
+        super().__init__(num_expert, world)
+        self.ids = ids
+        self.gate = nn.Linear(1, self.tot_expert)          # parameters so that DDP-style code finds a router
+
+    def forward(self, x):
+        idx = self.ids.view(-1, 1)
+        score = torch.sigmoid(self.gate.bias)[idx.view(-1)].view(-1, 1).float()
+        self.set_loss(None)
+        return idx, score
+
+
+def _skew_rank_fn(rank, world, kw, scale):
+    cfg = MoEConfig(**kw)
+    full = _full_params(cfg, 0)
+    ids = _slots_of_rank(rank, scale)
+    gate = _FixedGate(ids, cfg.experts_per_rank, world)
+    with torch.no_grad():
+        gate.gate.bias.copy_(torch.linspace(-1, 1, cfg.num_experts))
+    layer = MoELayer(cfg, gate=gate)
+    load_shard(layer, {**full, "gate.weight": gate.gate.weight.detach(), "gate.bias": gate.gate.bias.detach()}, rank)
+    g = torch.Generator().manual_seed(7 + rank)
+    x = torch.randn(ids.numel(), cfg.d_model, generator=g).requires_grad_(True)
+    y = layer(x)
+    y.square().sum().backward()
+    return y.detach(), x.grad.clone(), layer.experts.h4toh.weight.grad.clone(), layer.count_table()
+
+
+def test_four_rank_layer_with_recorded_skew_and_capacity():
+    scale = 8                                       # about 1000 slots per rank (counts are floored) keeps the CPU run short
+    kw = dict(d_model=16, d_ffn=32, num_experts=E, top_k=1, capacity_factor=4.0, activation="relu",
+              dtype=torch.float32, ep_size=W, backend="cpu", max_tokens=1100)
+    cfg = MoEConfig(**kw)
+    res = run_ranks(_skew_rank_fn, W, kw, scale, timeout=240)
+    full = {k: v.clone().requires_grad_(True) for k, v in _full_params(cfg, 0).items()}
+    xs, routing = [], []
+    for r in range(W):
+        ids = _slots_of_rank(r, scale)
+        g = torch.Generator().manual_seed(7 + r)
+        xs.append(torch.randn(ids.numel(), cfg.d_model, generator=g).requires_grad_(True))
+        score = torch.sigmoid(torch.linspace(-1, 1, E))[ids].view(-1, 1)
+        routing.append((ids.view(-1, 1), score))
+    # every rank applies the capacity to its own token count, like the layer does
+    ys = [dense_moe_oracle([xs[r]], full, top_k=1, capacity=cfg.capacity(xs[r].shape[0]), activation="relu",
+                           routing=[routing[r]])[0] for r in range(W)]
+    sum(y.square().sum() for y in ys).backward()
+    dropped = 0
+    for r in range(W):
+        y, gx, gw2, table = res[r]
+        assert torch.allclose(y, ys[r].detach(), atol=1e-5, rtol=1e-4)
+        assert torch.allclose(gx, xs[r].grad, atol=1e-5, rtol=1e-4)
+        assert torch.allclose(gw2, full["h4toh.weight"].grad[r * E_LOC:(r + 1) * E_LOC], atol=1e-5, rtol=1e-4)
+        cap = cfg.capacity(xs[r].shape[0])
+        want = [min(c // scale, cap) for c in RECORDED_COUNTS[r]]
+        assert table[r].tolist() == want
+        dropped += sum(c // scale for c in RECORDED_COUNTS[r]) - sum(want)
+    assert dropped > 0                                            # the hot experts exceed even a capacity factor of 4

@@ -53,6 +53,31 @@ def test_route_kernel_bit_exact(s, e, cap):
     assert torch.equal(kept.cpu().long(), ref.count)
 
 
+def test_route_kernel_on_recorded_skew():
+    """The recorded 4-rank x 64-expert histogram (a few experts draw thousands of slots, many draw none)."""
+    from ccfuser_b200 import native as N
+    from ccfuser_b200.ops.routing import route_local
+    from tests.fixtures import RECORDED_COUNTS
+    lib = N.load()
+    e, cap = 64, 512
+    i32 = dict(dtype=torch.int32, device="cuda")
+    for r, counts in enumerate(RECORDED_COUNTS):
+        ids = torch.repeat_interleave(torch.arange(e), torch.tensor(counts))
+        ids = ids[torch.randperm(ids.numel(), generator=torch.Generator().manual_seed(r))]
+        s = ids.numel()
+        expert = ids.int().cuda()
+        nb = (s + 1023) // 1024
+        pos, bh, bo = torch.empty(s, **i32), torch.zeros(nb * e, **i32), torch.zeros(nb * e, **i32)
+        raw, kept, ticket = torch.zeros(e, **i32), torch.zeros(e, **i32), torch.zeros(1, **i32)
+        N.check(lib.ccf_route(expert.data_ptr(), s, e, cap, pos.data_ptr(), bh.data_ptr(), bo.data_ptr(),
+                              raw.data_ptr(), kept.data_ptr(), ticket.data_ptr(), N.stream_ptr()), "route")
+        torch.cuda.synchronize()
+        ref = route_local(ids.view(-1, 1), e, cap)
+        assert raw.cpu().tolist() == counts
+        assert torch.equal(pos.cpu().long(), ref.pos)
+        assert torch.equal(kept.cpu().long(), ref.count)
+
+
 def test_route_ordered_gives_destination_order():
     """ccf_route_ordered: kept slots listed expert by expert starting at `first_expert`, in position order."""
     from ccfuser_b200 import native as N

@@ -65,5 +65,19 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def build_selftest() -> str:
+    """Build ``lib/ccf_selftest``, the stand-alone C++ check of the library (csrc/selftest.cu: numerics against a CPU
+    loop, throughput against cuBLAS). Not part of the default build: it links cuBLAS."""
+    build()
+    exe = os.path.join(LIB_DIR, "ccf_selftest")
+    subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
+                           os.path.join(CSRC, "selftest.cu"), "-o", exe, "-L", LIB_DIR, "-lccfuser_b200", "-lcublas",
+                           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"])
+    return exe
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--selftest" in sys.argv:
+        print(build_selftest())
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -446,23 +446,6 @@ static int launch_variant(const CUtensorMap* tm, const CcfGemmArgs& args, int gr
 
 extern "C" {
 
-struct CcfGemmLaunch {
-  CcfGemmArgs args;
-  const void* a0;
-  const void* a1;
-  const void* b0;
-  const void* b1;
-  long long a_rows, a_cols;  // 2-D views, cols contiguous
-  long long b_rows, b_cols;
-  int a_major, b_major;      // 0 = K-major, 1 = MN-major
-  int epi;                   // CcfEpilogue
-  int kgroup;                // 1 = k-grouped (wgrad)
-  int grid;                  // 0 = one CTA per SM
-  int device;                // CUDA device of the operands; made current for the calling thread (-1 = leave)
-  int two_cta;               // 1 = 256x256 tiles on CTA pairs (tcgen05 cta_group::2), 0 = 128x256 tiles per CTA
-  int pad0;
-};
-
 int ccf_gemm_smem_bytes() { return ccf::kSmemBytes; }
 
 // sizes of the argument blocks, so the Python mirror of the structures can be checked at load time

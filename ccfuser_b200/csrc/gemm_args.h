@@ -102,3 +102,22 @@ struct CcfGemmArgs {
   int pad1;
   CcfDispatchArgs disp;
 };
+
+// One launch of the grouped GEMM as the host entry point ccf_gemm_launch takes it: the kernel arguments plus the 2-D
+// views of the operands, from which the tensor maps are encoded.
+struct CcfGemmLaunch {
+  CcfGemmArgs args;
+  const void* a0;
+  const void* a1;
+  const void* b0;
+  const void* b1;
+  long long a_rows, a_cols;  // 2-D views, cols contiguous
+  long long b_rows, b_cols;
+  int a_major, b_major;      // 0 = K-major, 1 = MN-major
+  int epi;                   // CcfEpilogue
+  int kgroup;                // 1 = k-grouped (wgrad)
+  int grid;                  // 0 = one CTA per SM
+  int device;                // CUDA device of the operands; made current for the calling thread (-1 = leave)
+  int two_cta;               // 1 = 256x256 tiles on CTA pairs (tcgen05 cta_group::2), 0 = 128x256 tiles per CTA
+  int pad0;
+};

@@ -27,6 +27,29 @@ class _DeviceView:
         self._owner = owner
 
 
+def host_id() -> str:
+    """Identifies the machine (and boot) this process runs on: CUDA IPC handles are only meaningful inside it."""
+    import socket
+    boot = ""
+    try:
+        with open("/proc/sys/kernel/random/boot_id") as f:
+            boot = f.read().strip()
+    except OSError:
+        pass
+    return f"{socket.gethostname()}/{boot}"
+
+
+def check_same_host(hosts: Sequence[str]) -> None:
+    """The expert-parallel group exchanges rows through peer memory, so all its ranks must share one NVLink /
+    NVSwitch domain, i.e. one machine. Across machines use data parallelism over the expert-parallel groups
+    (utils/dist.py: make_ep_dp_groups)."""
+    if len(set(hosts)) > 1:
+        raise RuntimeError(
+            "the ranks of an expert-parallel group must run on one machine (peer memory over NVLink), but this group "
+            f"spans {len(set(hosts))}: {sorted(set(hosts))}. Keep ep_size within a node and put data parallelism across nodes "
+            "(make_ep_dp_groups(ep_size)).")
+
+
 class SymmBuffer:
     """One symmetric allocation. ``local`` is a uint8 tensor over this rank's memory; ``peer_ptr(r)``
     is the address at which rank r's copy is mapped in this process."""
@@ -49,8 +72,10 @@ class SymmBuffer:
             hb = lib.ccf_symm_handle_bytes()
             buf = C.create_string_buffer(hb)
             N.check(lib.ccf_symm_get_handle(self.base, buf), "ccf_symm_get_handle")
-            handles: List[Optional[bytes]] = [None] * self.world
-            dist.all_gather_object(handles, bytes(buf.raw), group=group)
+            gathered: List[Optional[tuple]] = [None] * self.world
+            dist.all_gather_object(gathered, (host_id(), bytes(buf.raw)), group=group)
+            check_same_host([g[0] for g in gathered])
+            handles = [g[1] for g in gathered]
             for r, h in enumerate(handles):
                 if r == self.rank:
                     continue

@@ -63,3 +63,11 @@ def test_plot_tool_writes_wellformed_svg(tmp_path):
     for p in made:
         root = ET.parse(p).getroot()
         assert root.tag.endswith("svg") and len(list(root.iter())) > 20
+
+
+def test_expert_parallel_group_must_share_a_machine():
+    import pytest
+    from ccfuser_b200.parallel.symm import check_same_host, host_id
+    check_same_host([host_id()] * 8)
+    with pytest.raises(RuntimeError, match="one machine"):
+        check_same_host(["node-a/1", "node-a/1", "node-b/2", "node-b/2"])

@@ -247,3 +247,32 @@ def rebalance_experts(layer, placement: Sequence[int], optimizer: Optional[torch
             p.grad = None
     history = getattr(layer, "placement_history", None)
     layer.placement_history = compose(history, placement) if history is not None else list(placement)
+
+
+def main(argv=None):
+    """Offline what-if on a saved ``[ranks, experts]`` count table (a ``torch.save``-d integer tensor), the use the
+    reference's scratch script makes of its recorded counts (mix_moe/mix_moe/t.py:142-148):
+
+        python -m ccfuser_b200.parallel.placement counts.pt [--topology "[[0,1],[2,3]]"] [--slack 0.05]
+    """
+    import argparse
+    import json
+    ap = argparse.ArgumentParser()
+    ap.add_argument("counts", help="file with a [ranks, experts] integer tensor")
+    ap.add_argument("--topology", default="", help="nested list of ranks as JSON; default flat")
+    ap.add_argument("--slack", type=float, default=0.05)
+    a = ap.parse_args(argv)
+    ct = torch.load(a.counts, map_location="cpu")
+    w, e = ct.shape
+    e_loc = e // w
+    topo = json.loads(a.topology) if a.topology else None
+    pl = plan_placement(ct, e_loc, topo, a.slack)
+    out = {"ranks": w, "experts": e, "before": placement_cost(ct, list(range(e)), e_loc),
+           "after": placement_cost(ct, pl, e_loc), "moved_experts": sum(1 for p, q in enumerate(pl) if p // e_loc != q // e_loc),
+           "placement": pl}
+    print(json.dumps(out))
+    return out
+
+
+if __name__ == "__main__":
+    main()

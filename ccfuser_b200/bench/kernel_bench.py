@@ -2,7 +2,9 @@
 mix_moe/mix_moe/kernel_evaluation.py:193-463 with the timing loops of mix_moe/csrc/cuda/mix_gemm.cu:619-662).
 
 "AG" = dispatch all-to-all -> GEMM-1 (one fused kernel here), "GA" = GEMM-2 -> combine all-to-all (one fused kernel
-plus the wait/reduce on the source). Routing is synthetic with a chosen locality (fraction of a rank's tokens that
+plus the wait/reduce on the source). ``--ag-epilogue plain`` (default) times what the reference's AG_test times, GEMM-1
+with its bias and one output (mix_moe/csrc/mix_moe.h:146-185); ``layer`` times the training layer's kernel, which also
+applies GELU and stores the pre-activation, and gives the baseline the same extra work. Routing is synthetic with a chosen locality (fraction of a rank's tokens that
 stay on the rank), top-1, 16384 tokens per GPU, 1024 -> 4096 -> 1024, swept over the remote fraction or over
 experts per GPU. Everything is timed on the device with CUDA events, max over ranks.
 
@@ -19,6 +21,7 @@ import torch
 import torch.distributed as dist
 
 from .. import MoEConfig, MoELayer
+from .. import native as N
 from ..utils.dist import init_distributed
 
 
@@ -75,7 +78,10 @@ def run(args, world, rank, e_loc, remote_frac):
         fm.stage_route_plan(idx, tokens)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         ev[0].record()
-        fm.stage_dispatch_gemm1(x, idx, gate, ex.htoh4.weight, ex.htoh4.bias)
+        if args.ag_epilogue == "plain":
+            fm.stage_dispatch_gemm1(x, idx, gate, ex.htoh4.weight, ex.htoh4.bias, save_pre=False, act=N.ACT_NONE)
+        else:
+            fm.stage_dispatch_gemm1(x, idx, gate, ex.htoh4.weight, ex.htoh4.bias)
         ev[1].record()
         fm.stage_gemm2_combine(ex.h4toh.weight, ex.h4toh.bias)
         fm.stage_reduce(tokens, y)
@@ -128,6 +134,10 @@ def run(args, world, rank, e_loc, remote_frac):
         else:
             recv.copy_(send)
 
+    b1t = ex.htoh4.bias.detach()
+    layer_epi = args.ag_epilogue == "layer"
+    pre = torch.empty_like(h) if layer_epi else None
+
     def gemm1():
         # rows arrive grouped by (source, expert); a real layer regroups them, here each segment is multiplied in place
         off = 0
@@ -135,8 +145,13 @@ def run(args, world, rank, e_loc, remote_frac):
             for e in range(e_loc):
                 c = int(recv_cnt[r, e])
                 if c:
-                    torch.mm(recv[off:off + c], w1t[e].t(), out=h[off:off + c])
+                    if layer_epi:
+                        torch.addmm(b1t[e], recv[off:off + c], w1t[e].t(), out=pre[off:off + c])
+                    else:
+                        torch.addmm(b1t[e], recv[off:off + c], w1t[e].t(), out=h[off:off + c])
                 off += c
+        if layer_epi:
+            h.copy_(torch.nn.functional.gelu(pre))
 
     def gemm2():
         off = 0
@@ -165,8 +180,11 @@ def run(args, world, rank, e_loc, remote_frac):
     offs = torch.tensor(per_expert, device="cuda", dtype=torch.int32).cumsum(0).to(torch.int32)
     has_grouped = hasattr(torch, "_grouped_mm")
 
+    eid = torch.repeat_interleave(torch.arange(e_loc, device="cuda"), torch.tensor(per_expert, device="cuda"))
+
     def gemm1_grouped():
-        return torch._grouped_mm(recv.index_select(0, perm), w1t.transpose(1, 2), offs=offs)
+        z = torch._grouped_mm(recv.index_select(0, perm), w1t.transpose(1, 2), offs=offs) + b1t[eid]
+        return torch.nn.functional.gelu(z) if layer_epi else z
 
     hg = gemm1_grouped() if has_grouped else None
 
@@ -182,7 +200,7 @@ def run(args, world, rank, e_loc, remote_frac):
     layer.release()
     del layer
     torch.cuda.empty_cache()
-    return {"bench": "fused_kernels_vs_nccl", "n_gpus": world, "tokens_per_gpu": tokens, "d_model": d, "d_ffn": f,
+    return {"bench": "fused_kernels_vs_nccl", "ag_epilogue": args.ag_epilogue, "n_gpus": world, "tokens_per_gpu": tokens, "d_model": d, "d_ffn": f,
             "experts_per_gpu": e_loc, "remote_frac": remote_frac,
             "fused_ag_ms": round(fused_ag, 4), "nccl_a2a_gemm1_ms": round(base_ag, 4), "nccl_a2a_in_ms": round(base_a2a_in, 4),
             "fused_ga_ms": round(fused_ga, 4), "gemm2_nccl_a2a_ms": round(base_ga, 4), "nccl_a2a_out_ms": round(base_a2a_out, 4),
@@ -201,6 +219,7 @@ def main():
     ap.add_argument("--d-ffn", type=int, default=4096)
     ap.add_argument("--experts-per-gpu", type=int, default=16)
     ap.add_argument("--remote-frac", type=float, default=0.25)
+    ap.add_argument("--ag-epilogue", default="plain", choices=["plain", "layer"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--out", default="")

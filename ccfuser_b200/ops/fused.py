@@ -349,10 +349,11 @@ class FusedMoE:
             N.check(lib.ccf_plan(C.byref(p), st), "ccf_plan")
         N.count(3)  # route (2 kernels) + plan
 
-    def stage_dispatch_gemm1(self, x, idx, gate_w, w1, b1, wg=None, bg=None, trace=None, save_pre=True):
+    def stage_dispatch_gemm1(self, x, idx, gate_w, w1, b1, wg=None, bg=None, trace=None, save_pre=True, act=None):
         """ONE kernel: push this rank's routed rows to their owners and run GEMM-1 (+ bias + activation) on the rows
         this rank owns, tile by tile as they arrive. ``save_pre=False`` (no backward will follow) skips the stores of
-        the pre-activations, which only the activation derivative needs."""
+        the pre-activations, which only the activation derivative needs. ``act`` overrides the configured activation
+        code of a non-gated FFN (the kernel benchmark times the bare dispatch + GEMM + bias)."""
         cfg, cc = self.cfg, self.ctx
         t, d = x.shape
         f, e_loc = cfg.d_ffn, cfg.experts_per_rank
@@ -367,7 +368,7 @@ class FusedMoE:
         else:
             G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT,
                      n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre if save_pre else None, bias0=b1,
-                     act=N.ACT_CODE[cfg.activation], **common)
+                     act=N.ACT_CODE[cfg.activation] if act is None else act, **common)
         cc.tile_flags.zero_()
 
     def stage_gemm2_combine(self, w2, b2, trace=None):

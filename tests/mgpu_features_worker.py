@@ -1,0 +1,95 @@
+"""Multi-GPU check of shadow experts and live expert re-placement on the fused backend, run as
+`torchrun --nproc-per-node W tests/mgpu_features_worker.py`. Prints 'MGPU_FEATURES_OK' on rank 0.
+
+Both features are compared against the same layer without them: replicated experts and moved experts must not
+change what the layer computes (beyond bf16 rounding of a different GEMM schedule)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ccfuser_b200 import MoEConfig, MoELayer  # noqa: E402
+from ccfuser_b200.utils.dist import init_distributed  # noqa: E402
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / b.norm().clamp_min(1e-6))
+
+
+def make(cfg, seed):
+    layer = MoELayer(cfg, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    with torch.no_grad():
+        for n, p in layer.named_parameters():
+            # router replicated (same seed on every rank), experts differ per rank
+            gen = g if n.startswith("gate.") else torch.Generator(device="cuda").manual_seed(seed + 1 + layer.ep_rank)
+            p.copy_((torch.randn(p.shape, device="cuda", generator=gen) * 0.05).to(p.dtype))
+        layer.gate.gate.bias[3] += 0.5          # one clearly popular expert
+    return layer
+
+
+def clear_tokens(layer, x, k):
+    lg = layer.gate.logits(x).float().sort(dim=-1, descending=True).values
+    return lg[:, k - 1] != lg[:, k]
+
+
+def main():
+    rank, _, world = init_distributed()
+    tokens, d, f, e_loc = 1024, 256, 512, 4
+    base_cfg = MoEConfig(d_model=d, d_ffn=f, num_experts=e_loc * world, top_k=2, capacity_factor=None, activation="gelu",
+                         dtype=torch.bfloat16, ep_size=world, backend="fused", max_tokens=tokens, recv_factor=4.0)
+    gx = torch.Generator(device="cuda").manual_seed(50 + rank)
+    x = (torch.randn(tokens, d, device="cuda", generator=gx) * 0.5).bfloat16()
+    gy = torch.randn(tokens, d, device="cuda", generator=gx).bfloat16()
+
+    # ---- shadow experts: forward and gradients equal those of the plain layer -------------------------------
+    plain = make(base_cfg, 5)
+    shadow = make(base_cfg.replace(shadow_experts=2), 5)
+    outs = []
+    for layer in (plain, shadow):
+        xi = x.clone().requires_grad_(True)
+        y = layer(xi)
+        y.backward(gy)
+        torch.cuda.synchronize()
+        layer.check_status()
+        outs.append((y.detach(), xi.grad, {n: p.grad.clone() for n, p in layer.named_parameters()}))
+    ids = shadow.last_stats["shadow_ids"].tolist()
+    assert 3 in ids, ids
+    assert int(shadow.count_table()[:, ids].sum()) == 0
+    errs = {"y": rel(outs[1][0], outs[0][0]), "dx": rel(outs[1][1], outs[0][1])}
+    for n in outs[0][2]:
+        errs[n] = rel(outs[1][2][n], outs[0][2][n])
+    bad = {k: v for k, v in errs.items() if not v < 3e-2}
+    assert not bad, f"rank {rank} shadow: {bad}"
+    shadow.release()
+
+    # ---- live re-placement across ranks ------------------------------------------------------------------------
+    e = e_loc * world
+    placement = list(range(e))
+    placement[0], placement[e - 1] = placement[e - 1], placement[0]          # first and last expert swap ranks
+    placement[1], placement[e_loc] = placement[e_loc], placement[1]
+    with torch.no_grad():
+        y0 = plain(x)
+        plain.rebalance(placement)
+        y1 = plain(x)
+        planned = plain.rebalance()
+        y2 = plain(x)
+        ok = clear_tokens(plain, x, 2)
+    torch.cuda.synchronize()
+    plain.check_status()
+    assert sorted(planned) == list(range(e))
+    assert float(ok.float().mean()) > 0.9
+    assert rel(y1[ok], y0[ok]) < 1e-2 and rel(y2[ok], y0[ok]) < 1e-2, (rel(y1[ok], y0[ok]), rel(y2[ok], y0[ok]))
+    plain.release()
+    dist.barrier()
+    if rank == 0:
+        print(f"MGPU_FEATURES_OK world={world} shadow_worst={max(errs.values()):.4f}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,5 +1,6 @@
 """Fused layer on 2 (and, when present, 4 or 8) GPUs of one node against the dense oracle, as child processes."""
 import os
+import signal
 import subprocess
 import sys
 
@@ -10,12 +11,19 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(world, port):
+def _run(world, port, worker="mgpu_worker.py", token="MGPU_OK", timeout=600):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", CCFUSER_WAIT_LIMIT_S="20")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mgpu_worker.py")]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0 and "MGPU_OK" in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", worker)]
+    # own session: if the run has to be cut short, the launcher and all its ranks go together
+    proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
+    try:
+        stdout, stderr = proc.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        stdout, stderr = proc.communicate()
+        raise AssertionError(f"timed out after {timeout} s\n" + stdout[-3000:] + stderr[-3000:])
+    assert proc.returncode == 0 and token in stdout, stdout[-3000:] + stderr[-3000:]
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -23,3 +31,11 @@ def test_fused_layer_multi_gpu(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _run(world, 29600 + world)
+
+
+@pytest.mark.xfail(strict=False, reason="shadow experts / re-placement on NCCL ranks: tolerances are provisional")
+@pytest.mark.parametrize("world", [2, 4])
+def test_shadow_and_rebalance_multi_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run(world, 29700 + world, worker="mgpu_features_worker.py", token="MGPU_FEATURES_OK", timeout=300)

@@ -159,6 +159,49 @@ def _declare(lib):
         fn.restype = restype
 
 
+class LaunchRecorder:
+    """Stands in for the library and records every launcher call instead of running it, so the host side of the fused
+    path (which launches, in which order, with which argument blocks) can be tested on a machine without a GPU.
+    Size queries and error strings go to the real library; everything else returns 0. Structures passed with
+    ``ctypes.byref`` are stored as their raw bytes (``GemmLaunch.from_buffer_copy`` turns them back into fields)."""
+
+    _PASS_THROUGH = ("ccf_sizeof_", "ccf_error_string", "ccf_gemm_smem_bytes", "ccf_symm_handle_bytes")
+
+    def __init__(self, real):
+        self._real = real
+        self.calls = []
+
+    def __getattr__(self, name):
+        fn = getattr(self._real, name)
+        if name.startswith(self._PASS_THROUGH):
+            return fn
+
+        def record(*args):
+            self.calls.append((name, tuple(bytes(a._obj) if hasattr(a, "_obj") else a for a in args)))
+            return 0
+        return record
+
+    def names(self):
+        return [c[0] for c in self.calls]
+
+
+class record_launches:
+    """Context manager: ``with record_launches() as rec: ...`` routes all library calls of this process to a
+    LaunchRecorder (no kernel runs, outputs stay uninitialised)."""
+
+    def __enter__(self):
+        global _lib
+        self._saved = load()
+        self.rec = LaunchRecorder(self._saved)
+        _lib = self.rec
+        return self.rec
+
+    def __exit__(self, *exc):
+        global _lib
+        _lib = self._saved
+        return False
+
+
 def check(rc: int, what: str):
     if rc != 0:
         msg = ""
@@ -171,6 +214,8 @@ def check(rc: int, what: str):
 
 
 def stream_ptr() -> int:
+    if not torch.cuda.is_available():
+        return 0   # host-side dry runs (LaunchRecorder)
     return torch.cuda.current_stream().cuda_stream
 
 

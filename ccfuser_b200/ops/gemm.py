@@ -26,7 +26,10 @@ class Workspace:
     @classmethod
     def get(cls, device) -> "Workspace":
         device = torch.device(device)
-        key = device.index if device.index is not None else torch.cuda.current_device()
+        if device.type != "cuda":
+            key = -1   # host-side dry runs
+        else:
+            key = device.index if device.index is not None else torch.cuda.current_device()
         ws = cls._by_device.get(key)
         if ws is None:
             ws = cls._by_device[key] = Workspace(device)
@@ -109,7 +112,10 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     L.a_rows, L.a_cols = a0.shape
     L.b_rows, L.b_cols = b0.shape
     L.a_major, L.b_major, L.epi, L.kgroup, L.grid = int(a_major), int(b_major), int(epi), int(bool(kgroup)), int(grid)
-    L.device = a0.device.index if a0.device.index is not None else torch.cuda.current_device()
+    if a0.device.type != "cuda":
+        L.device = -1
+    else:
+        L.device = a0.device.index if a0.device.index is not None else torch.cuda.current_device()
     if two_cta is None:
         two_cta = TWO_CTA_DEFAULT
     # the pair kernel needs 256-row output tiles in k-grouped mode

@@ -61,13 +61,27 @@ class SymmBuffer:
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.nbytes = (int(nbytes) + 1023) // 1024 * 1024
         self.device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+        self._opened: List[int] = []
+        self._cursor = 0
+        if self.device.type != "cuda":
+            # Host stand-in for dry runs of the launch logic (native.LaunchRecorder): ordinary host memory, and the
+            # peers' base addresses are exchanged as plain numbers that nothing dereferences.
+            self.local = torch.zeros(self.nbytes, dtype=torch.uint8)
+            self.base = self.local.data_ptr()
+            self._peer_base = [self.base]
+            if self.world > 1:
+                bases: List[Optional[int]] = [None] * self.world
+                dist.all_gather_object(bases, self.base, group=group)
+                self._peer_base = [int(b) for b in bases]
+            self._host = True
+            return
+        self._host = False
         p = C.c_void_p()
         with torch.cuda.device(self.device):
             N.check(lib.ccf_symm_alloc(self.nbytes, C.byref(p)), "ccf_symm_alloc")
         self.base = p.value
         self._peer_base: List[int] = [0] * self.world
         self._peer_base[self.rank] = self.base
-        self._opened: List[int] = []
         if self.world > 1:
             hb = lib.ccf_symm_handle_bytes()
             buf = C.create_string_buffer(hb)
@@ -85,7 +99,6 @@ class SymmBuffer:
                 self._opened.append(q.value)
             dist.barrier(group=group)
         self.local = torch.as_tensor(_DeviceView(self.base, self.nbytes, self), device=self.device)
-        self._cursor = 0
 
     def peer_ptr(self, rank: int, offset: int = 0) -> int:
         return self._peer_base[rank] + offset
@@ -110,6 +123,10 @@ class SymmBuffer:
 
     def close(self):
         if self.base is None:
+            return
+        if self._host:
+            self.local = None
+            self.base = None
             return
         lib = N.load()
         for q in self._opened:

@@ -1,0 +1,135 @@
+"""Host side of the fused path without a GPU: the library calls are recorded instead of run, and the sequence of
+launches and their argument blocks are checked (which kernels, which operands, which epilogues)."""
+import torch
+
+from ccfuser_b200 import MoEConfig, MoELayer
+from ccfuser_b200 import native as N
+
+
+def _layer(act="gelu", tokens=256, e=4, d=128, f=256, k=2, **kw):
+    cfg = MoEConfig(d_model=d, d_ffn=f, num_experts=e, top_k=k, activation=act, dtype=torch.bfloat16, ep_size=1,
+                    backend="fused", max_tokens=tokens, **kw)
+    return cfg, MoELayer(cfg, device="cpu")
+
+
+def _gemms(rec):
+    return [N.GemmLaunch.from_buffer_copy(c[1][0]) for c in rec.calls if c[0] == "ccf_gemm_launch"]
+
+
+def test_forward_backward_launch_sequence_gelu():
+    cfg, layer = _layer("gelu")
+    x = torch.randn(200, cfg.d_model).bfloat16().requires_grad_(True)
+    with N.record_launches() as rec:
+        y = layer(x)
+        n_fwd = len(rec.calls)
+        y.float().sum().backward()
+    names = rec.names()
+    assert names[:n_fwd] == ["ccf_topk_softmax", "ccf_route_ordered", "ccf_plan", "ccf_gemm_launch", "ccf_gemm_launch",
+                             "ccf_combine_wait", "ccf_combine_reduce"]
+    assert names[n_fwd:] == ["ccf_gemm_launch", "ccf_gemm_launch", "ccf_colsum_grouped", "ccf_gemm_launch",
+                             "ccf_colsum_grouped", "ccf_gemm_launch", "ccf_combine_wait", "ccf_combine_reduce",
+                             "ccf_topk_softmax_bwd"]
+    fm = layer._fused_impl()
+    ex = layer.experts
+    g1, g2, dg2, wg2, wg1, dg1 = _gemms(rec)
+    d, f, e = cfg.d_model, cfg.d_ffn, cfg.num_experts
+    # GEMM-1: dispatch fused in, bias + GELU, pre-activation saved for backward
+    assert (g1.epi, g1.a_major, g1.b_major, g1.kgroup) == (N.EPI_BIAS_ACT, N.MAJ_K, N.MAJ_K, 0)
+    assert (g1.args.n, g1.args.k, g1.args.num_groups, g1.args.b_group_rows, g1.args.act) == (f, d, e, f, N.ACT_GELU)
+    assert g1.a0 == fm.xrecv.data_ptr() and g1.b0 == ex.htoh4.weight.data_ptr() and g1.args.bias0 == ex.htoh4.bias.data_ptr()
+    assert g1.args.out0 == fm.h_act.data_ptr() and g1.args.out1 == fm.h_pre.data_ptr()
+    assert g1.args.tile_flags == fm.ctx.tile_flags.data_ptr() and g1.args.n_comm_ctas > 0
+    assert g1.args.disp.x == x.data_ptr() and g1.args.disp.backward == 0 and g1.args.disp.top_k == 2
+    assert g1.args.disp.peer_recv[0] == fm.xrecv.data_ptr() and g1.args.disp.e_total == e
+    assert g1.args.disp.capacity == cfg.capacity(200) and g1.args.disp.d == d
+    # GEMM-2: combine epilogue into this rank's combine buffer, finish token
+    assert (g2.epi, g2.args.n, g2.args.k, g2.args.send_finish, g2.args.world) == (N.EPI_COMBINE, d, f, 1, 1)
+    assert g2.a0 == fm.h_act.data_ptr() and g2.b0 == ex.h4toh.weight.data_ptr() and g2.args.peer_comb[0] == fm.comb.data_ptr()
+    assert g2.args.row_gate == fm.ctx.row_gate.data_ptr() and not g2.args.tile_flags and g2.args.n_comm_ctas == 0
+    # backward: dy dispatch + dgrad-2 with GELU', both wgrads k-grouped MN x MN, dgrad-1 combines into the gradient buffer
+    assert (dg2.epi, dg2.b_major, dg2.args.n, dg2.args.k) == (N.EPI_DACT, N.MAJ_MN, f, d)
+    assert dg2.a0 == fm.ctx.grecv.data_ptr() and dg2.b0 == ex.h4toh.weight.data_ptr() and dg2.args.aux0 == fm.h_pre.data_ptr()
+    assert dg2.args.disp.backward == 1 and dg2.args.disp.saved_comb == fm.comb.data_ptr() and dg2.args.disp.dgate
+    for w, a0, b0, m, n in ((wg2, fm.ctx.grecv, fm.h_act, d, f), (wg1, None, fm.xrecv, f, d)):
+        assert (w.epi, w.a_major, w.b_major, w.kgroup) == (N.EPI_STORE, N.MAJ_MN, N.MAJ_MN, 1)
+        assert (w.args.m_per_group, w.args.n, w.args.ld_out) == (m, n, n) and w.b0 == b0.data_ptr()
+        if a0 is not None:
+            assert w.a0 == a0.data_ptr()
+    assert wg1.a0 == dg2.args.out0                                  # wgrad-1 reads dh written by dgrad-2
+    assert (dg1.epi, dg1.b_major, dg1.args.n, dg1.args.k) == (N.EPI_COMBINE, N.MAJ_MN, d, f)
+    assert dg1.a0 == dg2.args.out0 and dg1.b0 == ex.htoh4.weight.data_ptr()
+    assert dg1.args.peer_comb[0] == fm.ctx.gcomb.data_ptr() and not dg1.args.row_gate and dg1.args.send_finish == 1
+    # gradients come back with the right shapes
+    assert ex.htoh4.weight.grad.shape == ex.htoh4.weight.shape and ex.h4toh.bias.grad.shape == ex.h4toh.bias.shape
+    assert x.grad.shape == x.shape and layer.gate.gate.weight.grad is not None
+
+
+def test_inference_forward_skips_pre_activation_stores_and_swiglu_operands():
+    cfg, layer = _layer("swiglu", bias=False)
+    x = torch.randn(100, cfg.d_model).bfloat16()
+    with N.record_launches() as rec, torch.no_grad():
+        layer(x)
+    g1, g2 = _gemms(rec)
+    ex, fm = layer.experts, layer._fused_impl()
+    assert g1.epi == N.EPI_SWIGLU and g1.b0 == ex.htoh4.weight.data_ptr() and g1.b1 == ex.htoh4_gate.weight.data_ptr()
+    assert g1.args.out0 == fm.h_act.data_ptr() and not g1.args.out1 and not g1.args.out2      # nothing saved for backward
+    assert not g1.args.bias0 and not g1.args.bias1 and not g2.args.bias0
+    x2 = x.clone().requires_grad_(True)
+    with N.record_launches() as rec:
+        layer(x2).float().sum().backward()
+    gem = _gemms(rec)
+    assert len(gem) == 2 + 5                                        # swiglu: dgrad-2, wgrad-2, two wgrad-1 halves, dgrad-1
+    assert gem[0].args.out1 == fm.h_pre.data_ptr() and gem[0].args.out2 == fm.h_pre2.data_ptr()
+    assert gem[2].epi == N.EPI_DSWIGLU and gem[2].args.aux0 == fm.h_pre.data_ptr() and gem[2].args.aux1 == fm.h_pre2.data_ptr()
+    assert gem[6].args.kseg == 2 and gem[6].b0 == ex.htoh4_gate.weight.data_ptr() and gem[6].b1 == ex.htoh4.weight.data_ptr()
+    assert "ccf_colsum_grouped" not in rec.names()                 # no biases, no bias gradients
+
+
+def test_epoch_advances_and_device_epoch_switch():
+    cfg, layer = _layer("relu")
+    x = torch.randn(64, cfg.d_model).bfloat16()
+    with N.record_launches() as rec, torch.no_grad():
+        layer(x)
+        layer(x)
+        layer._fused_impl().ctx.use_device_epoch()
+        layer(x)
+    plans = [c for c in rec.calls if c[0].startswith("ccf_plan")]
+    assert [c[0] for c in plans] == ["ccf_plan", "ccf_plan", "ccf_plan_dev_epoch"]
+    e1, e2 = (N.PlanArgs.from_buffer_copy(c[1][0]).epoch for c in plans[:2])
+    assert e2 == e1 + 1
+    assert plans[2][1][1] == layer._fused_impl().ctx.epoch_dev.data_ptr()
+    assert int(layer._fused_impl().ctx.epoch_dev) == e2           # the device counter starts where the host one stopped
+
+
+def _two_rank_fn(rank, world):
+    cfg = MoEConfig(d_model=128, d_ffn=256, num_experts=4, top_k=2, activation="gelu", dtype=torch.bfloat16,
+                    ep_size=world, backend="fused", max_tokens=128)
+    layer = MoELayer(cfg, device="cpu")
+    x = torch.randn(100, 128).bfloat16().requires_grad_(True)
+    with N.record_launches() as rec:
+        layer(x).float().sum().backward()
+    fm = layer._fused_impl()
+    g = _gemms(rec)
+    plan = N.PlanArgs.from_buffer_copy([c for c in rec.calls if c[0] == "ccf_plan"][0][1][0])
+    mine = {"xrecv": fm.xrecv.data_ptr(), "comb": fm.comb.data_ptr(), "grecv": fm.ctx.grecv.data_ptr(),
+            "gcomb": fm.ctx.gcomb.data_ptr(), "tile_flags": fm.ctx.tile_flags.data_ptr(), "done": fm.ctx.done.data_ptr(),
+            "cnt_table": fm.ctx.cnt_table.data_ptr(), "row_src": fm.ctx.row_src.data_ptr()}
+    seen = {"xrecv": list(g[0].args.disp.peer_recv)[:world], "comb": list(g[1].args.peer_comb)[:world],
+            "grecv": list(g[2].args.disp.peer_recv)[:world], "gcomb": list(g[-1].args.peer_comb)[:world],
+            "tile_flags": list(g[0].args.disp.peer_tile_flags)[:world], "done": list(g[1].args.peer_done)[:world],
+            "cnt_table": list(plan.peer_table)[:world], "row_src": list(g[0].args.disp.peer_row_src)[:world]}
+    return mine, seen, (plan.world, plan.my_rank, plan.e_loc, g[0].args.disp.my_rank, g[0].args.disp.experts_per_rank, g[1].args.world)
+
+
+def test_two_rank_peer_pointers_line_up():
+    """Every peer pointer a rank passes to its kernels is the address the owner itself uses for that buffer (host
+    stand-in memory, addresses exchanged as numbers), and its own completion counter slot on every rank."""
+    from tests.mp_util import run_ranks
+    res = run_ranks(_two_rank_fn, 2)
+    for r in range(2):
+        mine, seen, meta = res[r]
+        assert meta == (2, r, 2, r, 2, 2)
+        for key in ("xrecv", "comb", "grecv", "gcomb", "tile_flags", "cnt_table", "row_src"):
+            assert seen[key] == [res[0][0][key], res[1][0][key]], key
+        # rank r bumps element r of every rank's `done` array
+        assert seen["done"] == [res[0][0]["done"] + 4 * r, res[1][0]["done"] + 4 * r]

@@ -121,3 +121,20 @@ struct CcfGemmLaunch {
   int two_cta;               // 1 = 256x256 tiles on CTA pairs (tcgen05 cta_group::2), 0 = 128x256 tiles per CTA
   int pad0;
 };
+
+// Arguments of the count exchange + planning kernel (ccf_plan).
+struct CcfPlanArgs {
+  const int* count_kept;               // [E_total] this rank's kept rows per expert
+  int* peer_table[CCF_MAX_RANKS];      // count table [W, E_total] of every rank
+  int* peer_flag[CCF_MAX_RANKS];       // epoch flags [W] of every rank
+  int* dst_base;                       // out [E_total]
+  int* group_base;                     // out [E_loc]
+  int* group_rows;                     // out [E_loc]
+  int* sent_rows;                      // out [W] kept rows this rank sends to each owner
+  int* table_copy;                     // out [W, E_total] snapshot of the table (routing statistics)
+  int* local_begin;                    // out [E_loc] offset of this rank's own rows inside each local expert (optional)
+  int* local_rows;                     // out [E_loc] number of those rows
+  int* status;
+  unsigned long long wait_limit_ns;
+  int world, my_rank, e_total, e_loc, epoch, max_rows;
+};

@@ -178,21 +178,7 @@ __global__ void route_pos_kernel(const int* __restrict__ expert, int S, int E, c
 // Replaces the NCCL all-gather + .cpu() + Python block planner of the reference
 // (mix_moe/csrc/cuda/global_exchange.cpp:139-177, mix_moe/mix_moe/transformer.py:150-250).
 // ---------------------------------------------------------------------------------------------------
-struct PlanArgs {
-  const int* count_kept;               // [E_total] this rank's kept rows per expert
-  int* peer_table[CCF_MAX_RANKS];      // count table [W, E_total] of every rank
-  int* peer_flag[CCF_MAX_RANKS];       // epoch flags [W] of every rank
-  int* dst_base;                       // out [E_total]
-  int* group_base;                     // out [E_loc]
-  int* group_rows;                     // out [E_loc]
-  int* sent_rows;                      // out [W] kept rows this rank sends to each owner
-  int* table_copy;                     // out [W, E_total] snapshot of the table (routing statistics)
-  int* local_begin;                    // out [E_loc] offset of this rank's own rows inside each local expert (optional)
-  int* local_rows;                     // out [E_loc] number of those rows
-  int* status;
-  unsigned long long wait_limit_ns;
-  int world, my_rank, e_total, e_loc, epoch, max_rows;
-};
+using PlanArgs = ::CcfPlanArgs;   // gemm_args.h
 
 __device__ __forceinline__ void plan_body(const PlanArgs& a, const int epoch) {
   __shared__ int rows[CCF_MAX_GROUPS];

@@ -75,6 +75,35 @@ class PlanArgs(C.Structure):
     ]
 
 
+class Layer(C.Structure):
+    """Mirror of CcfLayer (csrc/runtime.h): addresses and sizes of one fused layer for the native runtime."""
+    _fields_ = [
+        ("w1", _vp), ("b1", _vp), ("wg", _vp), ("bg", _vp), ("w2", _vp), ("b2", _vp),
+        ("xrecv", _vp), ("comb", _vp), ("h_act", _vp), ("h_pre", _vp), ("h_pre2", _vp),
+        ("slot_pos", _vp), ("slot_row", _vp), ("sorted_slot", _vp), ("order_off", _vp), ("local_begin", _vp),
+        ("local_rows", _vp), ("count_raw", _vp), ("count_kept", _vp), ("dst_base", _vp), ("group_base", _vp),
+        ("group_rows", _vp), ("sent_rows", _vp), ("table_copy", _vp),
+        ("grecv", _vp), ("gcomb", _vp), ("row_src", _vp), ("row_gate", _vp), ("tile_flags", _vp), ("done", _vp),
+        ("done_cum", _vp), ("block_hist", _vp), ("block_off", _vp), ("ticket", _vp), ("sched", _vp), ("status", _vp),
+        ("epoch_dev", _vp),
+        ("peer_xrecv", _vp * MAX_RANKS), ("peer_comb", _vp * MAX_RANKS), ("peer_grecv", _vp * MAX_RANKS),
+        ("peer_gcomb", _vp * MAX_RANKS), ("peer_row_src", _vp * MAX_RANKS), ("peer_row_gate", _vp * MAX_RANKS),
+        ("peer_tile_flags", _vp * MAX_RANKS), ("peer_cnt_table", _vp * MAX_RANKS), ("peer_cnt_flag", _vp * MAX_RANKS),
+        ("peer_done", _vp * MAX_RANKS),
+        ("wait_limit_ns", C.c_ulonglong),
+        ("d_model", C.c_int), ("d_ffn", C.c_int), ("e_total", C.c_int), ("e_loc", C.c_int), ("top_k", C.c_int),
+        ("world", C.c_int), ("rank", C.c_int), ("act", C.c_int), ("swiglu", C.c_int), ("fp16", C.c_int),
+        ("max_rows", C.c_int), ("max_slots", C.c_int), ("n_comm_ctas", C.c_int), ("two_cta", C.c_int),
+        ("device", C.c_int), ("pad0", C.c_int),
+    ]
+
+
+class LayerGrads(C.Structure):
+    """Mirror of CcfLayerGrads (csrc/runtime.h)."""
+    _fields_ = [("dgate", _vp), ("dh", _vp), ("dh2", _vp), ("dw1", _vp), ("db1", _vp), ("dwg", _vp), ("dbg", _vp),
+                ("dw2", _vp), ("db2", _vp), ("dx", _vp)]
+
+
 _lib = None
 _lock = threading.Lock()
 LAUNCHES = [0]   # kernels of this library launched by this process (bench.py reports the count)
@@ -119,7 +148,8 @@ def load(build_if_missing: bool = True):
         lib = C.CDLL(path)
         _declare(lib)
         for name, struct in (("gemm_args", GemmArgs), ("dispatch_args", DispatchArgs),
-                             ("gemm_launch", GemmLaunch), ("plan_args", PlanArgs)):
+                             ("gemm_launch", GemmLaunch), ("plan_args", PlanArgs), ("layer", Layer),
+                             ("layer_grads", LayerGrads)):
             want = getattr(lib, "ccf_sizeof_" + name)()
             if want != C.sizeof(struct):
                 raise RuntimeError(f"ctypes mirror of {name} is {C.sizeof(struct)} bytes, library has {want}")
@@ -137,6 +167,8 @@ def _declare(lib):
         "ccf_topk_softmax_bwd": ([p, p, p, i, i, i, p, i, i, p], i),
         "ccf_route": ([p, i, i, i, p, p, p, p, p, p, p], i),
         "ccf_route_ordered": ([p, i, i, i, p, p, p, p, p, p, p, p, p, i, p], i),
+        "ccf_layer_forward": ([C.POINTER(Layer), p, p, p, p, i, i, i, i, p, p, i, p], i),
+        "ccf_layer_backward": ([C.POINTER(Layer), p, p, p, C.POINTER(LayerGrads), i, i, p, p, i, p], i),
         "ccf_plan": ([C.POINTER(PlanArgs), p], i),
         "ccf_plan_dev_epoch": ([C.POINTER(PlanArgs), p, p], i),
         "ccf_dispatch": ([C.POINTER(DispatchArgs), p, p, i, p], i),

@@ -209,6 +209,10 @@ class FusedMoE:
         self.check_every_call = bool(env_flag("CHECK_STATUS", 0))
         self.fused_router = bool(env_flag("FUSED_ROUTER", 0))
         self._save_pre = True   # whether the next forward stores the pre-activations (set per call by run_experts)
+        # CCFUSER_NATIVE_RUNTIME=1: one C call per forward / backward (csrc/runtime.cu) instead of one per launch
+        self.native_runtime = bool(env_flag("NATIVE_RUNTIME", 0))
+        self._desc = None
+        self._desc_key = None
 
     # ------------------------------------------------------------------------------------------
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
@@ -263,6 +267,48 @@ class FusedMoE:
         if self.check_every_call:
             self.ctx.check_status("fused MoE forward")
         return y
+
+    def native_desc(self) -> N.Layer:
+        """The layer's description for the native runtime (csrc/runtime.h: CcfLayer). Built once; rebuilt if a parameter
+        tensor has been replaced (its address changed)."""
+        cfg, cc, ex = self.cfg, self.ctx, self.layer.experts
+        swiglu = cfg.activation == "swiglu"
+        params = (ex.htoh4.weight, ex.htoh4.bias, ex.htoh4_gate.weight if swiglu else None,
+                  ex.htoh4_gate.bias if swiglu else None, ex.h4toh.weight, ex.h4toh.bias)
+        key = tuple(N.ptr(t) for t in params)
+        if self._desc is not None and self._desc_key == key:
+            return self._desc
+        L = N.Layer()
+        L.w1, L.b1, L.wg, L.bg, L.w2, L.b2 = key
+        L.xrecv, L.comb = self.xrecv.data_ptr(), self.comb.data_ptr()
+        L.h_act, L.h_pre, L.h_pre2 = self.h_act.data_ptr(), self.h_pre.data_ptr(), N.ptr(self.h_pre2)
+        for name in ("slot_pos", "slot_row", "sorted_slot", "order_off", "local_begin", "local_rows", "count_raw",
+                     "count_kept", "dst_base", "group_base", "group_rows", "sent_rows", "table_copy"):
+            setattr(L, name, getattr(self, name).data_ptr())
+        for name in ("grecv", "gcomb", "row_src", "row_gate", "tile_flags", "done", "done_cum", "block_hist", "block_off",
+                     "ticket", "epoch_dev"):
+            setattr(L, name, getattr(cc, name).data_ptr())
+        L.sched, L.status = cc.ws.sched.data_ptr(), cc.ws.status.data_ptr()
+        peers = {"peer_xrecv": self.buf.peer_ptrs(self.off_xrecv), "peer_comb": self.buf.peer_ptrs(self.off_comb),
+                 "peer_grecv": cc.peer("grecv"), "peer_gcomb": cc.peer("gcomb"), "peer_row_src": cc.peer("row_src"),
+                 "peer_row_gate": cc.peer("row_gate"), "peer_tile_flags": cc.peer("tile_flags"),
+                 "peer_cnt_table": cc.peer("cnt_table"), "peer_cnt_flag": cc.peer("cnt_flag"),
+                 "peer_done": [p + 4 * self.rank for p in cc.peer("done")]}
+        for name, ptrs in peers.items():
+            arr = getattr(L, name)
+            for r in range(self.world):
+                arr[r] = ptrs[r]
+        L.wait_limit_ns = cc.wait_ns
+        L.d_model, L.d_ffn, L.e_total, L.e_loc, L.top_k = cfg.d_model, cfg.d_ffn, cfg.num_experts, cfg.experts_per_rank, cfg.top_k
+        L.world, L.rank = self.world, self.rank
+        L.act, L.swiglu, L.fp16 = N.ACT_CODE[cfg.activation], int(swiglu), int(cfg.dtype == torch.float16)
+        L.max_rows, L.max_slots = self.max_rows, self.max_slots
+        L.n_comm_ctas = min(int(cc.n_comm), 1 << 30)
+        L.two_cta = int(G.TWO_CTA_DEFAULT)
+        L.device = self.device.index if (self.device.type == "cuda" and self.device.index is not None) else (
+            torch.cuda.current_device() if self.device.type == "cuda" else -1)
+        self._desc, self._desc_key = L, key
+        return L
 
     def close(self):
         """Free this layer's symmetric buffers (collective: call on every rank)."""
@@ -428,6 +474,22 @@ class _FusedMoEFn(torch.autograd.Function):
         t, d = x.shape
         idx = idx.contiguous()
         gate_w = gate_w.contiguous()
+        if fm.native_runtime:
+            y = torch.empty(t, d, dtype=x.dtype, device=x.device)
+            cc = fm.ctx
+            if not cc.device_epoch:
+                cc.epoch += 1
+            with nvtx_range("moe.forward_native"):
+                N.check(N.load().ccf_layer_forward(C.byref(fm.native_desc()), x.data_ptr(), idx.data_ptr(), gate_w.data_ptr(),
+                                                   y.data_ptr(), t, cfg.capacity(t), int(fm._save_pre),
+                                                   -1 if cc.device_epoch else cc.epoch, N.stream_ptr(), None, 0, None),
+                        "ccf_layer_forward")
+            N.count(8)   # route (2), plan, GEMM-1, GEMM-2, wait, reduce + the counter reset
+            ctx.fm = fm
+            ctx.tokens = t
+            ctx.save_for_backward(idx, gate_w, w1, wg, w2)
+            ctx.has_bias = (b1 is not None, bg is not None, b2 is not None)
+            return y
         with nvtx_range("moe.route_plan"):
             fm.stage_route_plan(idx, t)
         with nvtx_range("moe.dispatch_gemm1"):
@@ -455,6 +517,24 @@ class _FusedMoEFn(torch.autograd.Function):
         dy = dy.contiguous()
         dgate = torch.zeros(t * cfg.top_k, dtype=torch.float32, device=dy.device)  # dropped slots keep 0
         swiglu = cfg.activation == "swiglu"
+        if fm.native_runtime:
+            has_b1, has_bg, has_b2 = ctx.has_bias
+            mk = lambda like: torch.empty_like(like)                       # noqa: E731
+            bias = lambda n: torch.empty(e_loc, n, dtype=cfg.dtype, device=dy.device)   # noqa: E731
+            g = N.LayerGrads()
+            dh = torch.empty(fm.max_rows, f, dtype=cfg.dtype, device=dy.device)
+            dh2 = torch.empty_like(dh) if swiglu else None
+            dw1, dw2, dwg = mk(w1), mk(w2), (mk(wg) if swiglu else None)
+            db1, db2, dbg = (bias(f) if has_b1 else None), (bias(d) if has_b2 else None), (bias(f) if has_bg else None)
+            dx = torch.empty(t, d, dtype=dy.dtype, device=dy.device)
+            g.dgate, g.dh, g.dh2 = dgate.data_ptr(), dh.data_ptr(), N.ptr(dh2)
+            g.dw1, g.db1, g.dwg, g.dbg, g.dw2, g.db2, g.dx = (N.ptr(v) for v in (dw1, db1, dwg, dbg, dw2, db2, dx))
+            N.check(lib.ccf_layer_backward(C.byref(fm.native_desc()), dy.data_ptr(), idx.data_ptr(), gate_w.data_ptr(),
+                                           C.byref(g), t, cfg.capacity(t), st, None, 0, None), "ccf_layer_backward")
+            N.count(9 + int(has_b1) + int(has_b2) + int(has_bg) + int(swiglu))
+            if fm.check_every_call:
+                cc.check_status("fused MoE backward")
+            return dx, dgate.view(t, cfg.top_k), None, dw1, db1, dwg, dbg, dw2, db2, None
         # 1+2. push g*dy rows (dispatch role) + dgrad-2 with the activation derivative in the epilogue
         disp = fm._dispatch_args(dy, t, idx, gate_w, backward=True, dgate=dgate)
         common = dict(group_base=fm.group_base, group_rows=fm.group_rows, num_groups=e_loc, wait_ns=cc.wait_ns,

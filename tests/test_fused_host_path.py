@@ -1,9 +1,19 @@
 """Host side of the fused path without a GPU: the library calls are recorded instead of run, and the sequence of
 launches and their argument blocks are checked (which kernels, which operands, which epilogues)."""
+import pytest
 import torch
 
 from ccfuser_b200 import MoEConfig, MoELayer
 from ccfuser_b200 import native as N
+
+
+@pytest.fixture(autouse=True)
+def _fresh_context():
+    """Layers of one process share their communication context; these tests change its mode, so each starts clean."""
+    from ccfuser_b200.ops.fused import CommContext
+    CommContext._instances.clear()
+    yield
+    CommContext._instances.clear()
 
 
 def _layer(act="gelu", tokens=256, e=4, d=128, f=256, k=2, **kw):

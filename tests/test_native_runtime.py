@@ -9,6 +9,15 @@ from ccfuser_b200 import MoEConfig, MoELayer
 from ccfuser_b200 import native as N
 
 
+@pytest.fixture(autouse=True)
+def _fresh_context():
+    """Layers of one process share their communication context; these tests change its mode, so each starts clean."""
+    from ccfuser_b200.ops.fused import CommContext
+    CommContext._instances.clear()
+    yield
+    CommContext._instances.clear()
+
+
 def _flat(s, prefix=""):
     out = {}
     for name, _ in s._fields_:

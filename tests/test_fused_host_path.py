@@ -143,3 +143,30 @@ def test_two_rank_peer_pointers_line_up():
             assert seen[key] == [res[0][0][key], res[1][0][key]], key
         # rank r bumps element r of every rank's `done` array
         assert seen["done"] == [res[0][0]["done"] + 4 * r, res[1][0]["done"] + 4 * r]
+
+
+def test_shadow_experts_on_the_fused_host_path():
+    """Replicated experts with the fused backend: their slots reach the kernels as expert id -1, the replicas run in
+    torch, and both parts receive gradients (kernels recorded, so only shapes, dtypes and wiring are checked)."""
+    cfg, layer = _layer("gelu", shadow_experts=1)
+    x = torch.randn(120, cfg.d_model).bfloat16().requires_grad_(True)
+    captured = {}
+    fm = layer._fused_impl()
+    orig = fm.run_experts
+
+    def spy(xx, idx, w):
+        captured["idx"] = idx.clone()
+        return orig(xx, idx, w)
+    fm.run_experts = spy
+    with N.record_launches() as rec:
+        # the recorded top-k kernel leaves its outputs uninitialised: give the router deterministic decisions instead
+        fm.route = lambda xx: (torch.arange(xx.shape[0] * 2, dtype=torch.int32).view(-1, 2) % cfg.num_experts,
+                               torch.full((xx.shape[0], 2), 0.5, requires_grad=True))
+        y = layer(x)
+        y.float().sum().backward()
+    shadow = layer.last_stats["shadow_ids"].tolist()
+    idx = captured["idx"]
+    assert idx.dtype == torch.int32 and (idx == shadow[0]).sum() == 0 and (idx == -1).sum() == 120 * 2 // cfg.num_experts
+    assert rec.names().count("ccf_gemm_launch") == 6
+    assert y.shape == x.shape and y.dtype == torch.bfloat16
+    assert layer.experts.htoh4.weight.grad is not None and x.grad is not None

@@ -170,3 +170,24 @@ def test_shadow_experts_on_the_fused_host_path():
     assert rec.names().count("ccf_gemm_launch") == 6
     assert y.shape == x.shape and y.dtype == torch.bfloat16
     assert layer.experts.htoh4.weight.grad is not None and x.grad is not None
+
+
+def test_gpt_model_with_fused_layers_host_side():
+    """The model the smoke test and the benchmark run, with its MoE layers on the fused backend (kernels recorded)."""
+    from ccfuser_b200.models.gpt_moe import GPTMoE, GPTMoEConfig
+    c = GPTMoEConfig(vocab_size=1024, n_layer=4, n_head=4, d_model=256, d_ffn=512, seq_len=64, num_experts=8,
+                     backend="fused", max_tokens=256)
+    model = GPTMoE(c, device="cpu")
+    ids = torch.randint(0, c.vocab_size, (4, 64))
+    with N.record_launches() as rec:
+        model(ids, ids.roll(-1, 1)).backward()
+    n_moe = len(model.moe_layers())
+    assert n_moe == 2
+    assert rec.names().count("ccf_gemm_launch") == 6 * n_moe
+    assert rec.names().count("ccf_plan") == n_moe and rec.names().count("ccf_topk_softmax_bwd") == n_moe
+    # both layers share one communication context (same group, sizes and dtype) but own their forward buffers
+    a, b = (l._fused_impl() for l in model.moe_layers())
+    assert a.ctx is b.ctx and a.xrecv.data_ptr() != b.xrecv.data_ptr()
+    epochs = [N.PlanArgs.from_buffer_copy(c_[1][0]).epoch for c_ in rec.calls if c_[0] == "ccf_plan"]
+    assert epochs == [1, 2]
+    assert all(p.grad is not None for l in model.moe_layers() for p in l.experts.parameters())

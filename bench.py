@@ -32,6 +32,9 @@ def parse():
     ap.add_argument("--batch", type=int, default=8, help="sequences per GPU")
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--no-layer-bench", action="store_true")
+    ap.add_argument("--rebalance", action="store_true",
+                    help="after the warm-up, move experts between GPUs to the placement planned from the observed routing "
+                         "counts (same model function, less load on the busiest GPU); off by default")
     return ap.parse_args()
 
 
@@ -187,6 +190,17 @@ def main():
     for i in range(args.warmup):
         trainer.step_device(*dev_batches[i % 4])
     sync()
+    moved = None
+    if args.rebalance and args.impl == "ours" and world > 1:
+        # expert placement from the routing counts of the last warm-up step, layer by layer (collective), then one
+        # more untimed step so that the timed region starts from a steady state
+        moved = 0
+        e_loc = c.num_experts // world
+        for m in model.moe_layers():
+            pl = m.rebalance(optimizer=trainer.opt)
+            moved += sum(1 for slot, old in enumerate(pl) if slot // e_loc != old // e_loc)
+        trainer.step_device(*dev_batches[0])
+        sync()
     sampler = ClockSampler(visible_index(local_rank))
     sampler.start()
     launches0 = N.LAUNCHES[0]
@@ -251,7 +265,7 @@ def main():
                        "global_batch": args.batch * world, "seq_len": seq, "parallelism": f"ep{world}" + (f"+dp{world}" if world > 1 else ""),
                        "optimizer": "sgd", "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2",
                        "loss": round(float(loss.detach()), 4), "capacity_factor": None, "max_rank_load_over_balanced": imbalance,
-                       "overflow": overflow},
+                       "overflow": overflow, "experts_moved_by_rebalance": moved},
             "clocks": clocks,
             "e2e": {"value": round(tokens_per_step * args.steps / (ms2 / 1e3), 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": 2 * args.batch * seq * 8, "d2h_bytes_per_step": 4, "last_loss": round(last, 4)},

@@ -157,3 +157,40 @@ def test_shadow_experts_match_the_oracle_and_return_gradients_to_the_owner():
         assert int(table[:, shadow].sum()) == 0
     gate_w = sum(r[2]["gate.gate.weight"] for r in res)
     assert torch.allclose(gate_w, full["gate.weight"].grad, atol=1e-5, rtol=1e-4)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# re-placement inside a training loop (the sequence bench.py --rebalance runs)
+# ---------------------------------------------------------------------------------------------------------------
+def _train_rebalance_fn(rank, world):
+    from ccfuser_b200.models.gpt_moe import GPTMoE, GPTMoEConfig
+    from ccfuser_b200.train import TrainStep
+    torch.manual_seed(0)
+    c = GPTMoEConfig(vocab_size=128, n_layer=4, n_head=2, d_model=32, d_ffn=64, seq_len=16, num_experts=8, top_k=2,
+                     ep_size=world, backend="cpu", max_tokens=64, dtype=torch.float32)
+    model = GPTMoE(c)
+    trainer = TrainStep(model, lr=1e-2, optimizer="sgd")
+    g = torch.Generator().manual_seed(10 + rank)
+    ids = torch.randint(0, 128, (4, 16), generator=g)
+    labels = ids.roll(-1, 1)
+    for _ in range(2):
+        trainer.step_device(ids, labels)
+    with torch.no_grad():
+        before = float(model(ids, labels))
+    moved = 0
+    for m in model.moe_layers():
+        pl = m.rebalance(optimizer=trainer.opt)
+        moved += sum(1 for slot, old in enumerate(pl) if slot // 4 != old // 4)
+    with torch.no_grad():
+        after = float(model(ids, labels))
+    l1 = float(trainer.step_device(ids, labels))
+    l2 = float(trainer.step_device(ids, labels))
+    return before, after, moved, l1, l2
+
+
+def test_rebalance_between_training_steps_keeps_the_loss():
+    res = run_ranks(_train_rebalance_fn, 2)
+    for before, after, moved, l1, l2 in res:
+        assert abs(before - after) < 1e-5
+        assert l2 < l1 + 1e-3                       # training goes on
+    assert res[0][2] == res[1][2]

@@ -103,6 +103,8 @@ def main():
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--optimizer", default="sgd", choices=["sgd", "adamw"])
     ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--rebalance-every", type=int, default=0,
+                    help="every N steps re-place the experts of each MoE layer from its last routing counts (0 = never)")
     ap.add_argument("--save", default="", help="checkpoint prefix written at the end (per-rank expert shards + manifest)")
     ap.add_argument("--resume", default="", help="checkpoint prefix to load before training (any EP degree)")
     args = ap.parse_args()
@@ -129,6 +131,11 @@ def main():
         loss = wrapped(batch)
         loss.backward()
         opt.step()
+        if args.rebalance_every > 0 and args.variant != "dense" and (i + 1) % args.rebalance_every == 0:
+            from ..layers import MoELayer
+            for m in model.modules():
+                if isinstance(m, MoELayer) and m.count_table() is not None:
+                    m.rebalance(optimizer=opt)     # collective; the cost lands in this step's time
         if dev.type == "cuda":
             e.record()
             torch.cuda.synchronize()

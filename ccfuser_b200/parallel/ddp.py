@@ -49,3 +49,31 @@ def allreduce_replicated_grads(model: nn.Module, group=None, average: bool = Tru
         flat.div_(dist.get_world_size(group))
     for g, f in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
         g.copy_(f)
+
+
+def reduce_expert_grads(model: nn.Module, dp_group=None, scale: float = None):
+    """Gradients of the expert parameters when the expert-parallel group is smaller than the job ("EP inside a node, DP
+    over the rest", utils/dist.py: make_ep_dp_groups): every data-parallel replica of an expert has seen only the
+    tokens of its own expert-parallel group, so the replicas' gradients are summed over ``dp_group`` (the ranks that
+    hold the same experts). ``scale`` then multiplies the result; ``1 / world_size`` gives the expert parameters the
+    same mean-over-all-ranks convention that DistributedDataParallel applies to the replicated ones (without it an
+    expert's gradient is the plain sum over the ranks whose tokens it served, which is what the reference's ignore-list
+    set-up leaves, mix_moe/mix_moe/examples/mix_moe_ddp.py:139-152)."""
+    grads = [p.grad for p in model.parameters() if p.grad is not None and getattr(p, "skip_allreduce", False)]
+    if not grads:
+        return
+    replicas = dist.get_world_size(dp_group) if (dist.is_initialized() and dp_group is not None) else 1
+    if replicas > 1:
+        # one flat buffer per dtype keeps this at one or two collectives
+        by_dtype = {}
+        for g in grads:
+            by_dtype.setdefault(g.dtype, []).append(g)
+        for gs in by_dtype.values():
+            flat = torch._utils._flatten_dense_tensors(gs)
+            dist.all_reduce(flat, group=dp_group)
+            if scale is not None:
+                flat.mul_(scale)
+            for g, f in zip(gs, torch._utils._unflatten_dense_tensors(flat, gs)):
+                g.copy_(f)
+    elif scale is not None:
+        torch._foreach_mul_(grads, scale)

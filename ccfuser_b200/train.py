@@ -13,14 +13,20 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from .parallel.ddp import allreduce_replicated_grads, wrap_ddp
+from .parallel.ddp import allreduce_replicated_grads, reduce_expert_grads, wrap_ddp
 
 
 class TrainStep:
     def __init__(self, model: nn.Module, lr: float = 1e-3, optimizer: str = "sgd", dp_group=None,
-                 use_ddp: bool = True, aux_loss: bool = False):
+                 use_ddp: bool = True, aux_loss: bool = False, expert_dp_group=None, mean_expert_grads: bool = False):
+        """``dp_group``: ranks over which the replicated parameters are averaged (default: all). ``expert_dp_group``:
+        ranks that hold replicas of this rank's experts (second value of ``make_ep_dp_groups``) when the expert-parallel
+        group is smaller than the job. ``mean_expert_grads``: scale expert gradients by 1 / world size so that they
+        follow the same mean-over-ranks convention as the replicated parameters."""
         self.raw_model = model
         self.dp_group = dp_group
+        self.expert_dp_group = expert_dp_group
+        self.mean_expert_grads = mean_expert_grads
         self.distributed = dist.is_initialized() and dist.get_world_size(dp_group) > 1
         self.use_ddp = use_ddp and self.distributed
         self.model = wrap_ddp(model, dp_group) if self.use_ddp else model
@@ -50,6 +56,9 @@ class TrainStep:
         loss.backward()
         if self.distributed and not self.use_ddp:
             allreduce_replicated_grads(self.raw_model, self.dp_group)
+        if self.expert_dp_group is not None or self.mean_expert_grads:
+            scale = 1.0 / dist.get_world_size(self.dp_group) if (self.mean_expert_grads and dist.is_initialized()) else None
+            reduce_expert_grads(self.raw_model, self.expert_dp_group, scale)
         self.opt.step()
         return loss.detach()
 

@@ -79,3 +79,44 @@ def test_lm_iterator_and_checkpoint_resume(tmp_path):
         sys.argv = old
     import os
     assert os.path.exists(prefix + ".manifest.json") and os.path.exists(prefix + ".ep0of1.pt")
+
+
+def _ep_dp_rank(rank, world):
+    """4 ranks = 2 expert-parallel groups of 2 (ranks {0,1} and {2,3}) x 2 data-parallel replicas of every expert."""
+    from ccfuser_b200 import MoEConfig, MoELayer
+    from ccfuser_b200.parallel.ddp import allreduce_replicated_grads, reduce_expert_grads
+    from ccfuser_b200.utils.dist import make_ep_dp_groups
+    from tests.test_cpu_layer import _full_params, _inputs, load_shard
+    ep_group, dp_group = make_ep_dp_groups(2)
+    cfg = MoEConfig(d_model=32, d_ffn=64, num_experts=4, top_k=2, capacity_factor=None, activation="gelu",
+                    dtype=torch.float32, ep_size=2, backend="cpu", max_tokens=64)
+    layer = MoELayer(cfg, ep_group=ep_group)
+    assert layer.ep_rank == rank % 2
+    load_shard(layer, _full_params(cfg, 0), layer.ep_rank)
+    x = _inputs(world, 64, 32)[rank]
+    y = layer(x)
+    (y * torch.linspace(-1, 1, y.numel()).view_as(y)).sum().backward()
+    allreduce_replicated_grads(layer, None, average=True)          # router: mean over all 4 ranks
+    reduce_expert_grads(layer, dp_group, scale=1.0 / world)         # experts: sum over the 2 replicas, same convention
+    return {n: p.grad.clone() for n, p in layer.named_parameters()}, dist.get_process_group_ranks(dp_group)
+
+
+def test_expert_parallel_inside_data_parallel():
+    from ccfuser_b200 import MoEConfig
+    from ccfuser_b200.ops.reference import dense_moe_oracle
+    from tests.test_cpu_layer import _full_params, _inputs
+    world = 4
+    res = run_ranks(_ep_dp_rank, world)
+    cfg = MoEConfig(d_model=32, d_ffn=64, num_experts=4, top_k=2, capacity_factor=None, activation="gelu", dtype=torch.float32)
+    full = {k: v.clone().requires_grad_(True) for k, v in _full_params(cfg, 0).items()}
+    xs = _inputs(world, 64, 32)
+    ys = dense_moe_oracle(xs, full, top_k=2, capacity=None, activation="gelu")
+    (sum((y * torch.linspace(-1, 1, y.numel()).view_as(y)).sum() for y in ys) / world).backward()
+    assert [res[r][1] for r in range(4)] == [[0, 2], [1, 3], [0, 2], [1, 3]]
+    for r in range(world):
+        grads = res[r][0]
+        sl = slice((r % 2) * 2, (r % 2) * 2 + 2)
+        assert torch.allclose(grads["gate.gate.weight"], full["gate.weight"].grad, atol=1e-6, rtol=1e-4)
+        for name in ("htoh4", "h4toh"):
+            assert torch.allclose(grads[f"experts.{name}.weight"], full[name + ".weight"].grad[sl], atol=1e-6, rtol=1e-4)
+            assert torch.allclose(grads[f"experts.{name}.bias"], full[name + ".bias"].grad[sl], atol=1e-6, rtol=1e-4)

@@ -55,7 +55,8 @@ class _TXLStep(nn.Module):
         return loss
 
 
-def build(args, world, dev):
+def build(args, world, dev, ep_group=None):
+    """``world`` is the size of the expert-parallel group (the whole job unless --ep-size says otherwise)."""
     backend = {"dense": "auto", "nccl": "nccl", "fused": "fused"}[args.variant]
     moe = args.variant != "dense"
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
@@ -65,7 +66,7 @@ def build(args, world, dev):
         c = GPTMoEConfig(n_layer=args.layers or 12, n_head=12, d_model=768, d_ffn=3072, seq_len=s,
                          moe_every=(args.moe_every if moe else 0), num_experts=args.experts_per_gpu * world, top_k=args.top_k,
                          capacity_factor=args.cf or None, ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
-        model = _GPTStep(GPTMoE(c, device=dev))
+        model = _GPTStep(GPTMoE(c, ep_group=ep_group, device=dev))
         ids = torch.randint(0, c.vocab_size, (b, s), generator=g)
         batch = {"ids": ids, "labels": ids.roll(-1, 1)}
     elif args.model == "bert":
@@ -73,7 +74,7 @@ def build(args, world, dev):
         c = BertMoEConfig(n_layer=args.layers or 12, moe_layers=(2, 5, 8, 11) if moe else (), max_position=s,
                           num_experts=args.experts_per_gpu * world, top_k=args.top_k, capacity_factor=args.cf or None,
                           ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
-        model = _BertStep(BertMoEForQuestionAnswering(c, device=dev))
+        model = _BertStep(BertMoEForQuestionAnswering(c, ep_group=ep_group, device=dev))
         batch = {"ids": torch.randint(0, c.vocab_size, (b, s), generator=g), "mask": torch.ones(b, s, dtype=torch.long),
                  "types": torch.zeros(b, s, dtype=torch.long), "start": torch.randint(0, s, (b,), generator=g),
                  "end": torch.randint(0, s, (b,), generator=g)}
@@ -82,7 +83,7 @@ def build(args, world, dev):
         c = TransformerXLMoEConfig(n_layer=args.layers or 12, tgt_len=s, mem_len=s, moe=moe,
                                    num_experts=args.experts_per_gpu * world, top_k=args.top_k,
                                    capacity_factor=args.cf or None, ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
-        model = _TXLStep(TransformerXLMoE(c, device=dev))
+        model = _TXLStep(TransformerXLMoE(c, ep_group=ep_group, device=dev))
         batch = {"ids": torch.randint(1, 50, (b, s), generator=g), "labels": torch.randint(1, 50, (b, s), generator=g)}
     return model, {k: v.to(dev) for k, v in batch.items()}, b * s
 
@@ -103,6 +104,8 @@ def main():
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--optimizer", default="sgd", choices=["sgd", "adamw"])
     ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--ep-size", type=int, default=0,
+                    help="ranks per expert-parallel group (default: all); the groups are data-parallel replicas of each other")
     ap.add_argument("--rebalance-every", type=int, default=0,
                     help="every N steps re-place the experts of each MoE layer from its last routing counts (0 = never)")
     ap.add_argument("--save", default="", help="checkpoint prefix written at the end (per-rank expert shards + manifest)")
@@ -110,10 +113,15 @@ def main():
     args = ap.parse_args()
     rank, _, world = init_distributed()
     dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
-    model, batch, tokens = build(args, world, dev)
+    ep_size = args.ep_size or world
+    ep_group = expert_dp_group = None
+    if ep_size != world:
+        from ..utils.dist import make_ep_dp_groups
+        ep_group, expert_dp_group = make_ep_dp_groups(ep_size)
+    model, batch, tokens = build(args, ep_size, dev, ep_group)
     if args.resume:
         from ..utils.checkpoint import load_ep_checkpoint
-        load_ep_checkpoint(model, args.resume, rank, world)
+        load_ep_checkpoint(model, args.resume, rank % ep_size, ep_size)
     wrapped = wrap_ddp(model) if world > 1 else model
     params = [p for p in model.parameters() if p.requires_grad]
     opt = torch.optim.SGD(params, lr=args.lr) if args.optimizer == "sgd" else torch.optim.AdamW(params, lr=args.lr)
@@ -130,6 +138,9 @@ def main():
         opt.zero_grad(set_to_none=True)
         loss = wrapped(batch)
         loss.backward()
+        if expert_dp_group is not None and args.variant != "dense":
+            from ..parallel.ddp import reduce_expert_grads
+            reduce_expert_grads(model, expert_dp_group, scale=1.0 / world)   # replicas of an expert agree again
         opt.step()
         if args.rebalance_every > 0 and args.variant != "dense" and (i + 1) % args.rebalance_every == 0:
             from ..layers import MoELayer
@@ -157,7 +168,8 @@ def main():
                           "tokens_per_s": round(tokens * world / float(t) * 1e3, 1), "final_loss": round(float(loss.detach()), 4)}))
     if args.save:
         from ..utils.checkpoint import save_ep_checkpoint
-        save_ep_checkpoint(model, args.save, rank, world, extra={"model": args.model, "variant": args.variant})
+        if rank < ep_size:   # the other expert-parallel groups hold copies of the same shards
+            save_ep_checkpoint(model, args.save, rank, ep_size, extra={"model": args.model, "variant": args.variant})
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

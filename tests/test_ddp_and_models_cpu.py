@@ -120,3 +120,20 @@ def test_expert_parallel_inside_data_parallel():
         for name in ("htoh4", "h4toh"):
             assert torch.allclose(grads[f"experts.{name}.weight"], full[name + ".weight"].grad[sl], atol=1e-6, rtol=1e-4)
             assert torch.allclose(grads[f"experts.{name}.bias"], full[name + ".bias"].grad[sl], atol=1e-6, rtol=1e-4)
+
+
+def test_example_trainer_with_two_expert_parallel_groups():
+    """4 CPU ranks as 2 expert-parallel groups x 2 replicas through the example trainer's command line."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", "29653", "-m", "ccfuser_b200.examples.train", "--model", "gpt", "--variant", "nccl", "--ep-size", "2",
+           "--steps", "2", "--warmup", "0", "--layers", "2", "--batch", "2", "--seq", "16", "--experts-per-gpu", "2"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    out = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
+    rec = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")][-1]
+    assert rec["n_gpus"] == 4 and rec["final_loss"] == rec["final_loss"]      # finite

@@ -121,9 +121,12 @@ class MoELayer(nn.Module):
         return self._fused.routing_stats() if self._fused is not None else {}
 
     def check_status(self):
-        """Host read of the fused kernels' status word; raises MoECommTimeout / MoEOverflow / MoECommError."""
+        """Host read of the fused kernels' status word; raises MoECommTimeout / MoEOverflow / MoECommError. With
+        CCFUSER_CANARY=1 the guard regions around the symmetric buffers are verified as well."""
         if self._fused is not None:
             self._fused.ctx.check_status("MoELayer")
+            if self._fused.ctx.guard:
+                self._fused.ctx.check_canaries(extra=(self._fused.buf,))
 
     def release(self):
         """Free the symmetric buffers of the fused path (collective)."""

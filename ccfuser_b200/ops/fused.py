@@ -66,8 +66,10 @@ class CommContext:
             "cnt_flag": N.MAX_RANKS * 4,
             "done": N.MAX_RANKS * 4,
         }
-        total = sum(_round_up(v, 1024) for v in sizes.values()) + 1024
-        self.buf = SymmBuffer(total, group if world > 1 else None, device)
+        # CCFUSER_CANARY=1 (debug): a guard region after every symmetric sub-buffer, verified by check_canaries()
+        self.guard = 1024 if env_flag("CANARY", 0) else 0
+        total = sum(_round_up(v, 1024) + self.guard for v in sizes.values()) + 1024
+        self.buf = SymmBuffer(total, group if world > 1 else None, device, guard=self.guard)
         self.off = {k: self.buf.carve(v) for k, v in sizes.items()}
         v = self.buf.view
         self.grecv = v(self.off["grecv"], (max_rows, d_model), dtype)
@@ -108,6 +110,16 @@ class CommContext:
 
     def peer(self, name: str):
         return self.buf.peer_ptrs(self.off[name])
+
+    def check_canaries(self, extra=()):
+        """Debug (CCFUSER_CANARY=1): raise MoECommError if a write ran past the end of a symmetric sub-buffer of this
+        context or of the buffers in ``extra``. Reads device memory, so it synchronises."""
+        from ..errors import MoECommError
+        for buf in (self.buf,) + tuple(extra):
+            bad = buf.check_guards()
+            if bad:
+                raise MoECommError(f"guard region overwritten at byte offsets {bad} of a symmetric buffer "
+                                   f"(rank {self.rank}): a kernel wrote past the end of a sub-buffer")
 
     def use_device_epoch(self):
         """Move the call epoch into device memory (collective in effect: all ranks of the group at the same call)."""
@@ -180,8 +192,9 @@ class FusedMoE:
         # rows of the context may exceed this layer's bound (shared with bigger layers)
         self.max_rows = self.ctx.max_rows
         self.max_slots = self.ctx.max_slots
-        nbytes = _round_up(self.max_rows * cfg.d_model * 2, 1024) + _round_up(self.max_slots * cfg.d_model * 2, 1024)
-        self.buf = SymmBuffer(nbytes, group, self.device)
+        nbytes = (_round_up(self.max_rows * cfg.d_model * 2, 1024) + _round_up(self.max_slots * cfg.d_model * 2, 1024)
+                  + 2 * self.ctx.guard)
+        self.buf = SymmBuffer(nbytes, group, self.device, guard=self.ctx.guard)
         self.off_xrecv = self.buf.carve(self.max_rows * cfg.d_model * 2)
         self.off_comb = self.buf.carve(self.max_slots * cfg.d_model * 2)
         self.xrecv = self.buf.view(self.off_xrecv, (self.max_rows, cfg.d_model), cfg.dtype)

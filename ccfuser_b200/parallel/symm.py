@@ -54,8 +54,14 @@ class SymmBuffer:
     """One symmetric allocation. ``local`` is a uint8 tensor over this rank's memory; ``peer_ptr(r)``
     is the address at which rank r's copy is mapped in this process."""
 
-    def __init__(self, nbytes: int, group=None, device=None):
+    GUARD_BYTE = 0xA5
+
+    def __init__(self, nbytes: int, group=None, device=None, guard: int = 0):
+        """``guard`` > 0 (debug): every carved range is followed by that many bytes filled with a fixed pattern that
+        no kernel may touch; ``check_guards()`` tells whether a write ran past the end of a range."""
         lib = N.load()
+        self.guard = int(guard)
+        self._guards: List[int] = []
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not None) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
@@ -109,10 +115,22 @@ class SymmBuffer:
     def carve(self, nbytes: int, align: int = 1024) -> int:
         """Bump-allocate a sub-range; every rank must carve in the same order. Returns the byte offset."""
         off = (self._cursor + align - 1) // align * align
-        if off + nbytes > self.nbytes:
-            raise MemoryError(f"symmetric buffer exhausted ({off + nbytes} > {self.nbytes})")
+        if off + nbytes + self.guard > self.nbytes:
+            raise MemoryError(f"symmetric buffer exhausted ({off + nbytes + self.guard} > {self.nbytes})")
         self._cursor = off + nbytes
+        if self.guard:
+            self.local[self._cursor:self._cursor + self.guard].fill_(self.GUARD_BYTE)
+            self._guards.append(self._cursor)
+            self._cursor += self.guard
         return off
+
+    def check_guards(self) -> List[int]:
+        """Byte offsets of guard regions whose pattern has been overwritten (synchronises with the device)."""
+        bad = []
+        for off in self._guards:
+            if not bool((self.local[off:off + self.guard] == self.GUARD_BYTE).all()):
+                bad.append(off)
+        return bad
 
     def view(self, offset: int, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         n = 1

@@ -191,3 +191,17 @@ def test_gpt_model_with_fused_layers_host_side():
     epochs = [N.PlanArgs.from_buffer_copy(c_[1][0]).epoch for c_ in rec.calls if c_[0] == "ccf_plan"]
     assert epochs == [1, 2]
     assert all(p.grad is not None for l in model.moe_layers() for p in l.experts.parameters())
+
+
+def test_canary_guards_detect_an_overrun(monkeypatch):
+    from ccfuser_b200 import MoECommError
+    monkeypatch.setenv("CCFUSER_CANARY", "1")
+    cfg, layer = _layer("gelu")
+    fm = layer._fused_impl()
+    assert fm.ctx.guard == 1024 and len(fm.ctx.buf._guards) == 8 and len(fm.buf._guards) == 2
+    layer.check_status()                                            # clean
+    # a write one element past the end of the forward receive buffer
+    end = fm.off_xrecv + fm.max_rows * cfg.d_model * 2
+    fm.buf.local[end] = 0
+    with pytest.raises(MoECommError, match="guard region"):
+        layer.check_status()

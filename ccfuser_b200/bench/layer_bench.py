@@ -106,6 +106,7 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
            "d_ffn": args.d_ffn, "experts_per_gpu": experts_per_gpu, "top_k": args.top_k, "act": args.act, "cf": args.cf,
            "zipf": args.zipf, "dtype": args.dtype, "cuda_graph": graphed is not None, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
            "total_ms": round(total_ms, 4), "tflops_per_gpu": round(flops / total_ms / 1e9, 1),
+           "nvlink_bytes_per_gpu": int(nv_bytes), "roofline_ms": round(roof_ms, 4),
            "roofline_frac_of_" + src: round(roof_ms / total_ms, 3), **stats}
     layer.release()
     del layer

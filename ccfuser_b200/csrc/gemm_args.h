@@ -138,3 +138,11 @@ struct CcfPlanArgs {
   unsigned long long wait_limit_ns;
   int world, my_rank, e_total, e_loc, epoch, max_rows;
 };
+
+// Arguments of the on-stream barrier over the ranks of a group (ccf_flag_barrier).
+struct CcfBarrierArgs {
+  int* peer_flag[CCF_MAX_RANKS];   // barrier flags [W] of every rank; rank r writes element r everywhere
+  int* status;
+  unsigned long long wait_limit_ns;
+  int world, my_rank, epoch, pad0;
+};

@@ -401,6 +401,23 @@ __global__ void __launch_bounds__(256) sgd_step_kernel(void* p, const void* g, l
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// On-stream barrier of the ranks of a group: everything this rank issued before it on the stream is complete and
+// visible at system scope before any rank passes. One warp; rank r stores the call's epoch into element r of every
+// rank's flag array and waits (bounded) until its own array holds the epoch in every element. Not on the layer's hot
+// path (tile counters and completion counters order the data there); meant for set-up, tear-down and for users who
+// recycle buffers themselves. Stands in for nvshmemx_barrier_all_on_stream (mix_moe/csrc/mix_moe.h:271,336,420,467).
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32) flag_barrier_kernel(const __grid_constant__ CcfBarrierArgs a) {
+  const int tid = threadIdx.x;
+  __threadfence_system();
+  if (tid < a.world) st_release_sys(a.peer_flag[tid] + a.my_rank, a.epoch);
+  if (tid < a.world) {
+    if (!wait_flag_ge(a.peer_flag[a.my_rank] + tid, a.epoch, fail_fast_limit(a.status, a.wait_limit_ns)))
+      report_status(a.status, CCF_ERR_FLAG_TIMEOUT, 0x900000 | tid);
+  }
+}
+
 // A wait that nothing satisfies unless `flag` already holds `target`: used to exercise the timeout path.
 __global__ void wait_probe_kernel(const int* flag, int target, unsigned long long limit_ns, int* status) {
   if (!wait_flag_ge(flag, target, limit_ns)) report_status(status, CCF_ERR_FLAG_TIMEOUT, 0x123);
@@ -526,6 +543,14 @@ int ccf_sgd_step(void* p, const void* g, long long n, float lr, float wd, int fp
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 16) blocks = 148 * 16;
   ccf::sgd_step_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p, g, n, lr, wd, fp16);
+  return last_err();
+}
+
+int ccf_sizeof_barrier_args() { return static_cast<int>(sizeof(CcfBarrierArgs)); }
+
+int ccf_flag_barrier(const CcfBarrierArgs* a, void* stream) {
+  if (a->world < 1 || a->world > CCF_MAX_RANKS || a->my_rank < 0 || a->my_rank >= a->world) return -2;
+  ccf::flag_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
   return last_err();
 }
 

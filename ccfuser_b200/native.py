@@ -75,6 +75,11 @@ class PlanArgs(C.Structure):
     ]
 
 
+class BarrierArgs(C.Structure):
+    _fields_ = [("peer_flag", _vp * MAX_RANKS), ("status", _vp), ("wait_limit_ns", C.c_ulonglong),
+                ("world", C.c_int), ("my_rank", C.c_int), ("epoch", C.c_int), ("pad0", C.c_int)]
+
+
 class Layer(C.Structure):
     """Mirror of CcfLayer (csrc/runtime.h): addresses and sizes of one fused layer for the native runtime."""
     _fields_ = [
@@ -149,7 +154,7 @@ def load(build_if_missing: bool = True):
         _declare(lib)
         for name, struct in (("gemm_args", GemmArgs), ("dispatch_args", DispatchArgs),
                              ("gemm_launch", GemmLaunch), ("plan_args", PlanArgs), ("layer", Layer),
-                             ("layer_grads", LayerGrads)):
+                             ("layer_grads", LayerGrads), ("barrier_args", BarrierArgs)):
             want = getattr(lib, "ccf_sizeof_" + name)()
             if want != C.sizeof(struct):
                 raise RuntimeError(f"ctypes mirror of {name} is {C.sizeof(struct)} bytes, library has {want}")
@@ -169,6 +174,7 @@ def _declare(lib):
         "ccf_route_ordered": ([p, i, i, i, p, p, p, p, p, p, p, p, p, i, p], i),
         "ccf_layer_forward": ([C.POINTER(Layer), p, p, p, p, i, i, i, i, p, p, i, p], i),
         "ccf_layer_backward": ([C.POINTER(Layer), p, p, p, C.POINTER(LayerGrads), i, i, p, p, i, p], i),
+        "ccf_flag_barrier": ([C.POINTER(BarrierArgs), p], i),
         "ccf_plan": ([C.POINTER(PlanArgs), p], i),
         "ccf_plan_dev_epoch": ([C.POINTER(PlanArgs), p, p], i),
         "ccf_dispatch": ([C.POINTER(DispatchArgs), p, p, i, p], i),

@@ -65,6 +65,7 @@ class CommContext:
             "cnt_table": world * e_total * 4,
             "cnt_flag": N.MAX_RANKS * 4,
             "done": N.MAX_RANKS * 4,
+            "bar_flag": N.MAX_RANKS * 4,
         }
         # CCFUSER_CANARY=1 (debug): a guard region after every symmetric sub-buffer, verified by check_canaries()
         self.guard = 1024 if env_flag("CANARY", 0) else 0
@@ -81,6 +82,7 @@ class CommContext:
         self.cnt_flag = v(self.off["cnt_flag"], (N.MAX_RANKS,), torch.int32)
         self.done = v(self.off["done"], (N.MAX_RANKS,), torch.int32)
         self.done_cum = torch.zeros(N.MAX_RANKS, dtype=torch.int32, device=device)
+        self.bar_epoch = 0
         self.epoch = 0
         # The epoch can also live on the device (advanced by the plan kernel itself): needed when calls are replayed
         # from a CUDA graph, whose launch arguments are frozen. Switched on by GraphedForward or CCFUSER_DEVICE_EPOCH=1;
@@ -110,6 +112,19 @@ class CommContext:
 
     def peer(self, name: str):
         return self.buf.peer_ptrs(self.off[name])
+
+    def device_barrier(self):
+        """On-stream barrier over the ranks of this context's group (collective): returns at once on the host; work
+        queued on the stream after it starts only when every rank's stream has reached its barrier. Bounded like every
+        device wait: a missing rank ends it with a time-out status instead of a hang."""
+        self.bar_epoch += 1
+        a = N.BarrierArgs()
+        for r, p in enumerate(self.peer("bar_flag")):
+            a.peer_flag[r] = p
+        a.status, a.wait_limit_ns = self.ws.status.data_ptr(), self.wait_ns
+        a.world, a.my_rank, a.epoch = self.world, self.rank, self.bar_epoch
+        N.check(N.load().ccf_flag_barrier(C.byref(a), N.stream_ptr()), "ccf_flag_barrier")
+        N.count(1)
 
     def check_canaries(self, extra=()):
         """Debug (CCFUSER_CANARY=1): raise MoECommError if a write ran past the end of a symmetric sub-buffer of this

@@ -84,6 +84,12 @@ def main():
     assert sorted(planned) == list(range(e))
     assert float(ok.float().mean()) > 0.9
     assert rel(y1[ok], y0[ok]) < 1e-2 and rel(y2[ok], y0[ok]) < 1e-2, (rel(y1[ok], y0[ok]), rel(y2[ok], y0[ok]))
+    # ---- on-stream barrier of the group ------------------------------------------------------------------------
+    cc = plain._fused_impl().ctx
+    for _ in range(3):
+        cc.device_barrier()
+    torch.cuda.synchronize()
+    plain.check_status()
     plain.release()
     dist.barrier()
     if rank == 0:

@@ -198,10 +198,22 @@ def test_canary_guards_detect_an_overrun(monkeypatch):
     monkeypatch.setenv("CCFUSER_CANARY", "1")
     cfg, layer = _layer("gelu")
     fm = layer._fused_impl()
-    assert fm.ctx.guard == 1024 and len(fm.ctx.buf._guards) == 8 and len(fm.buf._guards) == 2
+    assert fm.ctx.guard == 1024 and len(fm.ctx.buf._guards) == 9 and len(fm.buf._guards) == 2
     layer.check_status()                                            # clean
     # a write one element past the end of the forward receive buffer
     end = fm.off_xrecv + fm.max_rows * cfg.d_model * 2
     fm.buf.local[end] = 0
     with pytest.raises(MoECommError, match="guard region"):
         layer.check_status()
+
+
+def test_device_barrier_arguments():
+    cfg, layer = _layer("gelu")
+    cc = layer._fused_impl().ctx
+    with N.record_launches() as rec:
+        cc.device_barrier()
+        cc.device_barrier()
+    a, b = (N.BarrierArgs.from_buffer_copy(c[1][0]) for c in rec.calls)
+    assert rec.names() == ["ccf_flag_barrier"] * 2
+    assert (a.world, a.my_rank, a.epoch, b.epoch) == (1, 0, 1, 2)
+    assert a.peer_flag[0] == cc.buf.peer_ptr(0, cc.off["bar_flag"]) and a.status == cc.ws.status.data_ptr()

@@ -29,7 +29,8 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
     cfg = MoEConfig(d_model=args.d_model, d_ffn=args.d_ffn, num_experts=experts_per_gpu * world, top_k=args.top_k,
                     capacity_factor=args.cf if args.cf > 0 else None, activation=args.act, bias=not args.no_bias,
-                    dtype=dtype, ep_size=world, backend=backend, max_tokens=tokens, recv_factor=args.recv_factor)
+                    dtype=dtype, ep_size=world, backend=backend, max_tokens=tokens, recv_factor=args.recv_factor,
+                    shadow_experts=args.shadow)
     layer = MoELayer(cfg, device="cuda")
     with torch.no_grad():
         for p in layer.parameters():
@@ -104,7 +105,7 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
     roof_ms = max(flops / (peak * 1e9), nv_bytes / (NVLINK_GBS * 1e6))
     out = {"bench": "moe_layer", "backend": backend, "n_gpus": world, "tokens_per_gpu": tokens, "d_model": args.d_model,
            "d_ffn": args.d_ffn, "experts_per_gpu": experts_per_gpu, "top_k": args.top_k, "act": args.act, "cf": args.cf,
-           "zipf": args.zipf, "dtype": args.dtype, "cuda_graph": graphed is not None, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
+           "zipf": args.zipf, "shadow_experts": args.shadow, "dtype": args.dtype, "cuda_graph": graphed is not None, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
            "total_ms": round(total_ms, 4), "tflops_per_gpu": round(flops / total_ms / 1e9, 1),
            "nvlink_bytes_per_gpu": int(nv_bytes), "roofline_ms": round(roof_ms, 4),
            "roofline_frac_of_" + src: round(roof_ms / total_ms, 3), **stats}
@@ -128,6 +129,7 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
     ap.add_argument("--zipf", type=float, default=0.0, help="Zipf exponent of expert popularity (router bias); 0 = off")
     ap.add_argument("--zipf-scale", type=float, default=1.0)
+    ap.add_argument("--shadow", type=int, default=0, help="replicate the n most popular experts of every step on all ranks")
     ap.add_argument("--backends", default="fused", help="comma list of fused,nccl")
     ap.add_argument("--forward-only", action="store_true")
     ap.add_argument("--graph", action="store_true", help="with --forward-only: replay the fused forward from a CUDA graph")

@@ -217,3 +217,28 @@ def test_device_barrier_arguments():
     assert rec.names() == ["ccf_flag_barrier"] * 2
     assert (a.world, a.my_rank, a.epoch, b.epoch) == (1, 0, 1, 2)
     assert a.peer_flag[0] == cc.buf.peer_ptr(0, cc.off["bar_flag"]) and a.status == cc.ws.status.data_ptr()
+
+
+def _rebalance_bf16_fn(rank, world):
+    import torch.distributed as dist
+    cfg = MoEConfig(d_model=128, d_ffn=256, num_experts=4, top_k=2, activation="swiglu", dtype=torch.bfloat16,
+                    ep_size=world, backend="fused", max_tokens=128)
+    layer = MoELayer(cfg, device="cpu")
+    fm = layer._fused_impl()
+    desc_before = bytes(fm.native_desc())
+    w = layer.experts.htoh4_gate.weight.detach().clone()
+    allw = [torch.empty_like(w) for _ in range(world)]
+    dist.all_gather(allw, w.float().contiguous().to(torch.float32).bfloat16())
+    gate_before = layer.gate.gate.weight.detach().clone()
+    placement = [3, 1, 2, 0]                                      # experts 0 and 3 swap ranks
+    layer.rebalance(placement)
+    full = torch.cat(allw, 0)
+    want = full[torch.tensor(placement)][rank * 2:(rank + 1) * 2]
+    ok_w = torch.equal(layer.experts.htoh4_gate.weight.detach(), want)
+    ok_g = torch.equal(layer.gate.gate.weight.detach(), gate_before[torch.tensor(placement)])
+    return ok_w, ok_g, bytes(fm.native_desc()) == desc_before
+
+
+def test_bf16_experts_migrate_between_ranks_and_kernel_pointers_stay_valid():
+    from tests.mp_util import run_ranks
+    assert run_ranks(_rebalance_bf16_fn, 2) == [(True, True, True)] * 2

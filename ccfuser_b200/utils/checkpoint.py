@@ -69,3 +69,16 @@ def load_ep_checkpoint(model: nn.Module, prefix: str, ep_rank: int, ep_size: int
     state.update(experts)
     model.load_state_dict(state, strict=strict)
     return manifest
+
+
+def import_reference_state(state: Dict[str, torch.Tensor], experts_per_rank: int) -> Dict[str, torch.Tensor]:
+    """Adapt a ``state_dict`` written by the reference package. Its expert tensors carry three extra leading rows, the
+    never-synchronised "popular expert" slots (``_Expert(num_local_expert + 3, ...)``,
+    mix_moe/mix_moe/transformer.py:449-453); every tensor under an ``experts.`` key whose first dimension exceeds
+    ``experts_per_rank`` is cut back to the real experts. Other entries are passed through."""
+    out = {}
+    for k, v in state.items():
+        if ".experts." in "." + k and torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] > experts_per_rank:
+            v = v[:experts_per_rank].clone()
+        out[k] = v
+    return out

@@ -71,3 +71,16 @@ def test_expert_parallel_group_must_share_a_machine():
     check_same_host([host_id()] * 8)
     with pytest.raises(RuntimeError, match="one machine"):
         check_same_host(["node-a/1", "node-a/1", "node-b/2", "node-b/2"])
+
+
+def test_import_of_a_reference_state_dict_drops_the_shadow_slots():
+    import torch
+    from ccfuser_b200 import MoEConfig, MoELayer
+    from ccfuser_b200.utils.checkpoint import import_reference_state
+    layer = MoELayer(MoEConfig(d_model=16, d_ffn=32, num_experts=4, dtype=torch.float32, backend="cpu"))
+    ref = {k: (torch.cat([v, torch.randn(3, *v.shape[1:])], 0) if k.startswith("experts.") else v.clone())
+           for k, v in layer.state_dict().items()}
+    assert ref["experts.htoh4.weight"].shape == (7, 32, 16)
+    state = import_reference_state(ref, 4)
+    layer.load_state_dict(state)
+    assert torch.equal(layer.experts.htoh4.weight, ref["experts.htoh4.weight"][:4])

@@ -144,3 +144,25 @@ def test_checkpoint_reshard_round_trip(tmp_path):
     third = MoELayer(cfg)
     load_ep_checkpoint(third, prefix + "4", 0, 1)
     assert torch.equal(full(x), third(x))
+
+
+def test_protocol_model_all_interleavings_are_safe():
+    """Exhaustive exploration of the abstract protocol: forward passes exchange counts, backward passes do not."""
+    from ccfuser_b200.parallel.protocol_model import check
+    assert check(world=2, calls=4, chunks=2) > 100
+    assert check(world=3, calls=4, chunks=1) > 1000
+    assert check(world=4, calls=2, chunks=1) > 10000
+    # uneven traffic, including a pair that exchanges nothing
+    assert check(world=3, calls=2, chunks=1, rows=[[2, 0, 1], [0, 3, 1], [1, 1, 0]]) > 500
+    # every call planned (inference: forward passes only) and no call planned after the first
+    assert check(world=2, calls=3, chunks=1, plan_every=1) > 50
+    assert check(world=2, calls=3, chunks=1, plan_every=100) > 50
+
+
+def test_protocol_model_finds_the_hazards_of_broken_variants():
+    import pytest
+    from ccfuser_b200.parallel.protocol_model import ProtocolViolation, check
+    for variant, what in (("token_before_store", "still uses the buffers"), ("no_token", "still uses the buffers"),
+                          ("absolute_targets", "before owner"), ("reset_after_finish", "arrival is lost")):
+        with pytest.raises(ProtocolViolation, match=what):
+            check(world=2, calls=2, chunks=1, variant=variant)

@@ -50,10 +50,23 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
     counters and the finish token are the only ordering between ranks). ``rows[r][o]`` = rows rank r sends to owner o per call (default 1 + (r + o) % 2 per
     chunk-able unit, scaled by ``chunks``). Variants: 'correct'; 'token_before_store' (finish token sent before the
     results); 'no_token' (sources wait for rows only); 'absolute_targets' (targets not cumulative);
-    'reset_after_finish' (arrival counters cleared after the finish token instead of before)."""
+    'reset_after_finish' (arrival counters cleared after the finish token instead of before); 'split_token' (a proposed
+    refinement, see the code: token in its own counter, checked per owner just before the next push)."""
     if rows is None:
         rows = [[chunks * (1 + (r + o) % 2) for o in range(world)] for r in range(world)]
     prog = _program(world, chunks)
+    if variant == "split_token":
+        # Proposed refinement: the finish token travels in a counter of its own. A source waits only for its rows before
+        # its reduce, and checks an owner's token just before it next pushes rows to that owner; the owner may then keep
+        # working on its buffers after it has returned the rows (owner_tail), e.g. a weight-gradient GEMM placed after
+        # the input-gradient GEMM.
+        prog = [("publish", 0, 0), ("wait_counts", 0, 0)]
+        for o in range(world):
+            prog.append(("wait_token", o, 0))
+            for c in range(chunks):
+                prog.append(("push", o, c))
+        prog += [("wait_rows", 0, 0), ("reset_tiles", 0, 0)] + [("store", s_, 0) for s_ in range(world)]
+        prog += [("owner_tail", 0, 0), ("finish", 0, 0), ("wait_done", 0, 0)]
     if variant == "token_before_store":
         i, j = prog.index(("finish", 0, 0)), prog.index(("store", 0, 0))
         prog.insert(j, prog.pop(i))
@@ -65,7 +78,7 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
     total_steps = n * calls
     # the owner's buffers of a call are in use until the last step of its owner-side work (in the kernels: until the last
     # CTA of the last owner-side kernel, whose epilogue still reads row metadata and, in backward, the saved activations)
-    release_at = max(i for i, st in enumerate(prog) if st[0] in ("store", "finish"))
+    release_at = max(i for i, st in enumerate(prog) if st[0] in ("store", "finish", "owner_tail"))
     expected = [sum(rows[s][o] for s in range(world)) for o in range(world)]     # rows owner o receives per call
 
     # state: per rank program counter (0 .. total_steps) plus the shared words, all derived data kept explicit
@@ -77,7 +90,8 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
                 tuple(tuple([0] * world) for _ in range(world)),      # done[s][o]
                 tuple(tuple([0] * world) for _ in range(world)),      # cum[s][o]
                 tuple(tuple([0] * world) for _ in range(world)),      # stored_calls[s][o]: calls whose rows o has returned to s
-                tuple([0] * world))                                   # released[o]: calls whose buffers owner o has let go
+                tuple([0] * world),                                   # released[o]: calls whose buffers owner o has let go
+                tuple(tuple([0] * world) for _ in range(world)))      # fin[s][o]: finish tokens of owner o seen by s (split_token)
 
     def fmt(state, who, step):
         return f"rank {who} at call {state[0][who] // n} step {step}; pcs {state[0]}"
@@ -91,7 +105,7 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
         explored += 1
         if explored > max_states:
             raise RuntimeError("state space larger than max_states")
-        pc, epoch, tile, done, cum, stored, released = state
+        pc, epoch, tile, done, cum, stored, released, fin = state
         if all(p == total_steps for p in pc):
             continue
         progressed = False
@@ -101,6 +115,7 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
             call, (kind, a, b) = pc[r] // n, prog[pc[r] % n]
             e2, t2, d2, c2, s2, rel2 = [list(x) for x in epoch], list(tile), [list(x) for x in done], \
                 [list(x) for x in cum], [list(x) for x in stored], list(released)
+            f2 = [list(x) for x in fin]
             planned = call % plan_every == 0
             if kind == "publish":
                 if planned:
@@ -130,12 +145,20 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
                 s = a
                 d2[s][r] += rows[s][r] * units
                 s2[s][r] = call + 1
+            elif kind == "wait_token":
+                if fin[r][a] < call:      # owner a's token of the previous call (nothing to wait for before the first)
+                    continue
+            elif kind == "owner_tail":
+                pass                      # still reading this call's buffers
             elif kind == "finish":
-                if variant != "no_token":
+                if variant == "split_token":
+                    for s in range(world):
+                        f2[s][r] += 1
+                elif variant != "no_token":
                     for s in range(world):
                         d2[s][r] += 1
             elif kind == "wait_done":
-                token = 0 if variant == "no_token" else 1
+                token = 0 if variant in ("no_token", "split_token") else 1
                 base = [0] * world if variant == "absolute_targets" else list(cum[r])
                 targets = [base[o] + rows[r][o] * units + token for o in range(world)]
                 if any(done[r][o] < targets[o] for o in range(world)):
@@ -151,7 +174,7 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
             p2 = list(pc)
             p2[r] += 1
             nxt = (tuple(p2), tuple(tuple(x) for x in e2), tuple(t2), tuple(tuple(x) for x in d2),
-                   tuple(tuple(x) for x in c2), tuple(tuple(x) for x in s2), tuple(rel2))
+                   tuple(tuple(x) for x in c2), tuple(tuple(x) for x in s2), tuple(rel2), tuple(tuple(x) for x in f2))
             if nxt not in seen:
                 seen.add(nxt)
                 stack.append(nxt)

@@ -159,6 +159,15 @@ def test_protocol_model_all_interleavings_are_safe():
     assert check(world=2, calls=3, chunks=1, plan_every=100) > 50
 
 
+def test_protocol_model_split_token_refinement_is_safe():
+    """Token in its own counter, checked per owner right before the next push: lets an owner keep using its buffers
+    after it has returned the rows. Safe in every interleaving, and strictly more concurrent than the current protocol."""
+    from ccfuser_b200.parallel.protocol_model import check
+    assert check(world=2, calls=4, chunks=1, variant="split_token") > check(world=2, calls=4, chunks=1)
+    assert check(world=3, calls=4, chunks=1, variant="split_token") > 5000
+    assert check(world=2, calls=4, chunks=2, variant="split_token", plan_every=100) > 500
+
+
 def test_protocol_model_finds_the_hazards_of_broken_variants():
     import pytest
     from ccfuser_b200.parallel.protocol_model import ProtocolViolation, check

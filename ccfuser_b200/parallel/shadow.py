@@ -116,3 +116,33 @@ def shadow_forward(x: torch.Tensor, which: torch.Tensor, score: torch.Tensor, pa
                        opt("htoh4_gate.bias") if activation == "swiglu" else None)
         y = y.index_add(0, tok, o * score[tok, slot].to(o.dtype).unsqueeze(1))
     return y
+
+
+def shadow_what_if(count_table: torch.Tensor, n: int, d_model: int, d_ffn: int, activation: str = "gelu",
+                   experts_per_rank: Optional[int] = None, elem: int = 2, backward: bool = True) -> Dict[str, float]:
+    """Host-side estimate for one step with the ``n`` most popular experts replicated: NVLink bytes per rank that the
+    replicas' tokens no longer cost, bytes that moving the replicas' weights (and, in training, their gradients) costs,
+    and the load of the busiest rank before and after (rows; a replica's rows are computed where their tokens are).
+    ``count_table[r, e]`` = rows rank r routes to expert e."""
+    ct = count_table.to(torch.float64).cpu()
+    w, e = ct.shape
+    e_loc = experts_per_rank or e // w
+    load = ct.sum(0)
+    ids = torch.sort(load, descending=True, stable=True).indices[:n]
+    owner = torch.arange(e) // e_loc
+    passes = 2 * (2 if backward else 1)                    # rows go out and come back, in forward and in backward
+    saved = 0.0
+    for i in ids.tolist():
+        remote = ct[:, i].clone()
+        remote[owner[i]] = 0.0                             # the owner's own rows never crossed NVLink
+        saved += float(remote.sum()) * d_model * elem * passes
+    mats = 3 if activation == "swiglu" else 2
+    # an all-reduce moves about 2 (W - 1) / W of the buffer per rank; once for the weights, once for their gradients
+    added = n * mats * d_model * d_ffn * elem * 2.0 * (w - 1) / w * (2 if backward else 1) * w
+    rank_rows = torch.zeros(w, dtype=torch.float64).index_add(0, owner, load)
+    keep = torch.ones(e, dtype=torch.bool)
+    keep[ids] = False
+    after = torch.zeros(w, dtype=torch.float64).index_add(0, owner[keep], load[keep]) + ct[:, ids].sum(1)
+    return {"experts": ids.tolist(), "nvlink_bytes_saved": saved, "nvlink_bytes_added": added,
+            "max_rank_rows_before": float(rank_rows.max()), "max_rank_rows_after": float(after.max()),
+            "mean_rank_rows": float(load.sum() / w)}

@@ -129,3 +129,17 @@ def test_four_rank_layer_with_recorded_skew_and_capacity():
         assert table[r].tolist() == want
         dropped += sum(c // scale for c in RECORDED_COUNTS[r]) - sum(want)
     assert dropped > 0                                            # the hot experts exceed even a capacity factor of 4
+
+
+def test_shadow_what_if_on_recorded_skew():
+    from ccfuser_b200.parallel.shadow import shadow_what_if
+    ct = torch.tensor(RECORDED_COUNTS)
+    r = shadow_what_if(ct, 2, d_model=1024, d_ffn=4096, experts_per_rank=E_LOC)
+    assert r["experts"] == [34, 58] and r["mean_rank_rows"] == 8192
+    assert r["max_rank_rows_after"] < r["max_rank_rows_before"]
+    # at this layer size moving two experts' weights and gradients costs more NVLink bytes than their tokens did:
+    # replication buys balance here, not traffic
+    assert r["nvlink_bytes_added"] > r["nvlink_bytes_saved"] > 0
+    # with a wide model and a small FFN the trade flips
+    r2 = shadow_what_if(ct, 1, d_model=8192, d_ffn=256, experts_per_rank=E_LOC)
+    assert r2["nvlink_bytes_saved"] > r2["nvlink_bytes_added"]

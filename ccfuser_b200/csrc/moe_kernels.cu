@@ -459,8 +459,14 @@ static int route_impl(const int* expert, int S, int E, int cap, int* pos, int* b
                       int* count_raw, int* count_kept, int* ticket, int* order_off, int* sorted_slot, int* slot_row,
                       int first_expert, void* stream) {
   if (E > CCF_MAX_GROUPS) return -2;
-  if (S == 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (S == 0) {
+    // a call without tokens on this rank still takes part in the count exchange: its counts are zero, not stale
+    cudaMemsetAsync(count_raw, 0, sizeof(int) * E, st);
+    cudaMemsetAsync(count_kept, 0, sizeof(int) * E, st);
+    if (order_off != nullptr) cudaMemsetAsync(order_off, 0, sizeof(int) * (E + 1), st);
+    return last_err();
+  }
   const int nb = (S + ccf::kRouteBlock - 1) / ccf::kRouteBlock;
   ccf::route_hist_kernel<<<nb, ccf::kRouteBlock, 0, st>>>(expert, S, E, cap, pos, block_hist, block_off, count_raw,
                                                           count_kept, ticket, order_off, first_expert);

@@ -103,3 +103,30 @@ def test_single_process_and_compat_constructor():
             for k, v in layer.state_dict().items()}
     ref = dense_moe_oracle([x.reshape(-1, 32)], full, top_k=2, capacity=None)[0]
     assert torch.allclose(y.reshape(-1, 32), ref, atol=1e-5)
+
+
+def _empty_rank_fn(rank, world):
+    cfg = MoEConfig(d_model=32, d_ffn=64, num_experts=4, top_k=2, capacity_factor=None, activation="gelu",
+                    dtype=torch.float32, ep_size=world, backend="cpu", max_tokens=64)
+    layer = MoELayer(cfg)
+    load_shard(layer, _full_params(cfg, 0), rank)
+    tokens = 0 if rank == 1 else 48                       # rank 1 has nothing to route in this call
+    x = _inputs(world, 48, 32)[rank][:tokens].clone().requires_grad_(True)
+    y = layer(x)
+    y.sum().backward()
+    return y.detach(), x.grad.clone(), layer.experts.htoh4.weight.grad.clone()
+
+
+def test_a_rank_without_tokens_still_takes_part():
+    world = 2
+    res = run_ranks(_empty_rank_fn, world)
+    cfg = MoEConfig(d_model=32, d_ffn=64, num_experts=4, top_k=2, capacity_factor=None, activation="gelu", dtype=torch.float32)
+    full = {k: v.clone().requires_grad_(True) for k, v in _full_params(cfg, 0).items()}
+    xs = [_inputs(world, 48, 32)[0].clone().requires_grad_(True), torch.zeros(0, 32, requires_grad=True)]
+    ys = dense_moe_oracle(xs, full, top_k=2, capacity=None, activation="gelu")
+    sum(y.sum() for y in ys).backward()
+    assert res[1][0].shape == (0, 32)
+    assert torch.allclose(res[0][0], ys[0].detach(), atol=1e-5, rtol=1e-4)
+    assert torch.allclose(res[0][1], xs[0].grad, atol=1e-5, rtol=1e-4)
+    for r in range(world):                                # rank 1's experts still served rank 0's tokens
+        assert torch.allclose(res[r][2], full["htoh4.weight"].grad[r * 2:(r + 1) * 2], atol=1e-5, rtol=1e-4)

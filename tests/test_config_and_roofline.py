@@ -84,3 +84,28 @@ def test_import_of_a_reference_state_dict_drops_the_shadow_slots():
     state = import_reference_state(ref, 4)
     layer.load_state_dict(state)
     assert torch.equal(layer.experts.htoh4.weight, ref["experts.htoh4.weight"][:4])
+
+
+def test_native_entry_points_reject_bad_arguments_before_touching_the_device():
+    import ctypes as C
+    from ccfuser_b200 import native as N
+    lib = N.load()
+    ok = dict(tokens=128, d=256, e=64, k=2)
+
+    def router(**kw):
+        a = dict(ok, **kw)
+        return lib.ccf_router_topk(None, None, None, a["tokens"], a["d"], a["e"], a["k"], 0, None, None, None, None, 0, -1, None)
+    assert router(e=257) == -2 and router(k=9) == -2 and router(k=3, e=2) == -2 and router(d=32) == -2
+    assert router(d=260) == -2 and router(tokens=0) == -2
+    b = N.BarrierArgs()
+    b.world, b.my_rank = 9, 0
+    assert lib.ccf_flag_barrier(C.byref(b), None) == -2
+    b.world, b.my_rank = 4, 4
+    assert lib.ccf_flag_barrier(C.byref(b), None) == -2
+    assert lib.ccf_layer_forward(None, None, None, None, None, 0, 0, 0, 0, None, None, 0, None) == -2
+    layer = N.Layer()
+    layer.world = 0
+    assert lib.ccf_layer_forward(C.byref(layer), None, None, None, None, 0, 0, 0, 0, None, None, 0, None) == -2
+    p = N.PlanArgs()
+    p.e_total, p.world = 300, 2
+    assert lib.ccf_plan(C.byref(p), None) == -2

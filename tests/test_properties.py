@@ -1,0 +1,73 @@
+"""Property tests (hypothesis) of the routing rule and of the single-process layer against the dense oracle."""
+import torch
+from hypothesis import given, settings, strategies as st
+
+from ccfuser_b200 import MoEConfig, MoELayer
+from ccfuser_b200.ops.reference import dense_moe_oracle
+from ccfuser_b200.ops.routing import global_plan, route_local
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 40), st.integers(1, 4), st.integers(1, 12), st.integers(1, 30), st.integers(0, 2 ** 31 - 1),
+       st.floats(0.0, 0.5))
+def test_routing_rule_invariants(tokens, k, experts, capacity, seed, drop_frac):
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.randint(0, experts, (tokens, k), generator=g)
+    idx[torch.rand(tokens, k, generator=g) < drop_frac] = -1          # slots that are not routed at all
+    plan = route_local(idx, experts, capacity)
+    flat = idx.reshape(-1)
+    assert plan.raw_count.sum() == (flat >= 0).sum()
+    assert torch.equal(plan.count, plan.raw_count.clamp(max=capacity)) and plan.keep.sum() == plan.count.sum()
+    assert not plan.keep[flat < 0].any()
+    for e in range(experts):
+        mine = (flat == e).nonzero().view(-1)
+        # positions inside an expert follow slot order; exactly the first `capacity` are kept
+        assert plan.pos[mine].tolist() == list(range(mine.numel()))
+        assert plan.keep[mine].tolist() == [p < capacity for p in range(mine.numel())]
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.integers(1, 4), st.integers(1, 6), st.integers(0, 2 ** 31 - 1))
+def test_global_plan_segments_tile_aligned_and_disjoint(world, e_loc, seed):
+    g = torch.Generator().manual_seed(seed)
+    table = torch.randint(0, 300, (world, world * e_loc), generator=g)
+    table[torch.rand(table.shape, generator=g) < 0.3] = 0
+    gp = global_plan(table, e_loc)
+    assert (gp.expert_base % 128 == 0).all()
+    for owner in range(world):
+        spans = sorted((int(gp.expert_base[e] + gp.src_offset[r, e]), int(gp.expert_base[e] + gp.src_offset[r, e] + table[r, e]))
+                       for e in range(owner * e_loc, (owner + 1) * e_loc) for r in range(world) if table[r, e])
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+        assert not spans or spans[-1][1] <= int(gp.rank_rows[owner])
+
+
+@settings(max_examples=12, deadline=None)
+@given(st.integers(1, 33), st.sampled_from(["gelu", "relu", "swiglu"]), st.integers(1, 3), st.sampled_from([None, 0.5, 1.0, 2.0]),
+       st.booleans(), st.integers(0, 10 ** 6))
+def test_single_process_layer_matches_oracle(tokens, act, k, cf, bias, seed):
+    torch.manual_seed(seed)
+    cfg = MoEConfig(d_model=16, d_ffn=24, num_experts=5, top_k=k, capacity_factor=cf, activation=act, bias=bias,
+                    dtype=torch.float32, backend="cpu", max_tokens=64)
+    layer = MoELayer(cfg)
+    x = torch.randn(tokens, 16, requires_grad=True)
+    y = layer(x)
+    y.square().sum().backward()
+    full = {"gate.weight": layer.gate.gate.weight.detach(), "gate.bias": layer.gate.gate.bias.detach()}
+    for name in ("htoh4", "h4toh", "htoh4_gate"):
+        if hasattr(layer.experts, name):
+            m = getattr(layer.experts, name)
+            full[name + ".weight"] = m.weight.detach().clone().requires_grad_(True)
+            full[name + ".bias"] = None if m.bias is None else m.bias.detach().clone().requires_grad_(True)
+    xr = x.detach().clone().requires_grad_(True)
+    yr = dense_moe_oracle([xr], full, top_k=k, capacity=cfg.capacity(tokens), activation=act)[0]
+    yr.square().sum().backward()
+    assert torch.allclose(y, yr, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(layer.experts.h4toh.weight.grad, full["h4toh.weight"].grad, atol=1e-5, rtol=1e-3)
+
+
+def test_one_expert_top1_is_a_dense_ffn():
+    torch.manual_seed(0)
+    cfg = MoEConfig(d_model=16, d_ffn=32, num_experts=1, top_k=1, activation="gelu", dtype=torch.float32, backend="cpu")
+    layer = MoELayer(cfg)
+    x = torch.randn(3, 7, 16)
+    assert torch.allclose(layer(x), layer.experts.expert_forward(0, x.reshape(-1, 16)).reshape(3, 7, 16), atol=1e-6)

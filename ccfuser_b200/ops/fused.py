@@ -113,6 +113,22 @@ class CommContext:
     def peer(self, name: str):
         return self.buf.peer_ptrs(self.off[name])
 
+    def close(self):
+        """Free this context's symmetric buffers (collective over its group; call after the layers that use it have
+        been released and their work has completed)."""
+        for name in ("grecv", "gcomb", "row_src", "row_gate", "tile_flags", "cnt_table", "cnt_flag", "done"):
+            setattr(self, name, None)
+        self.buf.close()
+        for k, v in list(self._instances.items()):
+            if v is self:
+                del self._instances[k]
+
+    @classmethod
+    def close_all(cls):
+        """Free every communication context of this process (collective; e.g. before destroying the process group)."""
+        for ctx in list(cls._instances.values()):
+            ctx.close()
+
     def device_barrier(self):
         """On-stream barrier over the ranks of this context's group (collective): returns at once on the host; work
         queued on the stream after it starts only when every rank's stream has reached its barrier. Bounded like every

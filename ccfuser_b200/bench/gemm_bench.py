@@ -24,6 +24,18 @@ def measured_peaks():
         return 1590.0, 6650.0, "fallback"
 
 
+def measured_sustained_tflops(default: float = 1400.0) -> float:
+    """cuBLAS bf16 rate of a seconds-long back-to-back loop under the power cap (MEASURED_PEAKS.json): the applicable
+    ceiling for kernels timed inside a long step, as opposed to the burst rate of a single isolated launch."""
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f).get("bf16_tflops_sustained", default))
+    except Exception:
+        return default
+
+
 def time_fn(fn, iters=10, warmup=3, flush_mb=256):
     flush = torch.empty(flush_mb * 1024 * 1024, dtype=torch.uint8, device="cuda")
     for _ in range(warmup):

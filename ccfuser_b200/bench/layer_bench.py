@@ -20,7 +20,7 @@ import torch.distributed as dist
 
 from .. import MoEConfig, MoELayer, zipf_router_bias
 from ..utils.dist import init_distributed
-from .gemm_bench import measured_peaks
+from .gemm_bench import measured_peaks, measured_sustained_tflops
 
 NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (900 nominal)
 
@@ -103,12 +103,14 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
     total_ms = float(t[2]) if not args.forward_only else float(t[0])
     nv_bytes = rows * args.d_model * 2 * (world - 1) / max(1, world) * (2 if args.forward_only else 4)
     roof_ms = max(flops / (peak * 1e9), nv_bytes / (NVLINK_GBS * 1e6))
+    roof_sus_ms = max(flops / (measured_sustained_tflops() * 1e9), nv_bytes / (NVLINK_GBS * 1e6))
     out = {"bench": "moe_layer", "backend": backend, "n_gpus": world, "tokens_per_gpu": tokens, "d_model": args.d_model,
            "d_ffn": args.d_ffn, "experts_per_gpu": experts_per_gpu, "top_k": args.top_k, "act": args.act, "cf": args.cf,
            "zipf": args.zipf, "shadow_experts": args.shadow, "dtype": args.dtype, "cuda_graph": graphed is not None, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
            "total_ms": round(total_ms, 4), "tflops_per_gpu": round(flops / total_ms / 1e9, 1),
            "nvlink_bytes_per_gpu": int(nv_bytes), "roofline_ms": round(roof_ms, 4),
-           "roofline_frac_of_" + src: round(roof_ms / total_ms, 3), **stats}
+           "roofline_frac_of_" + src: round(roof_ms / total_ms, 3),
+           "roofline_frac_of_" + src + "_sustained": round(roof_sus_ms / total_ms, 3), **stats}
     layer.release()
     del layer
     torch.cuda.empty_cache()

@@ -12,7 +12,7 @@ from __future__ import annotations
 import argparse
 import json
 
-from .gemm_bench import measured_peaks
+from .gemm_bench import measured_peaks, measured_sustained_tflops
 
 NVLINK_GBS = 770.0
 
@@ -77,6 +77,11 @@ def main():
     if a.measured_ms > 0:
         r["measured_ms"] = a.measured_ms
         r["fraction_of_roofline"] = round(r["target_ms"] / a.measured_ms, 3)
+        # the same against the sustained (power-capped) GEMM rate, the ceiling that applies to a step-long kernel sequence
+        sus = roofline(a.tokens, a.d_model, a.d_ffn, a.top_k, a.act, a.gpus, not a.forward_only, a.kept_fraction,
+                       peak_tflops=measured_sustained_tflops(), experts_per_gpu=a.experts_per_gpu)
+        r["sustained_peak_tflops"] = sus["peak_tflops"]
+        r["fraction_of_roofline_sustained"] = round(sus["target_ms"] / a.measured_ms, 3)
     print(json.dumps(r))
 
 

@@ -128,15 +128,27 @@ def layer_bench(torch, dist, world, rank, steps=5, warmup=3):
             times.append(s.elapsed_time(e))
     layer._fused_impl().ctx.check_status("layer bench")
     ms = sorted(times)[len(times) // 2]
-    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    # rows the busiest rank's experts actually processed (slots beyond the capacity do no work), like the time: max over ranks
+    rows = float(layer._fused_impl().group_rows.sum())
+    t = torch.tensor([ms, rows], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    flops = 3 * 2 * 3 * 4096 * 14336 * tokens * 2  # (fwd + 2x bwd) x 2 FLOP x 3 matrices x top-2 rows
+    ms, rows = float(t[0]), float(t[1])
+    flops = 3 * 2 * 3 * 4096 * 14336 * rows  # (fwd + 2x bwd) x 2 FLOP x 3 matrices x processed rows
     layer.release()
     del layer
     torch.cuda.empty_cache()
-    return {"fwd_bwd_ms": round(float(t.item()), 3), "tflops_per_gpu": round(flops / float(t.item()) / 1e9, 1),
-            "config": "16384 tok/GPU, d4096, SwiGLU ffn14336, 8 experts/GPU, top-2, cf1.2, bf16"}
+    out = {"fwd_bwd_ms": round(ms, 3), "tflops_per_gpu": round(flops / ms / 1e9, 1), "rows_processed_max_rank": int(rows),
+           "slots_per_rank": tokens * 2,
+           "config": "16384 tok/GPU, d4096, SwiGLU ffn14336, 8 experts/GPU, top-2, cf1.2, bf16"}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+        out["frac_of_measured_cublas_burst"] = round(flops / ms / 1e9 / float(peaks["bf16_tflops"]), 3)
+        out["frac_of_measured_cublas_sustained"] = round(flops / ms / 1e9 / float(peaks["bf16_tflops_sustained"]), 3)
+    except Exception:
+        pass
+    return out
 
 
 def main():

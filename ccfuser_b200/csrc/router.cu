@@ -24,6 +24,43 @@ constexpr int kRtMaxStages = 8;
 constexpr int kRtABytes = BM * BK * 2;   // 128 rows x 128 bytes
 constexpr int kRtMaxK = 8;
 
+// Running top-kRtMaxK selection, best first. A candidate enters only if it is strictly greater than the current last
+// entry and bubbles up past strictly smaller ones, so among equal logits the lower expert id stays in front (candidates
+// are offered in ascending id order). Host-callable so that the rule can be tested without a GPU.
+__host__ __device__ __forceinline__ void topk_offer(float (&tv)[kRtMaxK], int (&ti)[kRtMaxK], float v, int e) {
+  if (v > tv[kRtMaxK - 1]) {
+    tv[kRtMaxK - 1] = v;
+    ti[kRtMaxK - 1] = e;
+#pragma unroll
+    for (int j = kRtMaxK - 1; j > 0; --j) {
+      if (tv[j] > tv[j - 1]) {
+        const float fv = tv[j]; tv[j] = tv[j - 1]; tv[j - 1] = fv;
+        const int iv = ti[j]; ti[j] = ti[j - 1]; ti[j - 1] = iv;
+      }
+    }
+  }
+}
+
+// softmax over the first k selected logits -> idx[k], w[k]
+__host__ __device__ __forceinline__ void topk_finish(const float (&tv)[kRtMaxK], const int (&ti)[kRtMaxK], int k, int* idx,
+                                                     float* w) {
+  float ex[kRtMaxK];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRtMaxK; ++j) {
+    ex[j] = (j < k) ? expf(tv[j] - tv[0]) : 0.f;
+    sum += ex[j];
+  }
+  const float inv = 1.f / sum;
+#pragma unroll
+  for (int j = 0; j < kRtMaxK; ++j) {
+    if (j < k) {
+      idx[j] = ti[j];
+      w[j] = ex[j] * inv;
+    }
+  }
+}
+
 struct __align__(16) RouterCtrl {
   uint64_t full[kRtMaxStages];
   uint64_t empty[kRtMaxStages];
@@ -149,36 +186,11 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           float v = __uint_as_float(racc[i]) + ctrl->bias[e];
           if (a.logits != nullptr && row < a.tokens && e < a.e) a.logits[static_cast<size_t>(row) * a.e + e] = v;
           if (e >= a.e) v = -INFINITY;
-          if (v > tv[kRtMaxK - 1]) {
-            tv[kRtMaxK - 1] = v;
-            ti[kRtMaxK - 1] = e;
-#pragma unroll
-            for (int j = kRtMaxK - 1; j > 0; --j) {
-              if (tv[j] > tv[j - 1]) {
-                const float fv = tv[j]; tv[j] = tv[j - 1]; tv[j - 1] = fv;
-                const int iv = ti[j]; ti[j] = ti[j - 1]; ti[j - 1] = iv;
-              }
-            }
-          }
+          topk_offer(tv, ti, v, e);
         }
       }
-      if (row < a.tokens) {
-        float ex[kRtMaxK];
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < kRtMaxK; ++j) {
-          ex[j] = (j < a.k) ? expf(tv[j] - tv[0]) : 0.f;
-          sum += ex[j];
-        }
-        const float inv = 1.f / sum;
-#pragma unroll
-        for (int j = 0; j < kRtMaxK; ++j) {
-          if (j < a.k) {
-            a.idx[static_cast<size_t>(row) * a.k + j] = ti[j];
-            a.w[static_cast<size_t>(row) * a.k + j] = ex[j] * inv;
-          }
-        }
-      }
+      if (row < a.tokens)
+        topk_finish(tv, ti, a.k, a.idx + static_cast<size_t>(row) * a.k, a.w + static_cast<size_t>(row) * a.k);
     } else {
       report_status(a.status, CCF_ERR_MBAR_TIMEOUT, 0x42);
     }
@@ -201,6 +213,20 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 }  // namespace ccf
 
 extern "C" {
+
+// The epilogue's selection rule on host memory (fp32 logits [tokens, e] -> idx, w), for tests without a GPU.
+int ccf_router_select_host(const float* logits, int tokens, int e, int k, int* idx, float* w) {
+  using namespace ccf;
+  if (e < 1 || e > 256 || k < 1 || k > kRtMaxK || k > e) return -2;
+  for (int t = 0; t < tokens; ++t) {
+    float tv[kRtMaxK];
+    int ti[kRtMaxK];
+    for (int j = 0; j < kRtMaxK; ++j) { tv[j] = -INFINITY; ti[j] = -1; }
+    for (int i = 0; i < e; ++i) topk_offer(tv, ti, logits[static_cast<size_t>(t) * e + i], i);
+    topk_finish(tv, ti, k, idx + static_cast<size_t>(t) * k, w + static_cast<size_t>(t) * k);
+  }
+  return 0;
+}
 
 // x [tokens, d] and wg [e, d] are 2-byte row-major operands of the same type (fp16 = 1: half, 0: bf16), bias [e] of
 // that type or null. idx [tokens, k] int32 and w [tokens, k] fp32 are written; logits_f32 [tokens, e] only if not null.

@@ -168,6 +168,7 @@ def _declare(lib):
         "ccf_gemm_launch": ([C.POINTER(GemmLaunch), p], i),
         "ccf_gemm_smem_bytes": ([], i),
         "ccf_router_topk": ([p, p, p, i, i, i, i, i, p, p, p, p, ull, i, p], i),
+        "ccf_router_select_host": ([p, i, i, i, p, p], i),
         "ccf_topk_softmax": ([p, i, i, i, i, i, p, p, p], i),
         "ccf_topk_softmax_bwd": ([p, p, p, i, i, i, p, i, i, p], i),
         "ccf_route": ([p, i, i, i, p, p, p, p, p, p, p], i),

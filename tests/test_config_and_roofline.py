@@ -109,3 +109,23 @@ def test_native_entry_points_reject_bad_arguments_before_touching_the_device():
     p = N.PlanArgs()
     p.e_total, p.world = 300, 2
     assert lib.ccf_plan(C.byref(p), None) == -2
+
+
+def test_router_selection_rule_on_the_host():
+    """The one-kernel router's epilogue rule (running top-8 with stable ties, softmax over the first k), compiled for
+    the host from the same source, against the reference top-k + softmax."""
+    import torch
+    from ccfuser_b200 import native as N
+    from ccfuser_b200.gates import topk_softmax_reference
+    lib = N.load()
+    g = torch.Generator().manual_seed(3)
+    for t, e, k in ((300, 8, 2), (257, 64, 2), (100, 200, 8), (64, 256, 4), (50, 5, 5), (10, 1, 1)):
+        logits = torch.randn(t, e, generator=g)
+        logits[::7] = torch.round(logits[::7] * 2) / 2            # many exact ties
+        logits[3] = 0.25                                           # a row of all-equal logits
+        idx = torch.empty(t, k, dtype=torch.int32)
+        w = torch.empty(t, k, dtype=torch.float32)
+        assert lib.ccf_router_select_host(logits.contiguous().data_ptr(), t, e, k, idx.data_ptr(), w.data_ptr()) == 0
+        ridx, rw = topk_softmax_reference(logits, k)
+        assert torch.equal(idx.long(), ridx)
+        assert torch.allclose(w, rw, atol=1e-6)

@@ -241,15 +241,27 @@ class record_launches:
         return False
 
 
+# Argument checks of the host launchers return small negative numbers before any CUDA call is made; failures of CUDA
+# calls come back as minus the cudaError_t value. The two ranges overlap for -2 ... -8, so a message names both readings.
+ARG_ERRORS = {-2: "argument out of range", -3: "n must be a multiple of 32", -4: "k-grouped GEMM needs m_per_group % 128 == 0",
+              -5: "k must be a multiple of 8", -6: "no kernel for this combination of operand majors and epilogue",
+              -7: "cudaSetDevice failed", -8: "the CTA-pair kernel needs m_per_group % 256 == 0 in k-grouped mode"}
+
+
 def check(rc: int, what: str):
     if rc != 0:
-        msg = ""
+        parts = []
+        if rc in ARG_ERRORS:
+            parts.append("argument check: " + ARG_ERRORS[rc])
         if -1000 < rc < 0:
             try:
-                msg = load().ccf_error_string(rc).decode()
+                parts.append("or CUDA error %d: %s" % (-rc, load().ccf_error_string(rc).decode()) if parts else
+                             "CUDA error %d: %s" % (-rc, load().ccf_error_string(rc).decode()))
             except Exception:
                 pass
-        raise RuntimeError(f"{what} failed with code {rc} {msg}")
+        elif rc <= -1000:
+            parts.append("driver error %d while encoding a tensor map" % (-rc - 1000))
+        raise RuntimeError(f"{what} failed with code {rc} ({'; '.join(parts)})")
 
 
 def stream_ptr() -> int:

@@ -386,7 +386,7 @@ class FusedMoE:
         rs, rg, tf = ctx.peer("row_src"), ctx.peer("row_gate"), ctx.peer("tile_flags")
         for r in range(self.world):
             a.peer_recv[r], a.peer_row_src[r], a.peer_row_gate[r], a.peer_tile_flags[r] = recv[r], rs[r], rg[r], tf[r]
-        a.work_counter = ctx.ws.sched.data_ptr() + 8
+        a.work_counter = ctx.ws.sched.data_ptr() + 4 * G.Workspace.DISPATCH_WORK
         a.tokens, a.top_k, a.d = tokens, cfg.top_k, cfg.d_model
         a.capacity = cfg.capacity(tokens)
         a.experts_per_rank, a.my_rank = cfg.experts_per_rank, self.rank

@@ -18,6 +18,9 @@ class Workspace:
     """Per-device scratch the kernels share: tile scheduler counters and the status word."""
 
     _by_device = {}
+    # elements of `sched`: next tile of the dynamic scheduler, CTAs that have finished, chunk claim counter of the
+    # dispatch role (each returned to zero by the last CTA of the kernel that used it); the rest is spare
+    TILE, FINISHED, DISPATCH_WORK = 0, 1, 2
 
     def __init__(self, device):
         self.sched = torch.zeros(8, dtype=torch.int32, device=device)
@@ -106,7 +109,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     g.total_index = int(total_index)
     if dispatch is not None:
         g.disp = dispatch
-        g.disp.work_counter = ws.sched.data_ptr() + 8
+        g.disp.work_counter = ws.sched.data_ptr() + 4 * Workspace.DISPATCH_WORK
     assert a0.dim() == 2 and b0.dim() == 2 and a0.is_contiguous() and b0.is_contiguous()
     L.a0, L.a1, L.b0, L.b1 = N.ptr(a0), N.ptr(a1), N.ptr(b0), N.ptr(b1)
     L.a_rows, L.a_cols = a0.shape

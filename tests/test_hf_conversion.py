@@ -56,3 +56,14 @@ def test_bert_qa_layers_become_moe():
     (out.loss + extra).backward()
     assert layers[1].experts.h4toh.weight.grad.abs().sum() > 0
     assert model.bert.encoder.layer[3].output.LayerNorm.weight.grad is not None
+
+
+def test_hf_example_trainer_runs_both_models_on_cpu():
+    from ccfuser_b200.examples import hf_train
+    common = ["--steps", "2", "--warmup", "0", "--layers", "4", "--heads", "2", "--hidden", "32", "--vocab", "128", "--batch", "2",
+              "--seq", "16", "--experts-per-gpu", "4", "--dtype", "fp32"]
+    for model, n_moe in (("gpt2", 4), ("bert", 1)):
+        for variant in ("dense", "nccl"):
+            out = hf_train.main(["--model", model, "--variant", variant] + common)
+            assert out["moe_layers"] == (0 if variant == "dense" else n_moe)
+            assert out["final_loss"] == out["final_loss"] and out["step_ms"] > 0

@@ -129,3 +129,32 @@ def test_router_selection_rule_on_the_host():
         ridx, rw = topk_softmax_reference(logits, k)
         assert torch.equal(idx.long(), ridx)
         assert torch.allclose(w, rw, atol=1e-6)
+
+
+def test_ae_harness_writes_the_reference_csv_columns(tmp_path, monkeypatch):
+    """The evaluation harness with its child runs replaced by canned records: file names and columns as the reference's
+    recorded data (moe_layer_*.csv, kernel_eval_*.csv, e2e_model_*.csv), and the figure tool accepts them."""
+    import csv
+    from ccfuser_b200.bench import ae, plot
+
+    def fake(gpus, module, args, port, timeout=1800):
+        if module.endswith("layer_bench"):
+            return [{"backend": b, "experts_per_gpu": e, "total_ms": 2.0 * f, "fwd_ms": 0.8 * f, "bwd_ms": 1.2 * f}
+                    for b, f in (("fused", 1.0), ("nccl", 4.0)) for e in (4, 8)]
+        if module.endswith("kernel_bench"):
+            return [{"experts_per_gpu": 16, "remote_frac": rf, "fused_ag_ms": 0.25, "nccl_a2a_gemm1_ms": 2.0, "nccl_a2a_in_ms": 0.1,
+                     "fused_ga_ms": 0.2, "gemm2_nccl_a2a_ms": 1.9, "nccl_a2a_out_ms": 0.1} for rf in (0.45, 0.25)]
+        return [{"step_ms": 33.0}]
+    monkeypatch.setattr(ae, "torchrun", fake)
+    p10, _ = ae.fig10(4, str(tmp_path), 3)
+    p12, _ = ae.fig12(4, str(tmp_path), 3)
+    p11, _ = ae.fig11(4, str(tmp_path), 3)
+    rows = list(csv.reader(open(p10)))
+    assert rows[0] == ["name", "num_expert", "total_time", "forward_time", "backward_time"] and len(rows) == 5
+    assert rows[1][0] == "ccfuser_b200" and rows[3][0] == "nccl_a2a"
+    assert list(csv.reader(open(p12[0])))[0] == ["kernel", "locality", "time", "all2all"]
+    assert list(csv.reader(open(p12[1])))[0] == ["kernel", "locality", "time", "all2all", "num_expert"]
+    e2e = list(csv.reader(open(p11)))
+    assert e2e[0] == ["name", "MOE-GPT", "MOE-BERT", "MOE-Transformer-xl"] and [r[0] for r in e2e[1:]] == ["naive", "nccl_a2a", "ccfuser_b200"]
+    made = plot.main(["--data", str(tmp_path), "--out", str(tmp_path / "fig")])
+    assert len(made) == 3 + 1 + 2 + 2

@@ -19,7 +19,7 @@ from .config import MoEConfig
 from .experts import Experts, scan_expert_params
 from .gates import NaiveGate
 from .parallel.a2a import moe_forward_a2a
-from .parallel.placement import plan_placement, rebalance_experts
+from .parallel.placement import placement_cost, plan_placement, rebalance_experts
 from .parallel.shadow import gather_shadow_params, select_popular, shadow_forward, split_shadow_slots
 
 
@@ -105,14 +105,23 @@ class MoELayer(nn.Module):
             return self._fused.routing_stats()["count_table"]
         return self.last_stats.get("count_table")
 
-    def rebalance(self, placement=None, optimizer=None, topology=None, slack: float = 0.05):
+    def rebalance(self, placement=None, optimizer=None, topology=None, slack: float = 0.05, min_gain: float = 0.0):
         """Move experts between ranks (collective over the expert-parallel group). With ``placement=None`` a placement
-        is planned from the counts of the last forward call; see parallel/placement.py. Returns the placement used."""
+        is planned from the counts of the last forward call; see parallel/placement.py. A planned placement is applied
+        only if it lowers the load of the busiest rank by at least the fraction ``min_gain`` (every rank takes the same
+        decision from the same table), so a periodic call does not shuffle weights for nothing. Returns the placement
+        used (the identity when nothing moved)."""
+        identity = list(range(self.config.num_experts))
         if placement is None:
             table = self.count_table()
             if table is None:
                 raise RuntimeError("no routing counts yet: run a forward pass first or pass a placement")
-            placement = plan_placement(table, self.config.experts_per_rank, topology, slack)
+            e_loc = self.config.experts_per_rank
+            placement = plan_placement(table, e_loc, topology, slack)
+            before = placement_cost(table, identity, e_loc)["max_rank_rows"]
+            after = placement_cost(table, placement, e_loc)["max_rank_rows"]
+            if before <= 0 or (before - after) / before < min_gain or after >= before:
+                return identity
         rebalance_experts(self, placement, optimizer)
         return list(placement)
 

@@ -59,6 +59,38 @@ def roofline(tokens, d_model, d_ffn, top_k, act, gpus, backward=True, kept_fract
             "target_ms": terms[bound], "bound": bound, "peak_source": src, "peak_tflops": peak_tflops}
 
 
+def kernel_estimates(rows: int, d_model: int, d_ffn: int, experts_per_gpu: int, act: str = "gelu", peak_tflops: float = None,
+                     hbm_gbs: float = None, elem: int = 2):
+    """Expected duration of each GEMM launch of one forward + backward pass on one rank that processes ``rows`` routed
+    rows: the slower of FLOPs at the sustained GEMM rate and the launch's compulsory HBM traffic (operands read once,
+    outputs written once) at the measured copy rate. To be written down before a measurement; the gap is the signal."""
+    if peak_tflops is None:
+        peak_tflops = measured_sustained_tflops()
+    if hbm_gbs is None:
+        hbm_gbs = measured_peaks()[1]
+    g = 2 if act == "swiglu" else 1                 # up-projection matrices
+    w1 = experts_per_gpu * g * d_model * d_ffn * elem
+    w2 = experts_per_gpu * d_model * d_ffn * elem
+    x, h = rows * d_model * elem, rows * d_ffn * elem
+    launches = {
+        # name: (FLOPs, bytes read + written)
+        "dispatch+gemm1": (2.0 * g * rows * d_model * d_ffn, x + w1 + h * (1 + g)),          # h_act + pre-activations
+        "gemm2+combine": (2.0 * rows * d_model * d_ffn, h + w2 + x),
+        "dy dispatch+dgrad2": (2.0 * rows * d_model * d_ffn, x + w2 + h * g + h * g),         # reads pre-activations, writes dh(,dh2)
+        "wgrad2": (2.0 * rows * d_model * d_ffn, x + h + w2),
+        "wgrad1": (2.0 * g * rows * d_model * d_ffn, h * g + x * g + w1),
+        "dgrad1+combine": (2.0 * g * rows * d_model * d_ffn, h * g + w1 + x),
+    }
+    out = {}
+    for name, (fl, by) in launches.items():
+        t_c, t_m = fl / (peak_tflops * 1e9), by / (hbm_gbs * 1e6)
+        out[name] = {"ms": round(max(t_c, t_m), 4), "compute_ms": round(t_c, 4), "hbm_ms": round(t_m, 4),
+                     "bound": "compute" if t_c >= t_m else "hbm", "expected_tensor_pct": round(100 * t_c / max(t_c, t_m), 1),
+                     "expected_dram_pct": round(100 * t_m / max(t_c, t_m), 1)}
+    out["total_ms"] = round(sum(v["ms"] for v in out.values()), 4)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=16384)
@@ -71,7 +103,13 @@ def main():
     ap.add_argument("--kept-fraction", type=float, default=1.0)
     ap.add_argument("--measured-ms", type=float, default=0.0)
     ap.add_argument("--experts-per-gpu", type=int, default=0, help="include the HBM traffic of this many experts' weights")
+    ap.add_argument("--per-kernel", action="store_true",
+                    help="print the expected duration and bound of each GEMM launch instead (needs --experts-per-gpu)")
     a = ap.parse_args()
+    if a.per_kernel:
+        rows = int(a.tokens * a.top_k * a.kept_fraction)
+        print(json.dumps(kernel_estimates(rows, a.d_model, a.d_ffn, max(1, a.experts_per_gpu), a.act), indent=1))
+        return
     r = roofline(a.tokens, a.d_model, a.d_ffn, a.top_k, a.act, a.gpus, not a.forward_only, a.kept_fraction,
                  experts_per_gpu=a.experts_per_gpu)
     if a.measured_ms > 0:

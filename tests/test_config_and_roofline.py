@@ -158,3 +158,15 @@ def test_ae_harness_writes_the_reference_csv_columns(tmp_path, monkeypatch):
     assert e2e[0] == ["name", "MOE-GPT", "MOE-BERT", "MOE-Transformer-xl"] and [r[0] for r in e2e[1:]] == ["naive", "nccl_a2a", "ccfuser_b200"]
     made = plot.main(["--data", str(tmp_path), "--out", str(tmp_path / "fig")])
     assert len(made) == 3 + 1 + 2 + 2
+
+
+def test_per_kernel_estimates():
+    from ccfuser_b200.bench.roofline import kernel_estimates
+    few = kernel_estimates(16384, 2048, 8192, 8, "gelu", peak_tflops=1392.0, hbm_gbs=6557.0)
+    many = kernel_estimates(16384, 2048, 8192, 64, "gelu", peak_tflops=1392.0, hbm_gbs=6557.0)
+    assert all(few[k]["bound"] == "compute" for k in few if k != "total_ms")
+    assert abs(few["gemm2+combine"]["ms"] - 2 * 16384 * 2048 * 8192 / 1392e9) < 1e-3
+    # with 64 experts on one GPU the weights alone make the first GEMM of each pass memory-bound
+    assert many["dispatch+gemm1"]["bound"] == "hbm" and many["total_ms"] > few["total_ms"]
+    sw = kernel_estimates(16384, 4096, 14336, 8, "swiglu", peak_tflops=1392.0, hbm_gbs=6557.0)
+    assert abs(sw["dispatch+gemm1"]["compute_ms"] - 2 * sw["gemm2+combine"]["compute_ms"]) < 1e-3

@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import contextlib
 import os
+import time
 from collections import defaultdict
 from typing import Dict, List
 
@@ -33,6 +34,12 @@ class StageTimer:
 
     @contextlib.contextmanager
     def stage(self, name: str):
+        if not torch.cuda.is_available():
+            # host fallback (CPU backend, tests): wall-clock of the enclosed code
+            t0 = time.perf_counter()
+            yield
+            self.events[name].append((time.perf_counter() - t0) * 1e3)
+            return
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         with nvtx_range(name):
@@ -41,5 +48,7 @@ class StageTimer:
         self.events[name].append((s, e))
 
     def summary(self) -> Dict[str, float]:
-        torch.cuda.synchronize()
-        return {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in self.events.items()}
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        return {k: sum(x if isinstance(x, float) else x[0].elapsed_time(x[1]) for x in v) / len(v)
+                for k, v in self.events.items()}

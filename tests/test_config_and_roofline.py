@@ -170,3 +170,16 @@ def test_per_kernel_estimates():
     assert many["dispatch+gemm1"]["bound"] == "hbm" and many["total_ms"] > few["total_ms"]
     sw = kernel_estimates(16384, 4096, 14336, 8, "swiglu", peak_tflops=1392.0, hbm_gbs=6557.0)
     assert abs(sw["dispatch+gemm1"]["compute_ms"] - 2 * sw["gemm2+combine"]["compute_ms"]) < 1e-3
+
+
+def test_stage_timer_on_the_host():
+    import time
+    from ccfuser_b200.utils.tracing import StageTimer, nvtx_range
+    t = StageTimer()
+    for _ in range(3):
+        with t.stage("sleep"):
+            time.sleep(0.01)
+        with t.stage("noop"), nvtx_range("x"):
+            pass
+    s = t.summary()
+    assert set(s) == {"sleep", "noop"} and s["sleep"] >= 9.0 > s["noop"]

@@ -42,6 +42,7 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
     gy = torch.randn(tokens, args.d_model, device="cuda", dtype=dtype, generator=g)
     flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     fwd, bwd = [], []
+    moved = None
     graphed = None
     if args.graph and args.forward_only and backend == "fused":
         from ..ops.fused import GraphedForward
@@ -74,6 +75,10 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
         if it >= args.warmup:
             fwd.append(e0.elapsed_time(e1))
             bwd.append(e1.elapsed_time(e2))
+        elif args.rebalance and it == max(0, args.warmup - 2) and world > 1 and graphed is None:
+            # one re-placement from the counts of this warm-up call; the remaining warm-up call runs on the new layout
+            pl = layer.rebalance()
+            moved = sum(1 for slot, old in enumerate(pl) if slot // experts_per_gpu != old // experts_per_gpu)
     if backend == "fused":
         layer._fused_impl().ctx.check_status("layer bench")
     med = lambda v: sorted(v)[len(v) // 2]
@@ -106,7 +111,7 @@ def run_config(args, world, rank, tokens, experts_per_gpu, backend):
     roof_sus_ms = max(flops / (measured_sustained_tflops() * 1e9), nv_bytes / (NVLINK_GBS * 1e6))
     out = {"bench": "moe_layer", "backend": backend, "n_gpus": world, "tokens_per_gpu": tokens, "d_model": args.d_model,
            "d_ffn": args.d_ffn, "experts_per_gpu": experts_per_gpu, "top_k": args.top_k, "act": args.act, "cf": args.cf,
-           "zipf": args.zipf, "shadow_experts": args.shadow, "dtype": args.dtype, "cuda_graph": graphed is not None, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
+           "zipf": args.zipf, "shadow_experts": args.shadow, "dtype": args.dtype, "cuda_graph": graphed is not None, "experts_moved_by_rebalance": moved, "fwd_ms": round(float(t[0]), 4), "bwd_ms": round(float(t[1]), 4),
            "total_ms": round(total_ms, 4), "tflops_per_gpu": round(flops / total_ms / 1e9, 1),
            "nvlink_bytes_per_gpu": int(nv_bytes), "roofline_ms": round(roof_ms, 4),
            "roofline_frac_of_" + src: round(roof_ms / total_ms, 3),
@@ -131,6 +136,7 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
     ap.add_argument("--zipf", type=float, default=0.0, help="Zipf exponent of expert popularity (router bias); 0 = off")
     ap.add_argument("--zipf-scale", type=float, default=1.0)
+    ap.add_argument("--rebalance", action="store_true", help="re-place the experts once during the warm-up (needs --warmup >= 2)")
     ap.add_argument("--shadow", type=int, default=0, help="replicate the n most popular experts of every step on all ranks")
     ap.add_argument("--backends", default="fused", help="comma list of fused,nccl")
     ap.add_argument("--forward-only", action="store_true")

@@ -71,3 +71,23 @@ def test_one_expert_top1_is_a_dense_ffn():
     layer = MoELayer(cfg)
     x = torch.randn(3, 7, 16)
     assert torch.allclose(layer(x), layer.experts.expert_forward(0, x.reshape(-1, 16)).reshape(3, 7, 16), atol=1e-6)
+
+
+@settings(max_examples=30, deadline=None)
+@given(st.integers(1, 4), st.integers(1, 5), st.integers(0, 2 ** 31 - 1), st.booleans())
+def test_planned_placement_is_a_balanced_permutation(world, e_loc, seed, nested):
+    from ccfuser_b200.parallel.placement import placement_cost, plan_placement
+    g = torch.Generator().manual_seed(seed)
+    e = world * e_loc
+    table = (torch.rand(world, e, generator=g).pow(4) * 1000).long()
+    topo = None
+    if nested and world == 4:
+        topo = [[0, 1], [2, 3]]
+    pl = plan_placement(table, e_loc, topo)
+    assert sorted(pl) == list(range(e))
+    assert pl == plan_placement(table.clone(), e_loc, topo)                       # deterministic
+    cost = placement_cost(table, pl, e_loc)
+    assert sum(cost["rank_rows"]) == int(table.sum()) and cost["local_rows"] + cost["cross_rows"] == int(table.sum())
+    # never worse than leaving every expert where it is by more than the heaviest single expert
+    ident = placement_cost(table, list(range(e)), e_loc)
+    assert cost["max_rank_rows"] <= ident["max_rank_rows"] + int(table.sum(0).max())

@@ -59,3 +59,78 @@ def evaluate_lm(model_step, iterator: LMOrderedIterator, max_batches: Optional[i
             total += float(model_step(x, y))
             n += 1
     return total / max(1, n)
+
+
+class Vocab:
+    """Word-level vocabulary built from text: ids by descending frequency (ties by first appearance), optional
+    ``<unk>`` / ``<eos>`` symbols, frequency and size limits. Covers what the training scripts need from the
+    vocabulary helper the reference vendors (mix_moe/mix_moe/examples/transformer-xl/utils/vocabulary.py)."""
+
+    def __init__(self, min_freq: int = 1, max_size: Optional[int] = None, lower: bool = False, add_eos: bool = True,
+                 unk: str = "<unk>", eos: str = "<eos>"):
+        self.min_freq, self.max_size, self.lower, self.add_eos = min_freq, max_size, lower, add_eos
+        self.unk, self.eos = unk, eos
+        self.counter: dict = {}
+        self.idx2sym: list = []
+        self.sym2idx: dict = {}
+
+    def tokenize(self, line: str):
+        line = line.strip()
+        if self.lower:
+            line = line.lower()
+        toks = line.split()
+        return toks + [self.eos] if (self.add_eos and toks) else toks
+
+    def count_lines(self, lines):
+        for line in lines:
+            for t in self.tokenize(line):
+                self.counter[t] = self.counter.get(t, 0) + 1
+
+    def build(self):
+        self.idx2sym, self.sym2idx = [], {}
+        for sym in (self.unk,) + ((self.eos,) if self.add_eos else ()):
+            self._add(sym)
+        order = sorted(self.counter.items(), key=lambda kv: -kv[1])      # stable: first appearance breaks ties
+        for sym, n in order:
+            if n < self.min_freq or (self.max_size is not None and len(self.idx2sym) >= self.max_size):
+                break
+            self._add(sym)
+        return self
+
+    def _add(self, sym):
+        if sym not in self.sym2idx:
+            self.sym2idx[sym] = len(self.idx2sym)
+            self.idx2sym.append(sym)
+
+    def encode_lines(self, lines) -> torch.Tensor:
+        unk = self.sym2idx[self.unk]
+        ids = [self.sym2idx.get(t, unk) for line in lines for t in self.tokenize(line)]
+        return torch.tensor(ids, dtype=torch.int64)
+
+    def decode(self, ids) -> str:
+        return " ".join(self.idx2sym[int(i)] for i in ids)
+
+    def __len__(self):
+        return len(self.idx2sym)
+
+
+class Corpus:
+    """train / valid / test token streams from three text files (or three lists of lines) sharing one vocabulary built
+    on the training split; ``iterator(split, ...)`` gives an ``LMOrderedIterator`` over it."""
+
+    def __init__(self, train, valid=None, test=None, **vocab_kw):
+        def lines(src):
+            if src is None:
+                return []
+            if isinstance(src, str):
+                with open(src, encoding="utf-8") as f:
+                    return f.readlines()
+            return list(src)
+        splits = {"train": lines(train), "valid": lines(valid), "test": lines(test)}
+        self.vocab = Vocab(**vocab_kw)
+        self.vocab.count_lines(splits["train"])
+        self.vocab.build()
+        self.data = {k: self.vocab.encode_lines(v) for k, v in splits.items()}
+
+    def iterator(self, split: str, batch_size: int, tgt_len: int, device=None, rank: int = 0, world: int = 1):
+        return LMOrderedIterator(self.data[split], batch_size, tgt_len, device=device, rank=rank, world=world)

@@ -137,3 +137,21 @@ def test_example_trainer_with_two_expert_parallel_groups():
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
     rec = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")][-1]
     assert rec["n_gpus"] == 4 and rec["final_loss"] == rec["final_loss"]      # finite
+
+
+def test_vocab_and_corpus(tmp_path):
+    from ccfuser_b200.utils.data import Corpus
+    train = tmp_path / "train.txt"
+    train.write_text("the cat sat on the mat\nthe dog sat\n\nA cat\n")
+    corpus = Corpus(str(train), valid=["the bird sat"], lower=True, min_freq=1)
+    v = corpus.vocab
+    assert v.idx2sym[:2] == ["<unk>", "<eos>"] and v.idx2sym[2] == "the"          # most frequent word first
+    assert len(v) == 2 + len({"the", "cat", "sat", "on", "mat", "dog", "a"})
+    ids = corpus.data["train"]
+    assert v.decode(ids[:7]) == "the cat sat on the mat <eos>" and int((ids == v.sym2idx["<eos>"]).sum()) == 3
+    assert v.decode(corpus.data["valid"]) == "the <unk> sat <eos>"
+    it = corpus.iterator("train", batch_size=2, tgt_len=3)
+    x, y = next(iter(it))
+    assert x.shape == (2, 3) and torch.equal(x[:, 1:], y[:, :-1])
+    small = Corpus(["a a a b b c"], max_size=4, add_eos=False)
+    assert small.vocab.idx2sym == ["<unk>", "a", "b", "c"]

@@ -80,7 +80,7 @@ def build(args, world, dev, ep_group=None):
                  "end": torch.randint(0, s, (b,), generator=g)}
     else:
         b, s = args.batch or 16, args.seq or 512
-        c = TransformerXLMoEConfig(n_layer=args.layers or 12, tgt_len=s, mem_len=s, moe=moe,
+        c = TransformerXLMoEConfig(n_token=getattr(args, "n_token", 0) or 100, n_layer=args.layers or 12, tgt_len=s, mem_len=s, moe=moe,
                                    num_experts=args.experts_per_gpu * world, top_k=args.top_k,
                                    capacity_factor=args.cf or None, ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
         model = _TXLStep(TransformerXLMoE(c, ep_group=ep_group, device=dev))
@@ -104,6 +104,9 @@ def main():
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--optimizer", default="sgd", choices=["sgd", "adamw"])
     ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--data", default="", help="txl only: training text file (word-level vocabulary built from it); "
+                                               "default is a fixed synthetic batch")
+    ap.add_argument("--valid", default="", help="txl only: validation text file, evaluated at the end")
     ap.add_argument("--ep-size", type=int, default=0,
                     help="ranks per expert-parallel group (default: all); the groups are data-parallel replicas of each other")
     ap.add_argument("--rebalance-every", type=int, default=0,
@@ -113,6 +116,13 @@ def main():
     args = ap.parse_args()
     rank, _, world = init_distributed()
     dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    corpus = train_iter = None
+    if args.data:
+        if args.model != "txl":
+            raise SystemExit("--data is supported for --model txl")
+        from ..utils.data import Corpus
+        corpus = Corpus(args.data, valid=args.valid or None)
+        args.n_token = len(corpus.vocab)
     ep_size = args.ep_size or world
     ep_group = expert_dp_group = None
     if ep_size != world:
@@ -125,9 +135,18 @@ def main():
     wrapped = wrap_ddp(model) if world > 1 else model
     params = [p for p in model.parameters() if p.requires_grad]
     opt = torch.optim.SGD(params, lr=args.lr) if args.optimizer == "sgd" else torch.optim.AdamW(params, lr=args.lr)
+    if corpus is not None:
+        train_iter = corpus.iterator("train", args.batch or 16, args.seq or 512, device=dev, rank=rank, world=world)
+        if len(train_iter) == 0:
+            raise SystemExit("the training text is shorter than one batch of batch x seq tokens per rank")
     times = []
     import time
     for i in range(args.warmup + args.steps):
+        if train_iter is not None:
+            x, y = train_iter.get_batch(i % len(train_iter))
+            if i % len(train_iter) == 0:
+                model.mems = None                      # a new pass over the text: the recurrence memory starts over
+            batch = {"ids": x, "labels": y}
         if world > 1:
             dist.barrier()
         t0 = time.perf_counter()
@@ -166,6 +185,13 @@ def main():
         print(json.dumps({"bench": "e2e", "model": args.model, "variant": args.variant, "n_gpus": world,
                           "experts_per_gpu": args.experts_per_gpu, "step_ms": round(float(t), 3),
                           "tokens_per_s": round(tokens * world / float(t) * 1e3, 1), "final_loss": round(float(loss.detach()), 4)}))
+    if corpus is not None and args.valid and corpus.data["valid"].numel() > (args.batch or 16) * ((args.seq or 512) + 1):
+        from ..utils.data import evaluate_lm
+        model.mems = None
+        val = evaluate_lm(lambda x, y: model({"ids": x, "labels": y}),
+                          corpus.iterator("valid", args.batch or 16, args.seq or 512, device=dev), max_batches=50)
+        if rank == 0:
+            print(json.dumps({"bench": "e2e", "model": args.model, "valid_loss": round(val, 4), "vocab": len(corpus.vocab)}))
     if args.save:
         from ..utils.checkpoint import save_ep_checkpoint
         if rank < ep_size:   # the other expert-parallel groups hold copies of the same shards

@@ -155,3 +155,25 @@ def test_vocab_and_corpus(tmp_path):
     assert x.shape == (2, 3) and torch.equal(x[:, 1:], y[:, :-1])
     small = Corpus(["a a a b b c"], max_size=4, add_eos=False)
     assert small.vocab.idx2sym == ["<unk>", "a", "b", "c"]
+
+
+def test_txl_example_trains_from_a_text_file(tmp_path, capsys):
+    import json
+    import random
+    import sys
+    from ccfuser_b200.examples import train
+    rnd = random.Random(0)
+    words = ["w%d" % i for i in range(40)]
+    (tmp_path / "train.txt").write_text("\n".join(" ".join(rnd.choice(words) for _ in range(12)) for _ in range(200)))
+    (tmp_path / "valid.txt").write_text("\n".join(" ".join(rnd.choice(words) for _ in range(12)) for _ in range(40)))
+    old = sys.argv
+    sys.argv = ["train", "--model", "txl", "--variant", "nccl", "--steps", "4", "--warmup", "0", "--layers", "2", "--batch", "4",
+                "--seq", "16", "--experts-per-gpu", "4", "--lr", "0.05", "--data", str(tmp_path / "train.txt"),
+                "--valid", str(tmp_path / "valid.txt")]
+    try:
+        train.main()
+    finally:
+        sys.argv = old
+    recs = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert recs[0]["final_loss"] == recs[0]["final_loss"]
+    assert recs[1]["vocab"] == 42 and recs[1]["valid_loss"] > 0

@@ -4,7 +4,7 @@ import sys
 
 COMMANDS = {
     "build": ("ccfuser_b200.build", "compile the CUDA library for sm_100a (--selftest: also the C++ self-test program)"),
-    "layer-bench": ("ccfuser_b200.bench.layer_bench", "MoE layer forward + backward timing (fig. 10 workload and the BASELINE configurations)"),
+    "layer-bench": ("ccfuser_b200.bench.layer_bench", "MoE layer forward + backward timing (fig. 10 workload, Mixtral-size layers, skewed routing, small-message forward)"),
     "kernel-bench": ("ccfuser_b200.bench.kernel_bench", "fused dispatch+GEMM / GEMM+combine against all-to-all + GEMM (fig. 12)"),
     "gemm-bench": ("ccfuser_b200.bench.gemm_bench", "grouped GEMM throughput on one GPU"),
     "ae": ("ccfuser_b200.bench.ae", "run the three evaluation experiments and write their CSV files"),

@@ -37,8 +37,54 @@ def clear_tokens(layer, x, k):
     return lg[:, k - 1] != lg[:, k]
 
 
+def ep_inside_dp(rank, world):
+    """Expert-parallel groups of two ranks replicated over the job: the fused backend on a sub-group against the
+    all-to-all backend on the same sub-group, then the replicas' expert gradients reduced over the data-parallel group."""
+    from ccfuser_b200.parallel.ddp import reduce_expert_grads
+    from ccfuser_b200.utils.dist import make_ep_dp_groups
+    ep_group, dp_group = make_ep_dp_groups(2)
+    tokens, d, f, e_loc = 512, 256, 512, 2
+    kw = dict(d_model=d, d_ffn=f, num_experts=2 * e_loc, top_k=2, capacity_factor=None, activation="gelu",
+              dtype=torch.bfloat16, ep_size=2, max_tokens=tokens, recv_factor=4.0)
+    outs = []
+    for backend in ("fused", "nccl"):
+        layer = MoELayer(MoEConfig(backend=backend, **kw), ep_group=ep_group, device="cuda")
+        g = torch.Generator(device="cuda").manual_seed(9)
+        with torch.no_grad():
+            for n, p in layer.named_parameters():
+                gen = g if n.startswith("gate.") else torch.Generator(device="cuda").manual_seed(20 + layer.ep_rank)
+                p.copy_((torch.randn(p.shape, device="cuda", generator=gen) * 0.05).to(p.dtype))
+        gx = torch.Generator(device="cuda").manual_seed(70 + rank)
+        x = (torch.randn(tokens, d, device="cuda", generator=gx) * 0.5).bfloat16().requires_grad_(True)
+        y = layer(x)
+        y.backward(torch.ones_like(y))
+        reduce_expert_grads(layer, dp_group, scale=1.0 / world)
+        torch.cuda.synchronize()
+        layer.check_status()
+        outs.append((y.detach(), x.grad, {n: p.grad.clone() for n, p in layer.named_parameters()}))
+        layer.release()
+    errs = {"y": rel(outs[0][0], outs[1][0]), "dx": rel(outs[0][1], outs[1][1])}
+    for n in outs[0][2]:
+        errs[n] = rel(outs[0][2][n], outs[1][2][n])
+    bad = {k: v for k, v in errs.items() if not v < 3e-2}
+    assert not bad, f"rank {rank} ep-inside-dp: {bad}"
+    # replicas agree after the reduction
+    w = outs[0][2]["experts.htoh4.weight"].float()
+    parts = [torch.empty_like(w) for _ in range(dist.get_world_size(dp_group))]
+    dist.all_gather(parts, w, group=dp_group)
+    assert all(torch.equal(parts[0], q) for q in parts)
+
+
 def main():
     rank, _, world = init_distributed()
+    if "--ep-inside-dp" in sys.argv:
+        assert world == 4, "needs 4 ranks"
+        ep_inside_dp(rank, world)
+        dist.barrier()
+        if rank == 0:
+            print("MGPU_EPDP_OK", flush=True)
+        dist.destroy_process_group()
+        return
     tokens, d, f, e_loc = 1024, 256, 512, 4
     base_cfg = MoEConfig(d_model=d, d_ffn=f, num_experts=e_loc * world, top_k=2, capacity_factor=None, activation="gelu",
                          dtype=torch.bfloat16, ep_size=world, backend="fused", max_tokens=tokens, recv_factor=4.0)

@@ -11,10 +11,10 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(world, port, worker="mgpu_worker.py", token="MGPU_OK", timeout=600):
+def _run(world, port, worker="mgpu_worker.py", token="MGPU_OK", timeout=600, args=()):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", CCFUSER_WAIT_LIMIT_S="20")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", worker)]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", worker)] + list(args)
     # own session: if the run has to be cut short, the launcher and all its ranks go together
     proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
     try:
@@ -39,3 +39,10 @@ def test_shadow_and_rebalance_multi_gpu(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _run(world, 29700 + world, worker="mgpu_features_worker.py", token="MGPU_FEATURES_OK", timeout=300)
+
+
+@pytest.mark.xfail(strict=False, reason="fused backend on an expert-parallel sub-group: first run on hardware pending")
+def test_expert_parallel_inside_data_parallel_multi_gpu():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    _run(4, 29710, worker="mgpu_features_worker.py", token="MGPU_EPDP_OK", timeout=300, args=["--ep-inside-dp"])

@@ -128,9 +128,10 @@ def test_example_trainer_with_two_expert_parallel_groups():
     import os
     import subprocess
     import sys
+    from tests.mp_util import _free_port
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
-           "--master-port", "29653", "-m", "ccfuser_b200.examples.train", "--model", "gpt", "--variant", "nccl", "--ep-size", "2",
+           "--master-port", str(_free_port()), "-m", "ccfuser_b200.examples.train", "--model", "gpt", "--variant", "nccl", "--ep-size", "2",
            "--steps", "2", "--warmup", "0", "--layers", "2", "--batch", "2", "--seq", "16", "--experts-per-gpu", "2"]
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
     out = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=600)

@@ -112,6 +112,9 @@ def main():
     ap.add_argument("--rebalance-every", type=int, default=0,
                     help="every N steps re-place the experts of each MoE layer from its last routing counts (0 = never)")
     ap.add_argument("--save", default="", help="checkpoint prefix written at the end (per-rank expert shards + manifest)")
+    ap.add_argument("--save-every", type=int, default=0,
+                    help="also write the checkpoint every N steps, so that a job restarted by the launcher "
+                         "(torchrun --max-restarts) can pick up with --resume")
     ap.add_argument("--resume", default="", help="checkpoint prefix to load before training (any EP degree)")
     args = ap.parse_args()
     rank, _, world = init_distributed()
@@ -129,9 +132,17 @@ def main():
         from ..utils.dist import make_ep_dp_groups
         ep_group, expert_dp_group = make_ep_dp_groups(ep_size)
     model, batch, tokens = build(args, ep_size, dev, ep_group)
+    start_step = 0
     if args.resume:
+        import os
         from ..utils.checkpoint import load_ep_checkpoint
-        load_ep_checkpoint(model, args.resume, rank % ep_size, ep_size)
+        if os.path.exists(args.resume + ".manifest.json"):
+            manifest = load_ep_checkpoint(model, args.resume, rank % ep_size, ep_size)
+            start_step = int(manifest.get("extra", {}).get("step", 0))
+            if rank == 0:
+                print(f"resumed from {args.resume} at step {start_step}", flush=True)
+        elif rank == 0:
+            print(f"no checkpoint at {args.resume} yet: starting from scratch", flush=True)
     wrapped = wrap_ddp(model) if world > 1 else model
     params = [p for p in model.parameters() if p.requires_grad]
     opt = torch.optim.SGD(params, lr=args.lr) if args.optimizer == "sgd" else torch.optim.AdamW(params, lr=args.lr)
@@ -174,6 +185,10 @@ def main():
             ms = (time.perf_counter() - t0) * 1e3
         if i >= args.warmup:
             times.append(ms)
+        if args.save and args.save_every > 0 and (i + 1) % args.save_every == 0 and rank < ep_size:
+            from ..utils.checkpoint import save_ep_checkpoint
+            save_ep_checkpoint(model, args.save, rank, ep_size, extra={"model": args.model, "variant": args.variant,
+                                                                      "step": start_step + i + 1})
         if rank == 0 and i % 10 == 0:
             print(f"STEP-{i}: step_time = {ms:.3f} ms, loss = {float(loss.detach()):.4f}", flush=True)
     avg = sum(times) / max(1, len(times))
@@ -195,7 +210,8 @@ def main():
     if args.save:
         from ..utils.checkpoint import save_ep_checkpoint
         if rank < ep_size:   # the other expert-parallel groups hold copies of the same shards
-            save_ep_checkpoint(model, args.save, rank, ep_size, extra={"model": args.model, "variant": args.variant})
+            save_ep_checkpoint(model, args.save, rank, ep_size, extra={"model": args.model, "variant": args.variant,
+                                                                      "step": start_step + args.warmup + args.steps})
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

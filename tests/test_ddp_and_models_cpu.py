@@ -75,6 +75,16 @@ def test_lm_iterator_and_checkpoint_resume(tmp_path):
         train.main()
         sys.argv = base + ["--steps", "1", "--resume", prefix]
         train.main()
+        # a restarted job: same command line every time, periodic checkpoints, resume from whatever is there
+        prefix2 = str(tmp_path / "job")
+        restartable = base + ["--steps", "3", "--save", prefix2, "--save-every", "2", "--resume", prefix2]
+        sys.argv = restartable
+        train.main()                                   # first attempt: nothing to resume
+        import json
+        assert json.load(open(prefix2 + ".manifest.json"))["extra"]["step"] == 3
+        sys.argv = restartable
+        train.main()                                   # "restart": continues from step 3
+        assert json.load(open(prefix2 + ".manifest.json"))["extra"]["step"] == 6
     finally:
         sys.argv = old
     import os

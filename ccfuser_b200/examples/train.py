@@ -132,20 +132,20 @@ def main():
         from ..utils.dist import make_ep_dp_groups
         ep_group, expert_dp_group = make_ep_dp_groups(ep_size)
     model, batch, tokens = build(args, ep_size, dev, ep_group)
+    wrapped = wrap_ddp(model) if world > 1 else model
+    params = [p for p in model.parameters() if p.requires_grad]
+    opt = torch.optim.SGD(params, lr=args.lr) if args.optimizer == "sgd" else torch.optim.AdamW(params, lr=args.lr)
     start_step = 0
     if args.resume:
         import os
         from ..utils.checkpoint import load_ep_checkpoint
         if os.path.exists(args.resume + ".manifest.json"):
-            manifest = load_ep_checkpoint(model, args.resume, rank % ep_size, ep_size)
+            manifest = load_ep_checkpoint(model, args.resume, rank % ep_size, ep_size, optimizer=opt)
             start_step = int(manifest.get("extra", {}).get("step", 0))
             if rank == 0:
                 print(f"resumed from {args.resume} at step {start_step}", flush=True)
         elif rank == 0:
             print(f"no checkpoint at {args.resume} yet: starting from scratch", flush=True)
-    wrapped = wrap_ddp(model) if world > 1 else model
-    params = [p for p in model.parameters() if p.requires_grad]
-    opt = torch.optim.SGD(params, lr=args.lr) if args.optimizer == "sgd" else torch.optim.AdamW(params, lr=args.lr)
     if corpus is not None:
         train_iter = corpus.iterator("train", args.batch or 16, args.seq or 512, device=dev, rank=rank, world=world)
         if len(train_iter) == 0:
@@ -187,8 +187,8 @@ def main():
             times.append(ms)
         if args.save and args.save_every > 0 and (i + 1) % args.save_every == 0 and rank < ep_size:
             from ..utils.checkpoint import save_ep_checkpoint
-            save_ep_checkpoint(model, args.save, rank, ep_size, extra={"model": args.model, "variant": args.variant,
-                                                                      "step": start_step + i + 1})
+            save_ep_checkpoint(model, args.save, rank, ep_size, optimizer=opt,
+                               extra={"model": args.model, "variant": args.variant, "step": start_step + i + 1})
         if rank == 0 and i % 10 == 0:
             print(f"STEP-{i}: step_time = {ms:.3f} ms, loss = {float(loss.detach()):.4f}", flush=True)
     avg = sum(times) / max(1, len(times))
@@ -210,8 +210,8 @@ def main():
     if args.save:
         from ..utils.checkpoint import save_ep_checkpoint
         if rank < ep_size:   # the other expert-parallel groups hold copies of the same shards
-            save_ep_checkpoint(model, args.save, rank, ep_size, extra={"model": args.model, "variant": args.variant,
-                                                                      "step": start_step + args.warmup + args.steps})
+            save_ep_checkpoint(model, args.save, rank, ep_size, optimizer=opt,
+                               extra={"model": args.model, "variant": args.variant, "step": start_step + args.warmup + args.steps})
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

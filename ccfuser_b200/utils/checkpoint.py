@@ -30,11 +30,16 @@ def ep_state_dict(model: nn.Module) -> Dict[str, Dict[str, torch.Tensor]]:
             "replicated": {k: v.detach().cpu() for k, v in sd.items() if k not in ek}}
 
 
-def save_ep_checkpoint(model: nn.Module, prefix: str, ep_rank: int, ep_size: int, extra: Optional[dict] = None):
-    """Every rank writes ``<prefix>.ep<rank>of<size>.pt``; rank 0 also writes the replicated part and a manifest."""
+def save_ep_checkpoint(model: nn.Module, prefix: str, ep_rank: int, ep_size: int, extra: Optional[dict] = None,
+                       optimizer: Optional[torch.optim.Optimizer] = None):
+    """Every rank writes ``<prefix>.ep<rank>of<size>.pt``; rank 0 also writes the replicated part and a manifest. With
+    ``optimizer`` every rank also writes its optimizer state (``<prefix>.opt<rank>of<size>.pt``: it covers this rank's
+    experts and its copy of the replicated parameters; it is reloaded only at the same expert-parallel degree)."""
     os.makedirs(os.path.dirname(os.path.abspath(prefix)) or ".", exist_ok=True)
     parts = ep_state_dict(model)
     torch.save(parts["experts"], f"{prefix}.ep{ep_rank}of{ep_size}.pt")
+    if optimizer is not None:
+        torch.save(optimizer.state_dict(), f"{prefix}.opt{ep_rank}of{ep_size}.pt")
     if ep_rank == 0:
         torch.save(parts["replicated"], f"{prefix}.replicated.pt")
         e_loc = {k: int(v.shape[0]) for k, v in parts["experts"].items()}
@@ -55,8 +60,11 @@ def reshard_expert_state(shards: List[Dict[str, torch.Tensor]], new_ep_size: int
     return out
 
 
-def load_ep_checkpoint(model: nn.Module, prefix: str, ep_rank: int, ep_size: int, strict: bool = True) -> dict:
-    """Load a checkpoint written at any EP degree into a model sharded over ``ep_size`` ranks."""
+def load_ep_checkpoint(model: nn.Module, prefix: str, ep_rank: int, ep_size: int, strict: bool = True,
+                       optimizer: Optional[torch.optim.Optimizer] = None) -> dict:
+    """Load a checkpoint written at any EP degree into a model sharded over ``ep_size`` ranks. ``optimizer`` state is
+    restored when the checkpoint has it for this degree; after a change of degree the optimizer starts fresh (the
+    returned manifest then carries ``"optimizer_restored": False``)."""
     with open(f"{prefix}.manifest.json") as f:
         manifest = json.load(f)
     old = int(manifest["ep_size"])
@@ -68,6 +76,12 @@ def load_ep_checkpoint(model: nn.Module, prefix: str, ep_rank: int, ep_size: int
     state = dict(torch.load(f"{prefix}.replicated.pt", map_location="cpu"))
     state.update(experts)
     model.load_state_dict(state, strict=strict)
+    if optimizer is not None:
+        path = f"{prefix}.opt{ep_rank}of{ep_size}.pt"
+        restored = old == ep_size and os.path.exists(path)
+        if restored:
+            optimizer.load_state_dict(torch.load(path, map_location="cpu"))
+        manifest["optimizer_restored"] = restored
     return manifest
 
 

@@ -188,3 +188,34 @@ def test_txl_example_trains_from_a_text_file(tmp_path, capsys):
     recs = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
     assert recs[0]["final_loss"] == recs[0]["final_loss"]
     assert recs[1]["vocab"] == 42 and recs[1]["valid_loss"] > 0
+
+
+def test_checkpoint_carries_optimizer_state(tmp_path):
+    from ccfuser_b200 import MoEConfig, MoELayer, load_ep_checkpoint, save_ep_checkpoint
+    torch.manual_seed(0)
+    cfg = MoEConfig(d_model=16, d_ffn=32, num_experts=4, dtype=torch.float32, backend="cpu")
+    layer = MoELayer(cfg)
+    opt = torch.optim.AdamW(layer.parameters(), lr=1e-2)
+    x = torch.randn(20, 16)
+    for _ in range(3):
+        opt.zero_grad()
+        layer(x).square().sum().backward()
+        opt.step()
+    prefix = str(tmp_path / "ck")
+    save_ep_checkpoint(layer, prefix, 0, 1, optimizer=opt, extra={"step": 3})
+    layer2 = MoELayer(cfg)
+    opt2 = torch.optim.AdamW(layer2.parameters(), lr=1e-2)
+    manifest = load_ep_checkpoint(layer2, prefix, 0, 1, optimizer=opt2)
+    assert manifest["optimizer_restored"] and manifest["extra"]["step"] == 3
+    for a, b in zip(layer.parameters(), layer2.parameters()):
+        assert torch.equal(a, b)
+        assert torch.equal(opt.state[a]["exp_avg_sq"], opt2.state[b]["exp_avg_sq"])
+    # the next step is identical on both
+    for l, o in ((layer, opt), (layer2, opt2)):
+        o.zero_grad()
+        l(x).square().sum().backward()
+        o.step()
+    assert all(torch.equal(a, b) for a, b in zip(layer.parameters(), layer2.parameters()))
+    # another expert-parallel degree: parameters re-sharded, optimizer starts fresh
+    cfg2 = cfg.replace(num_experts=4)
+    assert load_ep_checkpoint(MoELayer(cfg2), prefix, 0, 1, optimizer=None)["ep_size"] == 1

@@ -94,6 +94,27 @@ class MoEConfig:
         rows = min(rows, self.ep_size * tokens * self.top_k + e_loc * tile)
         return (rows + tile - 1) // tile * tile
 
+    def memory_estimate(self, layers: int = 1, training: bool = True) -> dict:
+        """Device memory per rank, in bytes, of ``layers`` fused MoE layers of this configuration that share one
+        expert-parallel group: parameters (and their gradients), the per-layer receive / combine / activation buffers,
+        the buffers shared by the layers of a group, and the transient tensors of one backward pass. For sizing
+        ``max_tokens`` and ``recv_factor`` against the 180 GB of a B200."""
+        esz = 2 if self.dtype in (torch.bfloat16, torch.float16) else 4
+        e_loc, d, f = self.experts_per_rank, self.d_model, self.d_ffn
+        mats = 3 if self.activation == "swiglu" else 2
+        rows, slots = self.max_recv_rows(), self.max_tokens * self.top_k
+        weights = e_loc * (mats * d * f + ((mats - 1) * f + d if self.bias else 0)) * esz
+        router = self.num_experts * (d + (1 if self.router_bias else 0)) * esz
+        per_layer = (rows * d + slots * d) * esz                                   # xrecv + comb (symmetric)
+        per_layer += rows * f * esz * (mats if training else 1)                    # h_act (+ pre-activations)
+        per_layer += (3 * slots + 2 * self.num_experts + 6 * e_loc) * 4            # routing index arrays
+        shared = (rows * d + slots * d) * esz + rows * 8                           # grecv + gcomb + row metadata
+        transient = (rows * f * esz * (mats - 1) + weights) if training else 0     # dh(, dh2) + weight gradients of one layer
+        out = {"parameters": layers * (weights + router), "gradients": layers * (weights + router) if training else 0,
+               "layer_buffers": layers * per_layer, "group_buffers": shared, "backward_transient": transient}
+        out["total"] = sum(out.values())
+        return out
+
     def replace(self, **kw) -> "MoEConfig":
         return dataclasses.replace(self, **kw)
 

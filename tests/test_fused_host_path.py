@@ -242,3 +242,19 @@ def _rebalance_bf16_fn(rank, world):
 def test_bf16_experts_migrate_between_ranks_and_kernel_pointers_stay_valid():
     from tests.mp_util import run_ranks
     assert run_ranks(_rebalance_bf16_fn, 2) == [(True, True, True)] * 2
+
+
+def test_memory_estimate_matches_what_the_layer_allocates():
+    cfg, layer = _layer("swiglu", tokens=256, e=4, d=128, f=256)
+    fm = layer._fused_impl()
+    est = cfg.memory_estimate(layers=1, training=True)
+    params = sum(p.numel() * p.element_size() for p in layer.parameters())
+    assert est["parameters"] == params == est["gradients"]
+    sym_layer = fm.max_rows * cfg.d_model * 2 + fm.max_slots * cfg.d_model * 2
+    acts = sum(t.numel() * t.element_size() for t in (fm.h_act, fm.h_pre, fm.h_pre2))
+    assert abs(est["layer_buffers"] - (sym_layer + acts)) < 16 * 1024            # index arrays are the remainder
+    assert est["group_buffers"] >= fm.ctx.grecv.numel() * 2 + fm.ctx.gcomb.numel() * 2
+    big = MoEConfig(d_model=4096, d_ffn=14336, num_experts=64, top_k=2, capacity_factor=1.2, activation="swiglu",
+                    bias=False, ep_size=8, max_tokens=16384)
+    total_gb = big.memory_estimate(layers=1)["total"] / 2 ** 30
+    assert 8 < total_gb < 20                                                     # one Mixtral-size layer per rank

@@ -21,6 +21,7 @@ from ..layers import MoELayer
 
 @dataclasses.dataclass
 class BertMoEConfig:
+    """BERT-base sized encoder; ``moe_layers`` lists the layers whose FFN is an MoE layer (the reference uses 2, 5, 8, 11)."""
     vocab_size: int = 30522
     n_layer: int = 12
     n_head: int = 12
@@ -45,6 +46,7 @@ class BertMoEConfig:
 
 
 class BertSelfAttention(nn.Module):
+    """Bidirectional multi-head attention with a key padding mask."""
     def __init__(self, c: BertMoEConfig, device=None):
         super().__init__()
         self.n_head = c.n_head
@@ -71,6 +73,7 @@ class FFN(nn.Module):
 
 
 class BertLayer(nn.Module):
+    """Post-LN encoder layer: attention + residual LayerNorm, FFN (dense or MoE) + residual LayerNorm."""
     def __init__(self, c: BertMoEConfig, moe: bool, ep_group=None, device=None):
         super().__init__()
         self.attention = BertSelfAttention(c, device)

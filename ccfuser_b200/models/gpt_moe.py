@@ -22,6 +22,8 @@ from ..layers import MoELayer
 
 @dataclasses.dataclass
 class GPTMoEConfig:
+    """GPT-2 style decoder with an MoE FFN in every ``moe_every``-th block; the defaults are the benchmark model
+    (24 layers, d_model 2048, 16 heads, seq 1024, 64 experts, top-2, FFN 8192, GELU)."""
     vocab_size: int = 50257
     n_layer: int = 24
     n_head: int = 16
@@ -83,6 +85,7 @@ class CausalSelfAttention(nn.Module):
 
 
 class DenseFFN(nn.Module):
+    """The ordinary (non-MoE) feed-forward block of the same shape as one expert."""
     def __init__(self, c: GPTMoEConfig, device=None):
         super().__init__()
         self.act = c.activation
@@ -103,6 +106,7 @@ class DenseFFN(nn.Module):
 
 
 class Block(nn.Module):
+    """Pre-LN transformer block: attention, then a dense FFN or an MoE layer."""
     def __init__(self, c: GPTMoEConfig, moe: bool, ep_group=None, device=None):
         super().__init__()
         self.ln_1 = nn.LayerNorm(c.d_model, device=device, dtype=c.dtype)

@@ -24,6 +24,8 @@ from ..layers import MoELayer
 
 @dataclasses.dataclass
 class TransformerXLMoEConfig:
+    """Transformer-XL with relative positions and segment memory; ``moe=True`` puts an MoE layer in every decoder layer
+    (the reference's end-to-end configuration: 12 layers, d_model 512, 8 heads, d_inner 2048, tgt_len = mem_len = 512)."""
     n_token: int = 100
     n_layer: int = 12
     n_head: int = 8
@@ -51,6 +53,7 @@ class TransformerXLMoEConfig:
 
 
 class PositionalEmbedding(nn.Module):
+    """Sinusoidal embedding of relative positions."""
     def __init__(self, d, device=None):
         super().__init__()
         self.register_buffer("inv_freq", 1.0 / (10000 ** (torch.arange(0.0, d, 2.0, device=device) / d)),
@@ -62,6 +65,7 @@ class PositionalEmbedding(nn.Module):
 
 
 class PositionwiseFF(nn.Module):
+    """The dense feed-forward block (used when ``moe=False``)."""
     def __init__(self, c: TransformerXLMoEConfig, device=None):
         super().__init__()
         self.fc = nn.Linear(c.d_model, c.d_inner, device=device, dtype=c.dtype)
@@ -80,6 +84,8 @@ def _rel_shift(x):
 
 
 class RelPartialLearnableAttention(nn.Module):
+    """Multi-head attention over [memory, segment] with Transformer-XL's relative position terms (content and position
+    biases u, v; relative shift)."""
     def __init__(self, c: TransformerXLMoEConfig, device=None):
         super().__init__()
         self.n_head, self.d_head = c.n_head, c.d_head
@@ -107,6 +113,7 @@ class RelPartialLearnableAttention(nn.Module):
 
 
 class DecoderLayer(nn.Module):
+    """Attention with memory, then the position-wise FFN (dense or MoE)."""
     def __init__(self, c: TransformerXLMoEConfig, ep_group=None, device=None):
         super().__init__()
         self.attn = RelPartialLearnableAttention(c, device)

@@ -26,6 +26,7 @@ _vp = C.c_void_p
 
 
 class DispatchArgs(C.Structure):
+    """Mirror of CcfDispatchArgs (csrc/gemm_args.h)."""
     _fields_ = [
         ("x", _vp), ("slot_expert", _vp), ("slot_pos", _vp), ("dst_base", _vp), ("slot_gate", _vp),
         ("saved_comb", _vp), ("dgate", _vp), ("slot_row", _vp), ("sorted_slot", _vp), ("order_off", _vp),
@@ -39,6 +40,7 @@ class DispatchArgs(C.Structure):
 
 
 class GemmArgs(C.Structure):
+    """Mirror of CcfGemmArgs (csrc/gemm_args.h)."""
     _fields_ = [
         ("group_base", _vp), ("group_rows", _vp), ("tile_flags", _vp), ("local_begin", _vp), ("local_rows", _vp),
         ("out0", _vp), ("out1", _vp), ("out2", _vp), ("bias0", _vp), ("bias1", _vp), ("aux0", _vp), ("aux1", _vp),
@@ -55,6 +57,7 @@ class GemmArgs(C.Structure):
 
 
 class GemmLaunch(C.Structure):
+    """Mirror of CcfGemmLaunch (csrc/gemm_args.h)."""
     _fields_ = [
         ("args", GemmArgs),
         ("a0", _vp), ("a1", _vp), ("b0", _vp), ("b1", _vp),
@@ -65,6 +68,7 @@ class GemmLaunch(C.Structure):
 
 
 class PlanArgs(C.Structure):
+    """Mirror of CcfPlanArgs (csrc/gemm_args.h)."""
     _fields_ = [
         ("count_kept", _vp), ("peer_table", _vp * MAX_RANKS), ("peer_flag", _vp * MAX_RANKS),
         ("dst_base", _vp), ("group_base", _vp), ("group_rows", _vp), ("sent_rows", _vp), ("table_copy", _vp),
@@ -76,6 +80,7 @@ class PlanArgs(C.Structure):
 
 
 class BarrierArgs(C.Structure):
+    """Mirror of CcfBarrierArgs (csrc/gemm_args.h)."""
     _fields_ = [("peer_flag", _vp * MAX_RANKS), ("status", _vp), ("wait_limit_ns", C.c_ulonglong),
                 ("world", C.c_int), ("my_rank", C.c_int), ("epoch", C.c_int), ("pad0", C.c_int)]
 

@@ -22,6 +22,7 @@ import torch
 
 
 class LocalRouting(NamedTuple):
+    """Routing plan of one rank's slots (see route_local)."""
     expert: torch.Tensor   # [S] int64 expert id of each slot
     pos: torch.Tensor      # [S] int64 position of the slot inside (this rank, expert)
     keep: torch.Tensor     # [S] bool  position < capacity

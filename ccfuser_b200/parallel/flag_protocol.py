@@ -27,6 +27,8 @@ TILE = 128
 
 
 class EmulatedRank:
+    """The words of one rank that its peers write (receive buffer, arrival counters, combine buffer, completion counters)
+    with the operations peers perform on them and the bounded waits of the owner."""
     def __init__(self, rank: int, world: int, max_rows: int, max_slots: int, d: int):
         self.rank, self.world = rank, world
         self.recv = np.zeros((max_rows, d), dtype=np.float32)

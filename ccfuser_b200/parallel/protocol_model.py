@@ -25,6 +25,7 @@ from typing import Dict, List, Sequence, Tuple
 
 
 class ProtocolViolation(AssertionError):
+    """An invariant of the protocol failed in some reachable interleaving (the message carries the state)."""
     pass
 
 

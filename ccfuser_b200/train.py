@@ -17,6 +17,7 @@ from .parallel.ddp import allreduce_replicated_grads, reduce_expert_grads, wrap_
 
 
 class TrainStep:
+    """One optimisation step as a callable object: forward, backward, gradient reductions, optimizer; see the module docstring."""
     def __init__(self, model: nn.Module, lr: float = 1e-3, optimizer: str = "sgd", dp_group=None,
                  use_ddp: bool = True, aux_loss: bool = False, expert_dp_group=None, mean_expert_grads: bool = False):
         """``dp_group``: ranks over which the replicated parameters are averaged (default: all). ``expert_dp_group``:

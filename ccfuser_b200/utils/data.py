@@ -22,6 +22,7 @@ def synthetic_corpus(n_tokens: int, vocab_size: int, seed: int = 0, zipf: float 
 
 
 class LMOrderedIterator:
+    """Consecutive ``[batch, tgt_len]`` segments of ``batch`` parallel streams cut from one token stream; see the module docstring."""
     def __init__(self, data: torch.Tensor, batch_size: int, tgt_len: int, device=None, rank: int = 0, world: int = 1):
         """`data`: 1-D token ids. Each data-parallel rank takes its own contiguous share of the stream."""
         share = data.numel() // world

@@ -12,6 +12,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <string.h>
 
 #include "gemm_common.cuh"
 
@@ -135,7 +136,7 @@ struct PairTile {
 };
 
 template <bool kKGroup, int kEpi>
-__device__ __forceinline__ PairTile decode_pair_tile(int t, const CcfGemmArgs& a, const Ctrl2* c) {
+__host__ __device__ __forceinline__ PairTile decode_pair_tile(int t, const CcfGemmArgs& a, const Ctrl2* c) {
   PairTile ti;
   constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
   if constexpr (!kKGroup) {
@@ -177,6 +178,46 @@ __device__ __forceinline__ PairTile decode_pair_tile(int t, const CcfGemmArgs& a
   return ti;
 }
 
+// Tile tables of one launch, computed by one thread of every CTA at start-up (host-callable so that the tile order can
+// be checked exhaustively without a GPU): number of column tiles; pair tiles per group, split into phase A (tiles that
+// hold only rows this rank pushed itself) and phase B (the rest) with their prefix sums; total tiles and total rows.
+template <bool kKGroup, int kEpi>
+__host__ __device__ __forceinline__ void pair_tile_tables(const CcfGemmArgs& args, Ctrl2* ctrl) {
+  constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
+  const int nt = (args.n + bn_out - 1) / bn_out;
+  ctrl->n_tiles = nt;
+  if constexpr (!kKGroup) {
+    int acc_a = 0, acc_b = 0, rows = 0;
+    for (int g = 0; g < args.num_groups; ++g) {
+      const int gr = args.group_rows[g];
+      const int mt = (gr + PM - 1) / PM;
+      int a0 = 0, na = 0;
+      if (args.local_begin != nullptr && args.tile_flags != nullptr) {
+        const int lb = args.local_begin[g], le = min(gr, lb + args.local_rows[g]);
+        a0 = (lb + PM - 1) / PM;
+        // a tile is local-only when it lies inside [lb, le); the last tile of the group also counts when le == gr
+        int a1 = (le == gr) ? mt : le / PM;
+        na = max(0, a1 - a0);
+        if (na == 0) a0 = 0;
+      }
+      ctrl->a0[g] = static_cast<short>(a0);
+      ctrl->na[g] = static_cast<short>(na);
+      ctrl->mta_prefix[g] = acc_a;
+      ctrl->mt_prefix[g] = acc_b;
+      acc_a += na;
+      acc_b += mt - na;
+      rows += gr;
+    }
+    ctrl->mta_prefix[args.num_groups] = acc_a;
+    ctrl->mt_prefix[args.num_groups] = acc_b;
+    ctrl->tiles_a = acc_a * nt;
+    ctrl->total_tiles = (acc_a + acc_b) * nt;
+    ctrl->total_rows = rows;
+  } else {
+    ctrl->total_tiles = args.num_groups * (args.m_per_group / PM) * nt;
+  }
+}
+
 template <int kAMajor, int kBMajor, int kEpi, bool kKGroup>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
@@ -193,7 +234,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
   const int n_pairs = static_cast<int>(gridDim.x) >> 1;
   volatile int* abort_word = &ctrl->abort_word;
   const uint64_t limit = fail_fast_limit(args.status, args.wait_limit_ns);
-  constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
 
   // ---- set-up ------------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
@@ -206,38 +246,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
       mbar_init(smem_u32(&ctrl->acc_empty[s]), 2 * kEpiWarps);
     }
     ctrl->abort_word = 0;
-    const int nt = (args.n + bn_out - 1) / bn_out;
-    ctrl->n_tiles = nt;
-    if constexpr (!kKGroup) {
-      int acc_a = 0, acc_b = 0, rows = 0;
-      for (int g = 0; g < args.num_groups; ++g) {
-        const int gr = args.group_rows[g];
-        const int mt = (gr + PM - 1) / PM;
-        int a0 = 0, na = 0;
-        if (args.local_begin != nullptr && args.tile_flags != nullptr) {
-          const int lb = args.local_begin[g], le = min(gr, lb + args.local_rows[g]);
-          a0 = (lb + PM - 1) / PM;
-          // a tile is local-only when it lies inside [lb, le); the last tile of the group also counts when le == gr
-          int a1 = (le == gr) ? mt : le / PM;
-          na = max(0, a1 - a0);
-          if (na == 0) a0 = 0;
-        }
-        ctrl->a0[g] = static_cast<short>(a0);
-        ctrl->na[g] = static_cast<short>(na);
-        ctrl->mta_prefix[g] = acc_a;
-        ctrl->mt_prefix[g] = acc_b;
-        acc_a += na;
-        acc_b += mt - na;
-        rows += gr;
-      }
-      ctrl->mta_prefix[args.num_groups] = acc_a;
-      ctrl->mt_prefix[args.num_groups] = acc_b;
-      ctrl->tiles_a = acc_a * nt;
-      ctrl->total_tiles = (acc_a + acc_b) * nt;
-      ctrl->total_rows = rows;
-    } else {
-      ctrl->total_tiles = args.num_groups * (args.m_per_group / PM) * nt;
-    }
+    pair_tile_tables<kKGroup, kEpi>(args, ctrl);
     fence_barrier_init();
     fence_proxy_async();
     prefetch_tensormap(&tmA0);
@@ -518,3 +527,46 @@ int launch_pair_by_key(int key, const CUtensorMap* tm, const CcfGemmArgs& a, int
 }
 
 }  // namespace ccf
+
+// The tile sequence of a row-grouped launch of the CTA-pair kernel, computed on the host with the kernel's own
+// functions: for tile t in launch order, out[5 t ...] = {group, first row, first column, valid rows, phase (0 = A)}.
+// Host arrays in, nothing touches a device. Returns the number of tiles (only the first `cap` are written).
+extern "C" int ccf_debug_pair_tile_order(const int* group_base, const int* group_rows, const int* local_begin,
+                                         const int* local_rows, int num_groups, int n, int k, int gated, int swiglu,
+                                         int* out, int cap) {
+  using namespace ccf;
+  if (num_groups < 1 || num_groups > CCF_MAX_GROUPS) return -2;
+  static const int dummy_flags = 0;
+  CcfGemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.group_base = group_base;
+  a.group_rows = group_rows;
+  a.local_begin = local_begin;
+  a.local_rows = local_rows;
+  a.tile_flags = gated ? &dummy_flags : nullptr;
+  a.num_groups = num_groups;
+  a.n = n;
+  a.k = k;
+  a.kseg = 1;
+  Ctrl2* c = new Ctrl2;
+  int total;
+  if (swiglu) {
+    pair_tile_tables<false, CCF_EPI_SWIGLU>(a, c);
+    total = c->total_tiles;
+    for (int t = 0; t < total && t < cap; ++t) {
+      const PairTile ti = decode_pair_tile<false, CCF_EPI_SWIGLU>(t, a, c);
+      const int rec[5] = {ti.g, ti.row0, ti.n0, ti.rows_pair, t < c->tiles_a ? 0 : 1};
+      memcpy(out + 5 * t, rec, sizeof(rec));
+    }
+  } else {
+    pair_tile_tables<false, CCF_EPI_STORE>(a, c);
+    total = c->total_tiles;
+    for (int t = 0; t < total && t < cap; ++t) {
+      const PairTile ti = decode_pair_tile<false, CCF_EPI_STORE>(t, a, c);
+      const int rec[5] = {ti.g, ti.row0, ti.n0, ti.rows_pair, t < c->tiles_a ? 0 : 1};
+      memcpy(out + 5 * t, rec, sizeof(rec));
+    }
+  }
+  delete c;
+  return total;
+}

@@ -91,3 +91,48 @@ def test_planned_placement_is_a_balanced_permutation(world, e_loc, seed, nested)
     # never worse than leaving every expert where it is by more than the heaviest single expert
     ident = placement_cost(table, list(range(e)), e_loc)
     assert cost["max_rank_rows"] <= ident["max_rank_rows"] + int(table.sum(0).max())
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(1, 6), st.integers(0, 2 ** 31 - 1), st.integers(1, 3), st.booleans(), st.booleans())
+def test_pair_kernel_tile_order_covers_every_tile_once(groups, seed, n_tiles, gated, swiglu):
+    """The CTA-pair kernel's tile sequence, computed on the host by the kernel's own set-up and decode functions: every
+    (group, 256-row tile, column tile) exactly once, the tiles made only of locally pushed rows first."""
+    import numpy as np
+    from ccfuser_b200 import native as N
+    lib = N.load()
+    rnd = np.random.RandomState(seed % (2 ** 31))
+    rows = rnd.choice([0, 1, 127, 128, 255, 256, 257, 300, 511, 512, 513, 777, 1024, 1200], size=groups).astype(np.int32)
+    base = np.zeros(groups, dtype=np.int32)
+    for g in range(1, groups):
+        base[g] = base[g - 1] + (rows[g - 1] + 127) // 128 * 128
+    lb = np.array([rnd.randint(0, r + 1) for r in rows], dtype=np.int32)
+    lr = np.array([rnd.randint(0, r - b + 1) for r, b in zip(rows, lb)], dtype=np.int32)
+    if rnd.rand() < 0.3:
+        lr = (rows - lb).astype(np.int32)                       # local rows reach the end of the group
+    bn = 128 if swiglu else 256
+    n = n_tiles * bn
+    cap = 4096
+    out = np.full(cap * 5, -7, dtype=np.int32)
+    total = lib.ccf_debug_pair_tile_order(base.ctypes.data, rows.ctypes.data, lb.ctypes.data, lr.ctypes.data, groups, n, 512,
+                                          int(gated), int(swiglu), out.ctypes.data, cap)
+    want = sum(int((r + 255) // 256) for r in rows) * n_tiles
+    assert total == want
+    recs = out[:5 * total].reshape(total, 5)
+    seen = set()
+    last_phase = 0
+    for g, row0, n0, rows_pair, phase in recs.tolist():
+        i, rem = divmod(row0 - int(base[g]), 256)
+        assert rem == 0 and n0 % bn == 0 and 0 <= n0 < n
+        assert rows_pair == min(256, int(rows[g]) - i * 256) > 0
+        assert (g, i, n0) not in seen
+        seen.add((g, i, n0))
+        assert phase >= last_phase                             # all phase-A tiles come first
+        last_phase = phase
+        if phase == 0:
+            assert gated
+            le = min(int(rows[g]), int(lb[g]) + int(lr[g]))
+            assert i * 256 >= lb[g] and (i * 256 + rows_pair <= le)      # only rows this rank pushed itself
+    assert len(seen) == want
+    if not gated:
+        assert (recs[:, 4] == 1).all() if total else True

@@ -136,3 +136,28 @@ def test_pair_kernel_tile_order_covers_every_tile_once(groups, seed, n_tiles, ga
     assert len(seen) == want
     if not gated:
         assert (recs[:, 4] == 1).all() if total else True
+
+
+@settings(max_examples=15, deadline=None)
+@given(st.integers(1, 30), st.integers(1, 3), st.sampled_from([None, 1.0]), st.integers(0, 10 ** 6), st.floats(0.0, 0.6))
+def test_unrouted_slots_are_ignored_by_the_layer_and_by_the_oracle_alike(tokens, k, cf, seed, frac):
+    """Slots with expert id -1 (how replicated experts leave the expert-parallel path) contribute nothing and take no
+    capacity, in the all-to-all backend exactly as in the dense oracle."""
+    from ccfuser_b200.experts import Experts
+    from ccfuser_b200.parallel.a2a import moe_forward_a2a
+    torch.manual_seed(seed)
+    e, d, f = 4, 8, 12
+    experts = Experts(e, d, f, "gelu", True, dtype=torch.float32)
+    x = torch.randn(tokens, d)
+    idx = torch.randint(0, e, (tokens, k))
+    idx[torch.rand(tokens, k) < frac] = -1
+    score = torch.rand(tokens, k)
+    cfg = MoEConfig(d_model=d, d_ffn=f, num_experts=e, top_k=k, capacity_factor=cf, dtype=torch.float32)
+    cap = cfg.capacity(tokens)
+    y = moe_forward_a2a(x, idx, score, experts, num_experts=e, capacity=cap, group=None)
+    full = {"gate.weight": torch.zeros(e, d), "htoh4.weight": experts.htoh4.weight.detach(), "htoh4.bias": experts.htoh4.bias.detach(),
+            "h4toh.weight": experts.h4toh.weight.detach(), "h4toh.bias": experts.h4toh.bias.detach()}
+    yr = dense_moe_oracle([x], full, top_k=k, capacity=cap, activation="gelu", routing=[(idx, score)])[0]
+    assert torch.allclose(y, yr, atol=1e-5, rtol=1e-4)
+    untouched = (idx < 0).all(1)
+    assert (y[untouched] == 0).all()

@@ -13,7 +13,8 @@ state:
   its condition holds); the explorer interleaves the ranks' actions in every possible order (states are hashed, so the
   search is over states, not over schedules);
 * invariants are asserted at the actions they concern: a row of call *i* must find the owner's buffer released from call
-  *i - 1*; the owner's reset of its arrival counters must not lose an arrival; a source's wait for call *i* must not be
+  *i - 1*; a count table must not be overwritten before its owner has read the previous exchange; the owner's reset of
+  its arrival counters must not lose an arrival; a source's wait for call *i* must not be
   satisfied by anything that belongs to call *i + 1*; and no reachable state may be a deadlock.
 
 ``check(...)`` returns the number of states explored or raises ``ProtocolViolation`` with a trace. ``variant`` selects
@@ -92,7 +93,8 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
                 tuple(tuple([0] * world) for _ in range(world)),      # cum[s][o]
                 tuple(tuple([0] * world) for _ in range(world)),      # stored_calls[s][o]: calls whose rows o has returned to s
                 tuple([0] * world),                                   # released[o]: calls whose buffers owner o has let go
-                tuple(tuple([0] * world) for _ in range(world)))      # fin[s][o]: finish tokens of owner o seen by s (split_token)
+                tuple(tuple([0] * world) for _ in range(world)),      # fin[s][o]: finish tokens of owner o seen by s (split_token)
+                tuple([0] * world))                                   # tables_read[o]: count exchanges whose table o has consumed
 
     def fmt(state, who, step):
         return f"rank {who} at call {state[0][who] // n} step {step}; pcs {state[0]}"
@@ -106,7 +108,7 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
         explored += 1
         if explored > max_states:
             raise RuntimeError("state space larger than max_states")
-        pc, epoch, tile, done, cum, stored, released, fin = state
+        pc, epoch, tile, done, cum, stored, released, fin, tables_read = state
         if all(p == total_steps for p in pc):
             continue
         progressed = False
@@ -117,14 +119,21 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
             e2, t2, d2, c2, s2, rel2 = [list(x) for x in epoch], list(tile), [list(x) for x in done], \
                 [list(x) for x in cum], [list(x) for x in stored], list(released)
             f2 = [list(x) for x in fin]
+            tr2 = list(tables_read)
             planned = call % plan_every == 0
             if kind == "publish":
                 if planned:
+                    nth = call // plan_every                  # this is the nth count exchange (0-based)
                     for o in range(world):
+                        if tables_read[o] < nth:
+                            raise ProtocolViolation("rank %d overwrites the count table of rank %d, which has not read the "
+                                                    "previous exchange yet: %s" % (r, o, fmt(state, r, kind)))
                         e2[o][r] = call + 1
             elif kind == "wait_counts":
                 if planned and any(epoch[r][s] < call + 1 for s in range(world)):
                     continue
+                if planned:
+                    tr2[r] = call // plan_every + 1
             elif kind == "push":
                 o = a
                 if released[o] < call:
@@ -175,7 +184,7 @@ def check(world: int = 2, calls: int = 2, chunks: int = 2, rows: Sequence[Sequen
             p2 = list(pc)
             p2[r] += 1
             nxt = (tuple(p2), tuple(tuple(x) for x in e2), tuple(t2), tuple(tuple(x) for x in d2),
-                   tuple(tuple(x) for x in c2), tuple(tuple(x) for x in s2), tuple(rel2), tuple(tuple(x) for x in f2))
+                   tuple(tuple(x) for x in c2), tuple(tuple(x) for x in s2), tuple(rel2), tuple(tuple(x) for x in f2), tuple(tr2))
             if nxt not in seen:
                 seen.add(nxt)
                 stack.append(nxt)

@@ -183,3 +183,25 @@ def test_stage_timer_on_the_host():
             pass
     s = t.summary()
     assert set(s) == {"sleep", "noop"} and s["sleep"] >= 9.0 > s["noop"]
+
+
+def test_trace_analysis_on_a_synthetic_trace():
+    import torch
+    from ccfuser_b200.bench.overlap_trace import analyze
+    ctas, slots, kblocks = 4, 6, 32
+    t = torch.zeros(ctas, slots, 8, dtype=torch.int64)
+    for c in range(ctas):
+        t[c, slots - 1, 0] = 1000                                  # kernel start
+        clk = 1000
+        for i in range(3):                                         # three tiles per CTA
+            t[c, i, 0] = clk; t[c, i, 1] = clk + 50; t[c, i, 2] = clk + 400      # noqa: E702
+            t[c, i, 3] = clk + 100                                 # accumulator free 100 clk after the previous commit
+            t[c, i, 4] = clk + 300
+            t[c, i, 5] = clk + 300 + 20480                         # main loop at 80 % of the ideal 16384
+            t[c, i, 6] = t[c, i, 5] + 10
+            t[c, i, 7] = t[c, i, 6] + 6000
+            clk = int(t[c, i, 5])
+    r = analyze(t, kblocks, leaders_only=False)
+    assert r["tiles"] == 12 and r["main_loop_clk"] == 20480 and r["main_loop_efficiency"] == 0.8
+    assert r["acc_wait_clk"] == 100 and r["rows_wait_clk"] == 50 and r["epilogue_clk"] == 6000
+    assert analyze(torch.zeros(2, 3, 8, dtype=torch.int64), 8)["tiles"] == 0

@@ -62,6 +62,8 @@ def main():
     ap.add_argument("--d", type=int, default=4096)
     ap.add_argument("--f", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--trace", action="store_true",
+                    help="add per-tile clock statistics (main-loop time against its ideal, accumulator wait, epilogue time)")
     ap.add_argument("--out", default="", help="optional JSON file for the records")
     args = ap.parse_args()
     peak, _, src = measured_peaks()
@@ -73,13 +75,24 @@ def main():
     r = rows_per * e
     out = []
 
-    def report(name, flops, fn):
+    def report(name, flops, fn, kblocks=0):
+        """fn() launches the case; if it accepts ``trace=`` and --trace is given, one more launch records per-tile clocks."""
         med, best = time_fn(fn, args.iters)
         G.Workspace.get(dev).check(name)
         rec = {"case": name, "ms_median": round(med, 4), "ms_best": round(best, 4),
-               "tflops_median": round(flops / med / 1e9, 1), "frac_of_" + src + "_cublas_peak": round(flops / med / 1e9 / peak, 3)}
+               "tflops_median": round(flops / med / 1e9, 1), "frac_of_" + src + "_cublas_peak": round(flops / med / 1e9 / peak, 3),
+               "frac_of_" + src + "_cublas_sustained": round(flops / med / 1e9 / measured_sustained_tflops(), 3)}
+        if args.trace and kblocks > 0:
+            from .overlap_trace import analyze
+            tr = torch.zeros(148, 128, 8, dtype=torch.int64, device=dev)
+            fn(trace=tr)
+            torch.cuda.synchronize()
+            rec["per_tile"] = analyze(tr, kblocks)
         print(json.dumps(rec), flush=True)
         out.append(rec)
+
+    def gemm(**kw):
+        return lambda trace=None: G.launch(trace=trace, **kw)
 
     cases = args.cases.split(",")
     if "square" in cases:
@@ -95,28 +108,28 @@ def main():
     h = torch.empty(r, f, device=dev, dtype=torch.bfloat16)
     pre = torch.empty(r, f, device=dev, dtype=torch.bfloat16)
     if "fwd1" in cases:
-        report("fwd1_gelu", 2 * r * d * f, lambda: G.launch(
+        report("fwd1_gelu", 2 * r * d * f, gemm(
             a0=x, b0=w1.view(e * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT, n=f, k=d,
-            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=f, out0=h, out1=pre, act=N.ACT_GELU))
+            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=f, out0=h, out1=pre, act=N.ACT_GELU), kblocks=(d + 63) // 64)
     w2 = torch.randn(e, d, f, device=dev, dtype=torch.bfloat16) * 0.02
     y = torch.empty(r, d, device=dev, dtype=torch.bfloat16)
     if "fwd2" in cases:
-        report("fwd2_store", 2 * r * d * f, lambda: G.launch(
+        report("fwd2_store", 2 * r * d * f, gemm(
             a0=h, b0=w2.view(e * d, f), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_STORE, n=d, k=f,
-            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=y))
+            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=y), kblocks=(f + 63) // 64)
     if "dgrad" in cases:
-        report("dgrad2_dact", 2 * r * d * f, lambda: G.launch(
+        report("dgrad2_dact", 2 * r * d * f, gemm(
             a0=y, b0=w2.view(e * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DACT, n=f, k=d,
-            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=h, aux0=pre, act=N.ACT_GELU))
+            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=h, aux0=pre, act=N.ACT_GELU), kblocks=(d + 63) // 64)
     if "dgrad_plain" in cases:
-        report("dgrad2_plain_store", 2 * r * d * f, lambda: G.launch(
+        report("dgrad2_plain_store", 2 * r * d * f, gemm(
             a0=y, b0=w2.view(e * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, k=d,
-            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=h))
+            group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=h), kblocks=(d + 63) // 64)
     if "wgrad" in cases:
         dw = torch.empty(e, d, f, device=dev, dtype=torch.bfloat16)
-        report("wgrad2", 2 * r * d * f, lambda: G.launch(
+        report("wgrad2", 2 * r * d * f, gemm(
             a0=y, b0=h, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True, m_per_group=d,
-            group_base=gb, group_rows=gr, num_groups=e, out0=dw, ld_out=f))
+            group_base=gb, group_rows=gr, num_groups=e, out0=dw, ld_out=f), kblocks=(rows_per + 63) // 64)
     if args.out:
         os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
         with open(args.out, "w") as fh:

@@ -82,3 +82,25 @@ def global_plan(count_table: torch.Tensor, experts_per_rank: int, tile: int = 12
     base = torch.cumsum(padded, 1) - padded
     rank_rows = padded.sum(1)
     return GlobalPlan(expert_rows, base.reshape(-1), src_offset, rank_rows)
+
+
+class ClippedPlan(NamedTuple):
+    """The row layout when an owner's receive buffer holds only ``max_rows`` rows (what plan_kernel computes on the
+    device): rows beyond the buffer are refused by the dispatch role and left out of every count, on both sides."""
+    accepted: torch.Tensor     # [W, E] rows of (source, expert) that fit
+    sent_rows: torch.Tensor    # [W, W] rows source r sends to owner o (what r's completion wait expects back)
+    group_rows: torch.Tensor   # [E] rows each expert's GEMM processes on its owner
+    overflow: torch.Tensor     # [W] bool: owner o would have needed more than max_rows
+
+
+def clipped_plan(count_table: torch.Tensor, experts_per_rank: int, max_rows: int, tile: int = 128) -> ClippedPlan:
+    """count_table: [W, E] kept rows per (source rank, expert) after the capacity clamp."""
+    gp = global_plan(count_table, experts_per_rank, tile)
+    ct = count_table.to(torch.int64)
+    w, e = ct.shape
+    first = gp.expert_base.view(1, e) + gp.src_offset                       # first row of (r, e) on the owner
+    accepted = torch.minimum(ct, (max_rows - first).clamp_min(0))
+    owner = torch.arange(e) // experts_per_rank
+    sent = torch.zeros(w, w, dtype=torch.int64).index_add(1, owner, accepted)
+    group_rows = torch.minimum(gp.expert_rows, (max_rows - gp.expert_base).clamp_min(0))
+    return ClippedPlan(accepted, sent, group_rows, gp.rank_rows > max_rows)

@@ -80,3 +80,31 @@ def test_fused_layer_output_survives_expert_permutation():
     assert clear.float().mean() > 0.9
     assert _rel(y1[clear], y0[clear]) < 1e-2 and _rel(y2[clear], y0[clear]) < 1e-2
     layer.release()
+
+
+@_new
+def test_plan_kernel_matches_the_host_model_when_the_buffer_overflows():
+    """The device plan (rows per expert, rows this rank counts as sent) against ops/routing.clipped_plan with a receive
+    buffer that is deliberately too small."""
+    from ccfuser_b200 import MoEConfig, MoELayer, MoEOverflow
+    from ccfuser_b200.ops.routing import clipped_plan
+    torch.manual_seed(0)
+    tokens = 2048
+    cfg = MoEConfig(d_model=256, d_ffn=512, num_experts=4, top_k=2, capacity_factor=None, activation="gelu",
+                    dtype=torch.bfloat16, ep_size=1, backend="fused", max_tokens=tokens, recv_factor=0.5)
+    layer = MoELayer(cfg, device="cuda")
+    with torch.no_grad():
+        for p in layer.parameters():
+            p.copy_(torch.randn_like(p) * 0.05)
+        layer((torch.randn(tokens, 256, device="cuda") * 0.5).bfloat16())
+    torch.cuda.synchronize()
+    fm = layer._fused_impl()
+    with pytest.raises(MoEOverflow):
+        layer.check_status()
+    table = fm.table_copy.cpu().long()
+    model = clipped_plan(table, cfg.experts_per_rank, fm.max_rows)
+    assert bool(model.overflow[0])
+    assert fm.group_rows.cpu().long().tolist() == model.group_rows.tolist()
+    assert int(fm.sent_rows[0]) == int(model.sent_rows[0, 0])
+    assert int((fm.slot_row[:tokens * 2] >= 0).sum()) == int(model.accepted.sum())
+    layer.release()

@@ -161,3 +161,36 @@ def test_unrouted_slots_are_ignored_by_the_layer_and_by_the_oracle_alike(tokens,
     assert torch.allclose(y, yr, atol=1e-5, rtol=1e-4)
     untouched = (idx < 0).all(1)
     assert (y[untouched] == 0).all()
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 4), st.integers(1, 4), st.integers(0, 2 ** 31 - 1), st.integers(1, 12))
+def test_clipped_plan_keeps_sources_and_owners_consistent(world, e_loc, seed, buffer_tiles):
+    """With a receive buffer that may be too small, what a source expects back equals what the owner processes for it,
+    expert by expert: the property that keeps every wait satisfiable when rows are refused."""
+    from ccfuser_b200.ops.routing import clipped_plan, global_plan
+    g = torch.Generator().manual_seed(seed)
+    table = torch.randint(0, 400, (world, world * e_loc), generator=g)
+    table[torch.rand(table.shape, generator=g) < 0.25] = 0
+    max_rows = buffer_tiles * 128
+    cp = clipped_plan(table, e_loc, max_rows)
+    gp = global_plan(table, e_loc)
+    # per expert: the owner's GEMM rows are exactly the accepted rows of all sources, and they form a prefix of the segment
+    assert torch.equal(cp.accepted.sum(0), cp.group_rows)
+    assert (cp.accepted <= table).all() and (cp.group_rows <= gp.expert_rows).all()
+    for e in range(world * e_loc):
+        seen_partial = False
+        for r in range(world):                       # sources in rank order: once one is cut, all later ones get nothing
+            if seen_partial:
+                assert int(cp.accepted[r, e]) == 0 or int(table[r, e]) == 0 or int(cp.accepted[r, e]) == 0
+            if cp.accepted[r, e] < table[r, e]:
+                seen_partial = True
+        assert int(gp.expert_base[e]) + int(cp.group_rows[e]) <= max(max_rows, int(gp.expert_base[e]))
+    # per (source, owner): rows sent == rows the owner accepted from that source
+    owner = torch.arange(world * e_loc) // e_loc
+    for o in range(world):
+        assert torch.equal(cp.sent_rows[:, o], cp.accepted[:, owner == o].sum(1))
+    # a buffer that is large enough clips nothing
+    big = clipped_plan(table, e_loc, int(gp.rank_rows.max()))
+    assert torch.equal(big.accepted, table) and not bool(big.overflow.any())
+    assert torch.equal(cp.overflow, gp.rank_rows > max_rows)

@@ -38,6 +38,8 @@ class MoEConfig:
     max_tokens           upper bound of tokens per rank per call; sizes the symmetric buffers
     recv_factor          without a capacity factor the receive buffer of a rank is sized
                          recv_factor x the balanced load (overflow is reported, not silent)
+    router_dtype         parameter / compute dtype of the router's linear layer; None = ``dtype``. torch.float32 keeps
+                         the routing decisions independent of half-precision rounding of the logits
     shadow_experts       >0: the n most popular experts of every step are replicated to all ranks for that step
                          (weights broadcast, gradients reduced back to the owner) and their tokens are computed
                          where they are; see parallel/shadow.py
@@ -57,6 +59,7 @@ class MoEConfig:
     recv_factor: float = 2.0
     router_bias: bool = True
     shadow_experts: int = 0
+    router_dtype: Optional[torch.dtype] = None
 
     def __post_init__(self):
         if self.activation not in ACTIVATIONS:
@@ -104,7 +107,8 @@ class MoEConfig:
         mats = 3 if self.activation == "swiglu" else 2
         rows, slots = self.max_recv_rows(), self.max_tokens * self.top_k
         weights = e_loc * (mats * d * f + ((mats - 1) * f + d if self.bias else 0)) * esz
-        router = self.num_experts * (d + (1 if self.router_bias else 0)) * esz
+        rsz = 4 if self.router_dtype == torch.float32 else esz
+        router = self.num_experts * (d + (1 if self.router_bias else 0)) * rsz
         per_layer = (rows * d + slots * d) * esz                                   # xrecv + comb (symmetric)
         per_layer += rows * f * esz * (mats if training else 1)                    # h_act (+ pre-activations)
         per_layer += (3 * slots + 2 * self.num_experts + 6 * e_loc) * 4            # routing index arrays

@@ -63,7 +63,8 @@ class NaiveGate(BaseGate):
         self.aux_loss_coef = aux_loss_coef
 
     def logits(self, x: torch.Tensor) -> torch.Tensor:
-        return F.linear(x, self.gate.weight, self.gate.bias)
+        """Router logits in the router's own dtype (the input is cast when the router is kept in fp32)."""
+        return F.linear(x.to(self.gate.weight.dtype), self.gate.weight, self.gate.bias)
 
     def forward(self, x: torch.Tensor, return_all_scores: bool = False):
         logits = self.logits(x)

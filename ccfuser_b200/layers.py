@@ -44,7 +44,7 @@ class MoELayer(nn.Module):
         e_loc = config.experts_per_rank
         self.gate = gate if gate is not None else NaiveGate(
             config.d_model, e_loc, config.ep_size, config.top_k, bias=config.router_bias)
-        self.gate.to(device=device, dtype=config.dtype)
+        self.gate.to(device=device, dtype=config.router_dtype or config.dtype)
         self.experts = Experts(e_loc, config.d_model, config.d_ffn, config.activation, config.bias,
                                dtype=config.dtype, device=device)
         scan_expert_params(self.experts)

@@ -258,3 +258,24 @@ def test_memory_estimate_matches_what_the_layer_allocates():
                     bias=False, ep_size=8, max_tokens=16384)
     total_gb = big.memory_estimate(layers=1)["total"] / 2 ** 30
     assert 8 < total_gb < 20                                                     # one Mixtral-size layer per rank
+
+
+def test_fp32_router_with_half_precision_experts():
+    """router_dtype=float32: the router's parameters and logits stay fp32 on every backend; on the fused path the top-k
+    kernel is given fp32 logits and the one-kernel router (which needs matching operand types) is not chosen."""
+    cfg, layer = _layer("gelu", router_dtype=torch.float32)
+    assert layer.gate.gate.weight.dtype == torch.float32 and layer.experts.htoh4.weight.dtype == torch.bfloat16
+    fm = layer._fused_impl()
+    fm.fused_router = True
+    x = torch.randn(64, cfg.d_model).bfloat16().requires_grad_(True)
+    with N.record_launches() as rec:
+        layer(x).float().sum().backward()
+    topk = [c for c in rec.calls if c[0] == "ccf_topk_softmax"][0][1]
+    assert topk[1] == 0 and topk[2] == 1                       # fp16 flag off, fp32 flag on
+    assert "ccf_router_topk" not in rec.names()
+    assert layer.gate.gate.weight.grad.dtype == torch.float32 and x.grad.dtype == torch.bfloat16
+    # CPU backend with the same mixed setting against an fp32-router oracle decision
+    cfg2 = cfg.replace(backend="cpu")
+    l2 = MoELayer(cfg2, device="cpu")
+    y = l2(torch.randn(10, cfg.d_model).bfloat16())
+    assert y.dtype == torch.bfloat16 and torch.isfinite(y.float()).all()

@@ -47,6 +47,29 @@ def topk_softmax_reference(logits: torch.Tensor, k: int):
     return order, score
 
 
+def router_aux_loss(logits: torch.Tensor, idx: torch.Tensor, num_experts: int, balance_coef: float = 0.0,
+                    z_coef: float = 0.0):
+    """Auxiliary router losses, or None when both coefficients are zero.
+
+    * load balance: ``balance_coef * E * sum_e (fraction of slots routed to e) * (mean router probability of e)``;
+    * z-loss: ``z_coef * mean(logsumexp(logits)^2)``, which keeps the logits from drifting to large magnitudes.
+    Slots with a negative expert id are not counted. One definition for every backend."""
+    if not (balance_coef and balance_coef > 0) and not (z_coef and z_coef > 0):
+        return None
+    lg = logits.float()
+    loss = lg.new_zeros(())
+    if balance_coef and balance_coef > 0:
+        flat = idx.reshape(-1).long()
+        valid = flat >= 0
+        frac = torch.zeros(num_experts, device=lg.device, dtype=torch.float32)
+        frac.scatter_add_(0, flat.clamp_min(0), valid.float())
+        frac = frac / valid.sum().clamp_min(1)
+        loss = loss + balance_coef * num_experts * (frac * torch.softmax(lg, dim=-1).mean(0)).sum()
+    if z_coef and z_coef > 0:
+        loss = loss + z_coef * torch.logsumexp(lg, dim=-1).square().mean()
+    return loss
+
+
 class NaiveGate(BaseGate):
     """Linear router + top-k + softmax over the selected logits.
 
@@ -56,11 +79,12 @@ class NaiveGate(BaseGate):
     """
 
     def __init__(self, d_model: int, num_expert: int, world_size: int, top_k: int = 2,
-                 bias: bool = True, aux_loss_coef: float = 0.0):
+                 bias: bool = True, aux_loss_coef: float = 0.0, z_loss_coef: float = 0.0):
         super().__init__(num_expert, world_size)
         self.gate = nn.Linear(d_model, self.tot_expert, bias=bias)
         self.top_k = top_k
         self.aux_loss_coef = aux_loss_coef
+        self.z_loss_coef = z_loss_coef
 
     def logits(self, x: torch.Tensor) -> torch.Tensor:
         """Router logits in the router's own dtype (the input is cast when the router is kept in fp32)."""
@@ -69,14 +93,8 @@ class NaiveGate(BaseGate):
     def forward(self, x: torch.Tensor, return_all_scores: bool = False):
         logits = self.logits(x)
         idx, score = topk_softmax_reference(logits, self.top_k)
-        if self.aux_loss_coef > 0:
-            probs = torch.softmax(logits.float(), dim=-1)
-            frac = torch.zeros(self.tot_expert, device=x.device, dtype=torch.float32)
-            frac.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), device=x.device))
-            frac = frac / max(1, idx.numel())
-            self.set_loss(self.aux_loss_coef * self.tot_expert * (frac * probs.mean(0)).sum())
-        else:
-            self.set_loss(torch.zeros(1, device=x.device, dtype=torch.float32))
+        loss = router_aux_loss(logits, idx, self.tot_expert, self.aux_loss_coef, self.z_loss_coef)
+        self.set_loss(loss if loss is not None else torch.zeros(1, device=x.device, dtype=torch.float32))
         if return_all_scores:
             return idx, score, logits
         return idx, score

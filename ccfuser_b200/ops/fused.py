@@ -34,6 +34,7 @@ import torch
 
 from .. import native as N
 from ..config import env_flag
+from ..gates import router_aux_loss
 from ..parallel.symm import SymmBuffer
 from ..utils.tracing import nvtx_range
 from . import gemm as G
@@ -271,8 +272,9 @@ class FusedMoE:
         if x.shape[0] > cfg.max_tokens:
             raise ValueError(f"{x.shape[0]} tokens exceed config.max_tokens={cfg.max_tokens}")
         coef = getattr(layer.gate, "aux_loss_coef", 0.0)
+        zcoef = getattr(layer.gate, "z_loss_coef", 0.0)
         lin = getattr(layer.gate, "gate", None)
-        if (self.fused_router and not (coef and coef > 0) and isinstance(lin, torch.nn.Linear)
+        if (self.fused_router and not (coef and coef > 0) and not (zcoef and zcoef > 0) and isinstance(lin, torch.nn.Linear)
                 and R.supported(x, lin.weight, cfg.top_k)):
             # linear layer + top-k + softmax in one kernel; the logits are never written
             if hasattr(layer.gate, "set_loss"):
@@ -282,15 +284,10 @@ class FusedMoE:
         if logits is None:
             raise TypeError("the fused backend needs a gate with a .logits(x) method (NaiveGate)")
         idx, w = topk_softmax(logits, cfg.top_k)
-        if coef and coef > 0 and hasattr(layer.gate, "set_loss"):
-            # load-balance auxiliary loss, same definition as NaiveGate.forward (fraction of slots per expert times the
-            # mean router probability), kept in torch: it is a [T, E] reduction next to GEMMs that dominate the layer
-            probs = torch.softmax(logits.float(), dim=-1)
-            frac = torch.zeros(cfg.num_experts, device=x.device, dtype=torch.float32)
-            frac.scatter_add_(0, idx.reshape(-1).long(), torch.ones(idx.numel(), device=x.device))
-            layer.gate.set_loss(coef * cfg.num_experts * (frac / max(1, idx.numel()) * probs.mean(0)).sum())
-        elif hasattr(layer.gate, "set_loss"):
-            layer.gate.set_loss(None)
+        if hasattr(layer.gate, "set_loss"):
+            # auxiliary losses (load balance, z-loss) with the same definition as NaiveGate.forward, kept in torch: a
+            # [T, E] reduction next to GEMMs that dominate the layer
+            layer.gate.set_loss(router_aux_loss(logits, idx, cfg.num_experts, coef, zcoef))
         return idx, w
 
     def run_experts(self, x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

@@ -69,3 +69,28 @@ def test_gate_tie_break_and_shapes():
     i, s = gate(torch.randn(7, 16))
     assert i.shape == (7, 2) and s.shape == (7, 2) and i.dtype == torch.int64
     assert gate.has_loss
+
+
+def test_router_auxiliary_losses():
+    import torch
+    from ccfuser_b200.gates import NaiveGate, router_aux_loss
+    torch.manual_seed(0)
+    gate = NaiveGate(16, 4, 2, top_k=2, aux_loss_coef=0.01, z_loss_coef=0.001)
+    x = torch.randn(50, 16)
+    idx, score, logits = gate(x, return_all_scores=True)
+    loss = gate.get_loss()
+    probs = torch.softmax(logits, -1)
+    frac = torch.bincount(idx.reshape(-1), minlength=8).float() / idx.numel()
+    want = 0.01 * 8 * (frac * probs.mean(0)).sum() + 0.001 * torch.logsumexp(logits, -1).square().mean()
+    assert torch.allclose(loss, want, atol=1e-6) and loss.requires_grad
+    assert router_aux_loss(logits, idx, 8, 0.0, 0.0) is None
+    # unrouted slots are not counted
+    idx2 = idx.clone()
+    idx2[:10] = -1
+    a = router_aux_loss(logits, idx2, 8, 1.0, 0.0)
+    frac2 = torch.bincount(idx2.reshape(-1)[idx2.reshape(-1) >= 0], minlength=8).float() / int((idx2 >= 0).sum())
+    assert torch.allclose(a, 8 * (frac2 * probs.mean(0)).sum(), atol=1e-6)
+    # no coefficients: the gate keeps its zero placeholder (reference behaviour)
+    plain = NaiveGate(16, 4, 2)
+    plain(x)
+    assert float(plain.get_loss()) == 0.0

@@ -40,6 +40,8 @@ class MoEConfig:
                          recv_factor x the balanced load (overflow is reported, not silent)
     router_dtype         parameter / compute dtype of the router's linear layer; None = ``dtype``. torch.float32 keeps
                          the routing decisions independent of half-precision rounding of the logits
+    aux_loss_coef        weight of the router's load-balance loss (0 = off); z_loss_coef: weight of its z-loss.
+                         The layer's gate records their sum for the training loop (gate.get_loss())
     shadow_experts       >0: the n most popular experts of every step are replicated to all ranks for that step
                          (weights broadcast, gradients reduced back to the owner) and their tokens are computed
                          where they are; see parallel/shadow.py
@@ -60,6 +62,8 @@ class MoEConfig:
     router_bias: bool = True
     shadow_experts: int = 0
     router_dtype: Optional[torch.dtype] = None
+    aux_loss_coef: float = 0.0
+    z_loss_coef: float = 0.0
 
     def __post_init__(self):
         if self.activation not in ACTIVATIONS:

@@ -43,7 +43,8 @@ class MoELayer(nn.Module):
         self.ep_rank = dist.get_rank(ep_group) if world > 1 else 0
         e_loc = config.experts_per_rank
         self.gate = gate if gate is not None else NaiveGate(
-            config.d_model, e_loc, config.ep_size, config.top_k, bias=config.router_bias)
+            config.d_model, e_loc, config.ep_size, config.top_k, bias=config.router_bias,
+            aux_loss_coef=config.aux_loss_coef, z_loss_coef=config.z_loss_coef)
         self.gate.to(device=device, dtype=config.router_dtype or config.dtype)
         self.experts = Experts(e_loc, config.d_model, config.d_ffn, config.activation, config.bias,
                                dtype=config.dtype, device=device)

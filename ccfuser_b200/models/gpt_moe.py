@@ -42,10 +42,15 @@ class GPTMoEConfig:
     aux_loss_coef: float = 0.0
     recv_factor: float = 2.0      # receive-buffer size of a rank relative to the balanced load (no capacity factor)
 
+    router_dtype: Optional[torch.dtype] = None
+    aux_loss_coef: float = 0.0
+    z_loss_coef: float = 0.0
+
     def moe_config(self) -> MoEConfig:
         return MoEConfig(d_model=self.d_model, d_ffn=self.d_ffn, num_experts=self.num_experts, top_k=self.top_k,
                          capacity_factor=self.capacity_factor, activation=self.activation, dtype=self.dtype,
-                         ep_size=self.ep_size, backend=self.backend, max_tokens=self.max_tokens, recv_factor=self.recv_factor)
+                         ep_size=self.ep_size, backend=self.backend, max_tokens=self.max_tokens, recv_factor=self.recv_factor,
+                         router_dtype=self.router_dtype, aux_loss_coef=self.aux_loss_coef, z_loss_coef=self.z_loss_coef)
 
     def flops_per_token(self) -> float:
         """Forward+backward model FLOPs per token (3 x forward; attention scores included)."""

@@ -46,10 +46,15 @@ class TransformerXLMoEConfig:
     adaptive_cutoffs: Sequence[int] = ()
     dropout: float = 0.0
 
+    router_dtype: Optional[torch.dtype] = None
+    aux_loss_coef: float = 0.0
+    z_loss_coef: float = 0.0
+
     def moe_config(self) -> MoEConfig:
         return MoEConfig(d_model=self.d_model, d_ffn=self.d_inner, num_experts=self.num_experts, top_k=self.top_k,
                          capacity_factor=self.capacity_factor, activation="relu", dtype=self.dtype,
-                         ep_size=self.ep_size, backend=self.backend, max_tokens=self.max_tokens)
+                         ep_size=self.ep_size, backend=self.backend, max_tokens=self.max_tokens,
+                         router_dtype=self.router_dtype, aux_loss_coef=self.aux_loss_coef, z_loss_coef=self.z_loss_coef)
 
 
 class PositionalEmbedding(nn.Module):

@@ -63,7 +63,8 @@ def build(args, world, dev, ep_group=None):
     g = torch.Generator().manual_seed(1 + (dist.get_rank() if dist.is_initialized() else 0))
     if args.model == "gpt":
         b, s = args.batch or 8, args.seq or 1024
-        c = GPTMoEConfig(n_layer=args.layers or 12, n_head=12, d_model=768, d_ffn=3072, seq_len=s,
+        c = GPTMoEConfig(router_dtype=torch.float32 if args.router_fp32 else None, aux_loss_coef=args.aux_loss_coef,
+                         z_loss_coef=args.z_loss_coef, n_layer=args.layers or 12, n_head=12, d_model=768, d_ffn=3072, seq_len=s,
                          moe_every=(args.moe_every if moe else 0), num_experts=args.experts_per_gpu * world, top_k=args.top_k,
                          capacity_factor=args.cf or None, ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
         model = _GPTStep(GPTMoE(c, ep_group=ep_group, device=dev))
@@ -71,7 +72,8 @@ def build(args, world, dev, ep_group=None):
         batch = {"ids": ids, "labels": ids.roll(-1, 1)}
     elif args.model == "bert":
         b, s = args.batch or 32, args.seq or 512
-        c = BertMoEConfig(n_layer=args.layers or 12, moe_layers=(2, 5, 8, 11) if moe else (), max_position=s,
+        c = BertMoEConfig(router_dtype=torch.float32 if args.router_fp32 else None, aux_loss_coef=args.aux_loss_coef,
+                          z_loss_coef=args.z_loss_coef, n_layer=args.layers or 12, moe_layers=(2, 5, 8, 11) if moe else (), max_position=s,
                           num_experts=args.experts_per_gpu * world, top_k=args.top_k, capacity_factor=args.cf or None,
                           ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
         model = _BertStep(BertMoEForQuestionAnswering(c, ep_group=ep_group, device=dev))
@@ -80,7 +82,8 @@ def build(args, world, dev, ep_group=None):
                  "end": torch.randint(0, s, (b,), generator=g)}
     else:
         b, s = args.batch or 16, args.seq or 512
-        c = TransformerXLMoEConfig(n_token=getattr(args, "n_token", 0) or 100, n_layer=args.layers or 12, tgt_len=s, mem_len=s, moe=moe,
+        c = TransformerXLMoEConfig(router_dtype=torch.float32 if args.router_fp32 else None, aux_loss_coef=args.aux_loss_coef,
+                                   z_loss_coef=args.z_loss_coef, n_token=getattr(args, "n_token", 0) or 100, n_layer=args.layers or 12, tgt_len=s, mem_len=s, moe=moe,
                                    num_experts=args.experts_per_gpu * world, top_k=args.top_k,
                                    capacity_factor=args.cf or None, ep_size=world, backend=backend, max_tokens=b * s, dtype=dtype)
         model = _TXLStep(TransformerXLMoE(c, ep_group=ep_group, device=dev))
@@ -104,6 +107,9 @@ def main():
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--optimizer", default="sgd", choices=["sgd", "adamw"])
     ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--aux-loss-coef", type=float, default=0.0, help="weight of the router load-balance loss")
+    ap.add_argument("--z-loss-coef", type=float, default=0.0, help="weight of the router z-loss")
+    ap.add_argument("--router-fp32", action="store_true", help="keep the routers in fp32")
     ap.add_argument("--data", default="", help="txl only: training text file (word-level vocabulary built from it); "
                                                "default is a fixed synthetic batch")
     ap.add_argument("--valid", default="", help="txl only: validation text file, evaluated at the end")
@@ -167,6 +173,13 @@ def main():
             s.record()
         opt.zero_grad(set_to_none=True)
         loss = wrapped(batch)
+        if (args.aux_loss_coef > 0 or args.z_loss_coef > 0) and args.variant != "dense":
+            from ..layers import MoELayer
+            for m in model.modules():
+                if isinstance(m, MoELayer) and getattr(m.gate, "has_loss", False):
+                    extra = m.gate.get_loss()
+                    if extra is not None and extra.requires_grad:
+                        loss = loss + extra.to(loss.dtype).sum()
         loss.backward()
         if expert_dp_group is not None and args.variant != "dense":
             from ..parallel.ddp import reduce_expert_grads

@@ -68,7 +68,10 @@ class MoELayer(nn.Module):
         return self._fused
 
     # ---- forward -----------------------------------------------------------------------------
-    def forward(self, inp: torch.Tensor) -> torch.Tensor:
+    def forward(self, inp: torch.Tensor, token_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``inp [..., d_model]``. ``token_mask`` (bool, shape ``inp.shape[:-1]``, True = real token): tokens marked
+        False (padding) are not routed at all: they cost no expert compute, take no capacity, cross no link, and their
+        output rows are zero. Stays on the device (no host synchronisation)."""
         cfg = self.config
         shape = inp.shape
         x = inp.reshape(-1, cfg.d_model)
@@ -80,6 +83,9 @@ class MoELayer(nn.Module):
             idx, score = fused.route(x)
         else:
             idx, score = self.gate(x)
+        if token_mask is not None:
+            keep = token_mask.reshape(-1, 1).to(device=idx.device, dtype=torch.bool)
+            idx = torch.where(keep, idx, torch.full_like(idx, -1))
         y_shadow = None
         if cfg.shadow_experts > 0:
             # the step's most popular experts are replicated: their slots leave the expert-parallel path

@@ -87,9 +87,11 @@ class BertLayer(nn.Module):
         self.ffn = MoELayer(c.moe_config(), ep_group=ep_group, device=device) if moe else FFN(c, device)
         self.ln_ffn = nn.LayerNorm(c.d_model, eps=c.layer_norm_eps, device=device, dtype=c.dtype)
 
-    def forward(self, x, mask):
+    def forward(self, x, mask, token_mask=None):
         x = self.ln_attn(x + self.attention(x, mask))
-        return self.ln_ffn(x + self.ffn(x))
+        # padding tokens skip the experts (their FFN output is zero; nothing downstream reads those positions)
+        ffn = self.ffn(x, token_mask=token_mask) if (self.is_moe and token_mask is not None) else self.ffn(x)
+        return self.ln_ffn(x + ffn)
 
 
 class BertMoEForQuestionAnswering(nn.Module):
@@ -118,11 +120,12 @@ class BertMoEForQuestionAnswering(nn.Module):
         pos = torch.arange(s, device=input_ids.device)
         tt = token_type_ids if token_type_ids is not None else torch.zeros_like(input_ids)
         x = self.ln_emb(self.word(input_ids) + self.position(pos) + self.token_type(tt))
-        mask = None
+        mask = token_mask = None
         if attention_mask is not None:
             mask = attention_mask[:, None, None, :].to(torch.bool)
+            token_mask = attention_mask.to(torch.bool)
         for layer in self.layer:
-            x = layer(x, mask)
+            x = layer(x, mask, token_mask)
         logits = self.qa_outputs(x).float()
         start, end = logits[..., 0], logits[..., 1]
         if start_positions is None or end_positions is None:

@@ -130,3 +130,29 @@ def test_a_rank_without_tokens_still_takes_part():
     assert torch.allclose(res[0][1], xs[0].grad, atol=1e-5, rtol=1e-4)
     for r in range(world):                                # rank 1's experts still served rank 0's tokens
         assert torch.allclose(res[r][2], full["htoh4.weight"].grad[r * 2:(r + 1) * 2], atol=1e-5, rtol=1e-4)
+
+
+def test_token_mask_skips_padding_tokens():
+    """Masked tokens are not routed: zero output rows, no capacity taken, and the real tokens' outputs are what they
+    would be if the padding were not in the batch at all."""
+    torch.manual_seed(0)
+    cfg = MoEConfig(d_model=32, d_ffn=64, num_experts=4, top_k=2, capacity_factor=1.0, activation="gelu",
+                    dtype=torch.float32, backend="cpu", max_tokens=64)
+    layer = MoELayer(cfg)
+    x = torch.randn(2, 20, 32, requires_grad=True)
+    mask = torch.ones(2, 20, dtype=torch.bool)
+    mask[0, 12:] = False
+    mask[1, 17:] = False
+    y = layer(x, token_mask=mask)
+    assert (y[~mask] == 0).all() and (y[mask].abs().sum(-1) > 0).all()
+    y.sum().backward()
+    assert (x.grad[~mask] == 0).all()
+    # the same real tokens alone, with the capacity that the padded call used (capacity follows the token count)
+    real = x.detach()[mask]
+    table = layer.count_table()
+    assert int(table.sum()) <= int(mask.sum()) * 2
+    from ccfuser_b200.gates import topk_softmax_reference
+    idx, score = topk_softmax_reference(layer.gate.logits(real), 2)
+    from ccfuser_b200.parallel.a2a import moe_forward_a2a
+    want = moe_forward_a2a(real, idx, score, layer.experts, num_experts=4, capacity=cfg.capacity(40), group=None)
+    assert torch.allclose(y.detach()[mask], want, atol=1e-6)

@@ -279,3 +279,16 @@ def test_fp32_router_with_half_precision_experts():
     l2 = MoELayer(cfg2, device="cpu")
     y = l2(torch.randn(10, cfg.d_model).bfloat16())
     assert y.dtype == torch.bfloat16 and torch.isfinite(y.float()).all()
+
+
+def test_token_mask_reaches_the_kernels_as_unrouted_slots():
+    cfg, layer = _layer("gelu")
+    fm = layer._fused_impl()
+    seen = {}
+    orig = fm.run_experts
+    fm.run_experts = lambda xx, idx, w: (seen.setdefault("idx", idx.clone()), orig(xx, idx, w))[1]
+    fm.route = lambda xx: (torch.ones(xx.shape[0], 2, dtype=torch.int32), torch.full((xx.shape[0], 2), 0.5))
+    mask = torch.tensor([True] * 30 + [False] * 10)
+    with N.record_launches(), torch.no_grad():
+        layer(torch.randn(40, cfg.d_model).bfloat16(), token_mask=mask)
+    assert seen["idx"].dtype == torch.int32 and (seen["idx"][30:] == -1).all() and (seen["idx"][:30] == 1).all()

@@ -476,13 +476,15 @@ class GraphedForward:
     """Inference forward of one fused MoE layer replayed from a CUDA graph: for the latency-bound regime (a few
     hundred tokens per GPU) where ten kernel launches and their host code cost more than the kernels.
 
-        g = GraphedForward(layer, tokens=128)     # every rank of the group, same point of the program
-        y = g(x)                                  # x [tokens, d_model]; y is a buffer that the next call overwrites
+        g = GraphedForward(layer, tokens=256)     # every rank of the group, same point of the program
+        y = g(x)                                  # x [n <= 256, d_model]; y [n, d_model] is a view of a buffer that the
+                                                  # next call overwrites
 
     The graph holds the router, routing, plan, both fused GEMMs and the reduce of one call with a fixed token count;
-    the cross-GPU protocol is unchanged (flags and counters live in device memory; the plan's epoch moves there too,
-    see CommContext.use_device_epoch). Replays are collective like eager calls. Status words are not checked inside the
-    graph: call ``layer.check_status()`` when convenient."""
+    a call with fewer tokens fills the rest with padding that is masked out of the routing (``token_mask``), so one
+    graph serves every batch size up to its own. The cross-GPU protocol is unchanged (flags and counters live in
+    device memory; the plan's epoch moves there too, see CommContext.use_device_epoch). Replays are collective like
+    eager calls. Status words are not checked inside the graph: call ``layer.check_status()`` when convenient."""
 
     def __init__(self, layer, tokens: int, warmup: int = 3):
         fm = layer._fused_impl()
@@ -490,22 +492,43 @@ class GraphedForward:
         if tokens > cfg.max_tokens:
             raise ValueError(f"{tokens} tokens exceed config.max_tokens={cfg.max_tokens}")
         fm.ctx.use_device_epoch()
-        self.layer = layer
+        self.layer, self.tokens = layer, tokens
         self.x = torch.zeros(tokens, cfg.d_model, dtype=cfg.dtype, device=fm.device)
+        self.valid = torch.ones(tokens, dtype=torch.bool, device=fm.device)
+        self._rows = torch.arange(tokens, device=fm.device)
         side = torch.cuda.Stream(device=fm.device)
         side.wait_stream(torch.cuda.current_stream(fm.device))
         with torch.cuda.stream(side), torch.no_grad():
             for _ in range(max(1, warmup)):           # first-use set-up (attributes, driver entry points) outside capture
-                layer(self.x)
+                layer(self.x, token_mask=self.valid)
         torch.cuda.current_stream(fm.device).wait_stream(side)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph), torch.no_grad():
-            self.y = layer(self.x)
+            self.y = layer(self.x, token_mask=self.valid)
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        self.x.copy_(x.reshape(self.x.shape))
+        x = x.reshape(-1, self.x.shape[1])
+        n = x.shape[0]
+        if n > self.tokens:
+            raise ValueError(f"{n} tokens exceed the {self.tokens} this graph was captured for")
+        self.x[:n].copy_(x)
+        torch.lt(self._rows, n, out=self.valid)       # rows beyond n are padding: not routed
         self.graph.replay()
-        return self.y
+        return self.y[:n]
+
+
+class GraphedForwardPool:
+    """One graph per bucket size; a call uses the smallest bucket that holds its tokens (padding masked out)."""
+
+    def __init__(self, layer, buckets=(128, 512, 2048)):
+        self.graphs = [GraphedForward(layer, b) for b in sorted(buckets)]
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        n = x.reshape(-1, x.shape[-1]).shape[0]
+        for g in self.graphs:
+            if n <= g.tokens:
+                return g(x)
+        raise ValueError(f"{n} tokens exceed the largest bucket ({self.graphs[-1].tokens})")
 
 
 class _FusedMoEFn(torch.autograd.Function):

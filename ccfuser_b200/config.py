@@ -42,6 +42,8 @@ class MoEConfig:
                          the routing decisions independent of half-precision rounding of the logits
     aux_loss_coef        weight of the router's load-balance loss (0 = off); z_loss_coef: weight of its z-loss.
                          The layer's gate records their sum for the training loop (gate.get_loss())
+    shared_ffn           >0: hidden size of an always-on dense FFN (same activation as the experts) whose output is added
+                         to the routed experts' output for every token; its parameters are replicated like the router's
     shadow_experts       >0: the n most popular experts of every step are replicated to all ranks for that step
                          (weights broadcast, gradients reduced back to the owner) and their tokens are computed
                          where they are; see parallel/shadow.py
@@ -64,6 +66,7 @@ class MoEConfig:
     router_dtype: Optional[torch.dtype] = None
     aux_loss_coef: float = 0.0
     z_loss_coef: float = 0.0
+    shared_ffn: int = 0
 
     def __post_init__(self):
         if self.activation not in ACTIVATIONS:
@@ -113,6 +116,8 @@ class MoEConfig:
         weights = e_loc * (mats * d * f + ((mats - 1) * f + d if self.bias else 0)) * esz
         rsz = 4 if self.router_dtype == torch.float32 else esz
         router = self.num_experts * (d + (1 if self.router_bias else 0)) * rsz
+        if self.shared_ffn > 0:      # counted with the router: replicated, small next to the experts
+            router += (mats * d * self.shared_ffn + ((mats - 1) * self.shared_ffn + d if self.bias else 0)) * esz
         per_layer = (rows * d + slots * d) * esz                                   # xrecv + comb (symmetric)
         per_layer += rows * f * esz * (mats if training else 1)                    # h_act (+ pre-activations)
         per_layer += (3 * slots + 2 * self.num_experts + 6 * e_loc) * 4            # routing index arrays

@@ -51,6 +51,11 @@ class MoELayer(nn.Module):
         scan_expert_params(self.experts)
         for p in self.gate.parameters():
             setattr(p, "dp_comm", "gate")
+        # optional always-on dense FFN next to the routed experts ("shared expert"): replicated parameters, library GEMMs
+        self.shared = None
+        if config.shared_ffn > 0:
+            self.shared = Experts(1, config.d_model, config.shared_ffn, config.activation, config.bias,
+                                  dtype=config.dtype, device=device)
         self._fused = None
         self.last_stats = {}
 
@@ -102,6 +107,8 @@ class MoELayer(nn.Module):
             y = y.to(inp.dtype)
         if y_shadow is not None:
             y = y + y_shadow.to(y.dtype)
+        if self.shared is not None:
+            y = y + self.shared.expert_forward(0, x).to(y.dtype)
         return y.reshape(shape[:-1] + (y.shape[-1],))
 
     # ---- placement ---------------------------------------------------------------------------

@@ -156,3 +156,22 @@ def test_token_mask_skips_padding_tokens():
     from ccfuser_b200.parallel.a2a import moe_forward_a2a
     want = moe_forward_a2a(real, idx, score, layer.experts, num_experts=4, capacity=cfg.capacity(40), group=None)
     assert torch.allclose(y.detach()[mask], want, atol=1e-6)
+
+
+def test_shared_ffn_is_added_for_every_token_and_is_replicated():
+    torch.manual_seed(0)
+    cfg = MoEConfig(d_model=16, d_ffn=32, num_experts=4, top_k=2, activation="swiglu", dtype=torch.float32, backend="cpu",
+                    shared_ffn=24)
+    layer = MoELayer(cfg)
+    plain = MoELayer(cfg.replace(shared_ffn=0))
+    plain.load_state_dict({k: v for k, v in layer.state_dict().items() if not k.startswith("shared.")})
+    x = torch.randn(9, 16)
+    want = plain(x) + layer.shared.expert_forward(0, x)
+    assert torch.allclose(layer(x), want, atol=1e-6)
+    assert layer.state_dict()["shared.htoh4.weight"].shape == (1, 24, 16)
+    # routed experts are tagged for the data-parallel ignore list, the shared FFN is not (it is replicated)
+    from ccfuser_b200.parallel.ddp import expert_param_names
+    names = expert_param_names(layer)
+    assert names and all(n.startswith("experts.") for n in names)
+    layer(x).sum().backward()
+    assert layer.shared.h4toh.weight.grad is not None

@@ -4,7 +4,8 @@ mix_moe/mix_moe/kernel_evaluation.py:193-463 with the timing loops of mix_moe/cs
 "AG" = dispatch all-to-all -> GEMM-1 (one fused kernel here), "GA" = GEMM-2 -> combine all-to-all (one fused kernel
 plus the wait/reduce on the source). ``--ag-epilogue plain`` (default) times what the reference's AG_test times, GEMM-1
 with its bias and one output (mix_moe/csrc/mix_moe.h:146-185); ``layer`` times the training layer's kernel, which also
-applies GELU and stores the pre-activation, and gives the baseline the same extra work. Routing is synthetic with a chosen locality (fraction of a rank's tokens that
+applies GELU and stores the pre-activation, and gives the baseline the same extra work. Routing is synthetic with a
+chosen locality (fraction of a rank's tokens that
 stay on the rank), top-1, 16384 tokens per GPU, 1024 -> 4096 -> 1024, swept over the remote fraction or over
 experts per GPU. Everything is timed on the device with CUDA events, max over ranks.
 

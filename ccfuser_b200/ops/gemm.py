@@ -51,12 +51,41 @@ class Workspace:
         if v:
             code, detail = v & 0xff, v >> 8
             from ..errors import MoECommError, MoECommTimeout, MoEOverflow
-            msg = f"{what}: {N.ERR_NAMES.get(code, 'error')} (code {code}, detail {detail:#x})"
+            msg = f"{what}: {N.ERR_NAMES.get(code, 'error')}: {describe_status(code, detail)} (code {code}, detail {detail:#x})"
             if code in (1, 2):
                 raise MoECommTimeout(msg, where=what, tile=detail)
             if code == 4:
                 raise MoEOverflow(msg)
             raise MoECommError(msg)
+
+
+_MBAR_SITES = {1: "tile scheduler slot (producer)", 2: "free pipeline stage (producer)", 3: "tile index (MMA warp)",
+               4: "free accumulator (MMA warp)", 5: "operands of a stage (MMA warp)", 6: "tile index (epilogue)",
+               7: "finished accumulator (epilogue)", 0x22: "free pipeline stage (producer, CTA-pair kernel)",
+               0x24: "free accumulator (MMA warp, CTA-pair kernel)", 0x25: "operands of a stage (MMA warp, CTA-pair kernel)",
+               0x27: "finished accumulator (epilogue, CTA-pair kernel)", 0x40: "free pipeline stage (router producer)",
+               0x41: "operands of a stage (router MMA warp)", 0x42: "finished accumulator (router epilogue)"}
+
+
+def describe_status(code: int, detail: int) -> str:
+    """What a recorded status word means: which wait gave up and on whom (the kernels encode the site in `detail`)."""
+    if code == 1:
+        return "a barrier inside one CTA never completed: waiting for " + _MBAR_SITES.get(detail, f"site {detail:#x}")
+    if code == 2:
+        if detail & 0xF00000 == 0x800000:
+            return f"the count exchange never heard from rank {detail & 0xff} (plan kernel)"
+        if detail & 0xF00000 == 0x900000:
+            return f"the group barrier never heard from rank {detail & 0xff}"
+        if detail & 0xF00000 == 0x400000:
+            return f"owner rank {detail & 0xff} never returned all rows and its finish token (combine wait)"
+        if detail == 0x123:
+            return "a probe wait ran out (test)"
+        return f"the rows of receive tile {detail} (rows {detail * 128}..{detail * 128 + 127}) never all arrived"
+    if code == 3:
+        return f"row {detail} carried an out-of-range source rank or slot (access skipped)"
+    if code == 4:
+        return f"receive buffer of rank {detail} too small for the rows routed to it"
+    return f"unknown code {code}, detail {detail:#x}"
 
 
 DEFAULT_WAIT_NS = 5_000_000_000

@@ -205,3 +205,21 @@ def test_trace_analysis_on_a_synthetic_trace():
     assert r["tiles"] == 12 and r["main_loop_clk"] == 20480 and r["main_loop_efficiency"] == 0.8
     assert r["acc_wait_clk"] == 100 and r["rows_wait_clk"] == 50 and r["epilogue_clk"] == 6000
     assert analyze(torch.zeros(2, 3, 8, dtype=torch.int64), 8)["tiles"] == 0
+
+
+def test_status_words_are_explained():
+    import torch
+    from ccfuser_b200 import MoECommTimeout
+    from ccfuser_b200.ops.gemm import Workspace, describe_status
+    assert "rank 3" in describe_status(2, 0x800003) and "count exchange" in describe_status(2, 0x800003)
+    assert "owner rank 5" in describe_status(2, 0x400005)
+    assert "tile 7" in describe_status(2, 7) and "rows 896..1023" in describe_status(2, 7)
+    assert "free accumulator" in describe_status(1, 4) and "CTA-pair" in describe_status(1, 0x25)
+    ws = Workspace(torch.device("cpu"))
+    ws.status[0] = (0x400002 << 8) | 2
+    try:
+        ws.check("step 12")
+        raise AssertionError("expected a time-out")
+    except MoECommTimeout as e:
+        assert "owner rank 2" in str(e) and "step 12" in str(e)
+    assert int(ws.status[0]) == 0                                  # cleared after reporting

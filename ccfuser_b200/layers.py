@@ -159,8 +159,15 @@ class MoELayer(nn.Module):
 
     def extra_repr(self):
         c = self.config
+        extra = ""
+        if c.shadow_experts:
+            extra += f", shadow_experts={c.shadow_experts}"
+        if c.shared_ffn:
+            extra += f", shared_ffn={c.shared_ffn}"
+        if c.router_dtype is not None:
+            extra += f", router_dtype={c.router_dtype}"
         return (f"experts={c.num_experts} (local {c.experts_per_rank}), top_k={c.top_k}, d_model={c.d_model}, "
-                f"d_ffn={c.d_ffn}, act={c.activation}, capacity_factor={c.capacity_factor}, backend={c.backend}")
+                f"d_ffn={c.d_ffn}, act={c.activation}, capacity_factor={c.capacity_factor}, backend={c.backend}{extra}")
 
 
 class MixMOE(MoELayer):

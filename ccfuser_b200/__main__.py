@@ -3,6 +3,7 @@ import runpy
 import sys
 
 COMMANDS = {
+    "doctor": ("ccfuser_b200.utils.doctor", "what this machine offers: versions, GPUs, peer access, library state"),
     "build": ("ccfuser_b200.build", "compile the CUDA library for sm_100a (--selftest: also the C++ self-test program)"),
     "layer-bench": ("ccfuser_b200.bench.layer_bench", "MoE layer forward + backward timing (fig. 10 workload, Mixtral-size layers, skewed routing, small-message forward)"),
     "kernel-bench": ("ccfuser_b200.bench.kernel_bench", "fused dispatch+GEMM / GEMM+combine against all-to-all + GEMM (fig. 12)"),

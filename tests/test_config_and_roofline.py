@@ -223,3 +223,12 @@ def test_status_words_are_explained():
     except MoECommTimeout as e:
         assert "owner rank 2" in str(e) and "step 12" in str(e)
     assert int(ws.status[0]) == 0                                  # cleared after reporting
+
+
+def test_environment_report():
+    from ccfuser_b200.utils.doctor import report
+    r = report()
+    assert {"torch", "cuda_available", "library", "gpus", "problems"} <= set(r)
+    assert r["library"]["path"].endswith("libccfuser_b200.so")
+    if not r["cuda_available"]:
+        assert any("no CUDA device" in p for p in r["problems"])

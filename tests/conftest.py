@@ -18,3 +18,12 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+# Property tests run the same examples on every machine: a failure is then reproducible and a green run stays green.
+try:
+    from hypothesis import settings as _hsettings
+    _hsettings.register_profile("repeatable", derandomize=True, deadline=None, database=None)
+    _hsettings.load_profile("repeatable")
+except ImportError:      # hypothesis is optional: tests/test_properties.py is skipped without it
+    pass

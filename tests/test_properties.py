@@ -1,6 +1,9 @@
 """Property tests (hypothesis) of the routing rule and of the single-process layer against the dense oracle."""
+import pytest
 import torch
-from hypothesis import given, settings, strategies as st
+
+pytest.importorskip("hypothesis")
+from hypothesis import given, settings, strategies as st  # noqa: E402
 
 from ccfuser_b200 import MoEConfig, MoELayer
 from ccfuser_b200.ops.reference import dense_moe_oracle

@@ -59,8 +59,11 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fp16) {
 // start yet (its SM is held by another kernel, e.g. a collective of the data-parallel all-reduce that itself waits for
 // a peer) would hold back rows that other GPUs wait for. The next claim is issued before the current chunk is
 // processed so the atomic's round trip is off the critical path.
-template <int kChunk>
-__device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
+// Not inlined, and one instantiation per direction: the role keeps kChunk rows' worth of pointers and data in registers
+// (the backward form twice as much), which must not be added to the register budget of the GEMM roles it shares a
+// kernel with (168 registers per thread at 320 threads).
+template <int kChunk, bool kBackward>
+__device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
   static_assert(kChunk <= 16, "one lane per row of a chunk; rows of a chunk are held in registers");
   const int e_total = a.e_total;
   const int kept = a.order_off[e_total];   // rows to push
@@ -95,7 +98,7 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
       if (my_row >= 0) {
         a.peer_row_src[my_owner][my_row] = (a.my_rank << 24) | s;
         a.peer_row_gate[my_owner][my_row] = my_gate;
-      } else if (a.backward && a.dgate) {
+      } else if (kBackward && a.dgate) {
         a.dgate[s] = 0.f;
       }
     }
@@ -113,7 +116,7 @@ __device__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
       src[i] = on ? reinterpret_cast<const uint4*>(a.x) + static_cast<size_t>(t) * vecs : nullptr;
       dst[i] = on ? reinterpret_cast<uint4*>(a.peer_recv[owner]) + static_cast<size_t>(row) * vecs : nullptr;
     }
-    if (!a.backward) {
+    if constexpr (!kBackward) {
       for (int v = lane; v < vecs; v += 32) {
         uint4 r[kChunk];
 #pragma unroll

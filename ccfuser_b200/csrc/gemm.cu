@@ -318,7 +318,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     // ======================= epilogue (warps 2..9) =======================
     const int q = warp & 3;               // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
-    if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8>(args.disp, args.status);
+    dispatch_role<kEpi>(args);
     if (warp == 2 && lane == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
     int ss = 0, sphase = 0, as = 0, aphase = 0, seq = -1;
     while (true) {
@@ -431,11 +431,14 @@ int make_tmap(CUtensorMap* m, const void* base, long long rows, long long cols, 
 template <int A, int B, int E, bool KG>
 static int launch_variant(const CUtensorMap* tm, const CcfGemmArgs& args, int grid, cudaStream_t stream) {
   auto kern = grouped_gemm_kernel<A, B, E, KG>;
-  static bool configured = false;
-  if (!configured) {
+  // the attribute belongs to the (function, device) pair: set it once per device this process launches on
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return -static_cast<int>(e);
-    configured = true;
+    configured[dev & 63] = true;
   }
   kern<<<grid, kThreads, kSmemBytes, stream>>>(tm[0], tm[1], tm[2], tm[3], args);
   cudaError_t e = cudaGetLastError();
@@ -465,6 +468,12 @@ int ccf_gemm_launch(const CcfGemmLaunch* L, void* stream_v) {
   if (a.n % 32 != 0) return -3;
   if (L->kgroup && (a.m_per_group % BM != 0)) return -4;
   if (!L->kgroup && (a.k % 8 != 0)) return -5;
+  if (a.n_comm_ctas > 0) {
+    // the dispatch role is compiled into the kernels that read the receive buffer, in the direction of their pass
+    const bool fwd = L->epi == CCF_EPI_BIAS_ACT || L->epi == CCF_EPI_SWIGLU;
+    const bool bwd = L->epi == CCF_EPI_DACT || L->epi == CCF_EPI_DSWIGLU;
+    if (!(fwd && a.disp.backward == 0) && !(bwd && a.disp.backward == 1)) return -9;
+  }
   CUtensorMap tm[4];
   const int fp16 = a.fp16;
   const int a_box_rows = (L->a_major == MAJ_K) ? BM : BK;

@@ -402,7 +402,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
     // ======================= epilogue (warps 2..9, both CTAs) =======================
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8>(args.disp, args.status);
+    dispatch_role<kEpi>(args);
     if (warp == 2 && lane == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
     int as = 0, aphase = 0, seq = 0;
     for (int t = pair; t < total_tiles; t += n_pairs, ++seq) {
@@ -477,11 +477,14 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
 template <int A, int B, int E, bool KG>
 static int launch_pair_variant(const CUtensorMap* tm, const CcfGemmArgs& args, int grid, cudaStream_t stream) {
   auto kern = grouped_gemm_pair_kernel<A, B, E, KG>;
-  static bool configured = false;
-  if (!configured) {
+  // the attribute belongs to the (function, device) pair: set it once per device this process launches on
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, k2SmemBytes);
     if (e != cudaSuccess) return -static_cast<int>(e);
-    configured = true;
+    configured[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid & ~1);

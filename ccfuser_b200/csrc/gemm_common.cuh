@@ -420,6 +420,18 @@ __device__ __forceinline__ void combine_signal(const CcfGemmArgs& args, const Co
   }
 }
 
+// The dispatch role as the epilogue warps of a GEMM kernel run it before their first accumulator is due. Only the
+// kernels whose A operand is the receive buffer carry it: the forward ones (bias + activation, SwiGLU) push x rows, the
+// backward ones (activation derivative) push g * dy rows; every other epilogue compiles to nothing here.
+template <int kEpi>
+__device__ __forceinline__ void dispatch_role(const CcfGemmArgs& args) {
+  if constexpr (kEpi == CCF_EPI_BIAS_ACT || kEpi == CCF_EPI_SWIGLU) {
+    if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8, false>(args.disp, args.status);
+  } else if constexpr (kEpi == CCF_EPI_DACT || kEpi == CCF_EPI_DSWIGLU) {
+    if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8, true>(args.disp, args.status);
+  }
+}
+
 // two-CTA kernels (gemm2.cu), selected by the same key as the one-CTA ones
 int launch_pair_by_key(int key, const CUtensorMap* tm, const CcfGemmArgs& a, int grid, cudaStream_t stream);
 

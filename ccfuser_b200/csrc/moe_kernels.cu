@@ -16,7 +16,9 @@ namespace ccf {
 
 // ---------------------------------------------------------------------------------------------------
 // gate: top-k over E logits + softmax over the k selected values, one warp per token
-// (mix_moe/mix_moe/gates/naive_gate.py:31-38). Ties go to the lower expert id.
+// (mix_moe/mix_moe/gates/naive_gate.py:31-38). Ties go to the lower expert id. A NaN logit never wins a comparison, so
+// it is ranked as -inf (the ids written stay inside [0, E) whatever the row holds) and the row's k weights are NaN: a
+// diverged router shows up in the layer's output instead of as an index out of range.
 // ---------------------------------------------------------------------------------------------------
 template <int kMaxPerLane>
 __global__ void topk_softmax_kernel(const void* logits, int fp16, int is_f32, int T, int E, int K, int* idx_out,
@@ -25,6 +27,7 @@ __global__ void topk_softmax_kernel(const void* logits, int fp16, int is_f32, in
   const int lane = threadIdx.x & 31;
   if (warp >= T) return;
   float v[kMaxPerLane];
+  bool has_nan = false;
 #pragma unroll
   for (int i = 0; i < kMaxPerLane; ++i) {
     const int e = i * 32 + lane;
@@ -33,9 +36,13 @@ __global__ void topk_softmax_kernel(const void* logits, int fp16, int is_f32, in
       if (is_f32) x = reinterpret_cast<const float*>(logits)[static_cast<size_t>(warp) * E + e];
       else if (fp16) x = __half2float(reinterpret_cast<const __half*>(logits)[static_cast<size_t>(warp) * E + e]);
       else x = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[static_cast<size_t>(warp) * E + e]);
+      if (x != x) { has_nan = true; x = -INFINITY; }
     }
     v[i] = x;
   }
+  has_nan = __any_sync(0xffffffffu, has_nan);
+  // entries already taken: a bit per register so that a row of -inf (or NaN) still yields K distinct ids
+  unsigned taken = 0u;
   float sel_v[8];
   int sel_i[8];
   for (int j = 0; j < K; ++j) {
@@ -44,7 +51,7 @@ __global__ void topk_softmax_kernel(const void* logits, int fp16, int is_f32, in
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
       const int e = i * 32 + lane;
-      if (e < E && (v[i] > best || (v[i] == best && e < bi))) { best = v[i]; bi = e; }
+      if (e < E && !((taken >> i) & 1u) && (v[i] > best || (v[i] == best && e < bi))) { best = v[i]; bi = e; }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -54,10 +61,8 @@ __global__ void topk_softmax_kernel(const void* logits, int fp16, int is_f32, in
     }
     sel_v[j] = best;
     sel_i[j] = bi;
-    // remove the winner (unrolled select keeps v[] in registers)
-#pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i)
-      if ((bi & 31) == lane && (bi >> 5) == i) v[i] = -INFINITY;
+    // remove the winner
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
   }
   if (lane == 0) {
     const float mx = sel_v[0];
@@ -65,7 +70,7 @@ __global__ void topk_softmax_kernel(const void* logits, int fp16, int is_f32, in
     for (int j = 0; j < K; ++j) { sel_v[j] = __expf(sel_v[j] - mx); sum += sel_v[j]; }
     for (int j = 0; j < K; ++j) {
       idx_out[static_cast<size_t>(warp) * K + j] = sel_i[j];
-      w_out[static_cast<size_t>(warp) * K + j] = sel_v[j] / sum;
+      w_out[static_cast<size_t>(warp) * K + j] = has_nan ? __int_as_float(0x7fc00000) : sel_v[j] / sum;
     }
   }
 }
@@ -79,7 +84,9 @@ __global__ void topk_softmax_bwd_kernel(const int* idx, const float* w, const fl
   for (int j = 0; j < K; ++j) dot += w[static_cast<size_t>(t) * K + j] * dw[static_cast<size_t>(t) * K + j];
   for (int j = 0; j < K; ++j) {
     const float g = w[static_cast<size_t>(t) * K + j] * (dw[static_cast<size_t>(t) * K + j] - dot);
-    const size_t o = static_cast<size_t>(t) * E + idx[static_cast<size_t>(t) * K + j];
+    const int e = idx[static_cast<size_t>(t) * K + j];
+    if (e < 0 || e >= E) continue;   // an id outside the table (masked slot) has no logit to receive a gradient
+    const size_t o = static_cast<size_t>(t) * E + e;
     if (is_f32) reinterpret_cast<float*>(dlogits)[o] = g;
     else if (fp16) reinterpret_cast<__half*>(dlogits)[o] = __float2half(g);
     else reinterpret_cast<__nv_bfloat16*>(dlogits)[o] = __float2bfloat16(g);
@@ -273,7 +280,7 @@ __global__ void __launch_bounds__(256) plan_kernel_dev_epoch(const __grid_consta
 // ---------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) dispatch_kernel(const __grid_constant__ CcfDispatchArgs a, int* status,
                                                        int* done_ctas) {
-  dispatch_rows<8>(a, status);
+  if (a.backward) dispatch_rows<8, true>(a, status); else dispatch_rows<8, false>(a, status);
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -436,7 +443,7 @@ static int last_err() {
 }
 
 int ccf_topk_softmax(const void* logits, int fp16, int is_f32, int T, int E, int K, int* idx, float* w, void* stream) {
-  if (E > 256 || K > 8 || K < 1) return -2;
+  if (E > 256 || K > 8 || K < 1 || K > E) return -2;
   if (T == 0) return 0;
   const int threads = 256, blocks = (T * 32 + threads - 1) / threads;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

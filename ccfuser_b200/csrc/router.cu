@@ -25,15 +25,16 @@ constexpr int kRtABytes = BM * BK * 2;   // 128 rows x 128 bytes
 constexpr int kRtMaxK = 8;
 
 // Running top-kRtMaxK selection, best first. A candidate enters only if it is strictly greater than the current last
-// entry and bubbles up past strictly smaller ones, so among equal logits the lower expert id stays in front (candidates
-// are offered in ascending id order). Host-callable so that the rule can be tested without a GPU.
+// entry (or that entry is still empty, id -1) and bubbles up past strictly smaller or empty ones, so among equal logits
+// the lower expert id stays in front (candidates are offered in ascending id order) and a row of -inf logits still
+// yields the ids 0, 1, ... rather than none. Host-callable so that the rule can be tested without a GPU.
 __host__ __device__ __forceinline__ void topk_offer(float (&tv)[kRtMaxK], int (&ti)[kRtMaxK], float v, int e) {
-  if (v > tv[kRtMaxK - 1]) {
+  if (v > tv[kRtMaxK - 1] || ti[kRtMaxK - 1] < 0) {
     tv[kRtMaxK - 1] = v;
     ti[kRtMaxK - 1] = e;
 #pragma unroll
     for (int j = kRtMaxK - 1; j > 0; --j) {
-      if (tv[j] > tv[j - 1]) {
+      if (tv[j] > tv[j - 1] || ti[j - 1] < 0) {
         const float fv = tv[j]; tv[j] = tv[j - 1]; tv[j - 1] = fv;
         const int iv = ti[j]; ti[j] = ti[j - 1]; ti[j - 1] = iv;
       }
@@ -41,9 +42,9 @@ __host__ __device__ __forceinline__ void topk_offer(float (&tv)[kRtMaxK], int (&
   }
 }
 
-// softmax over the first k selected logits -> idx[k], w[k]
+// softmax over the first k selected logits -> idx[k], w[k]; `poison` (the row held a NaN logit) makes the weights NaN
 __host__ __device__ __forceinline__ void topk_finish(const float (&tv)[kRtMaxK], const int (&ti)[kRtMaxK], int k, int* idx,
-                                                     float* w) {
+                                                     float* w, bool poison = false) {
   float ex[kRtMaxK];
   float sum = 0.f;
 #pragma unroll
@@ -56,7 +57,7 @@ __host__ __device__ __forceinline__ void topk_finish(const float (&tv)[kRtMaxK],
   for (int j = 0; j < kRtMaxK; ++j) {
     if (j < k) {
       idx[j] = ti[j];
-      w[j] = ex[j] * inv;
+      w[j] = poison ? NAN : ex[j] * inv;
     }
   }
 }
@@ -175,6 +176,7 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       int ti[kRtMaxK];
 #pragma unroll
       for (int j = 0; j < kRtMaxK; ++j) { tv[j] = -INFINITY; ti[j] = -1; }
+      bool has_nan = false;   // a NaN logit is ranked as -inf and turns the row's weights into NaN
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       for (int c = 0; c < a.n_pad; c += 32) {
         uint32_t racc[32];
@@ -185,12 +187,14 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           const int e = c + i;
           float v = __uint_as_float(racc[i]) + ctrl->bias[e];
           if (a.logits != nullptr && row < a.tokens && e < a.e) a.logits[static_cast<size_t>(row) * a.e + e] = v;
-          if (e >= a.e) v = -INFINITY;
-          topk_offer(tv, ti, v, e);
+          if (e < a.e) {
+            if (v != v) { has_nan = true; v = -INFINITY; }
+            topk_offer(tv, ti, v, e);
+          }
         }
       }
       if (row < a.tokens)
-        topk_finish(tv, ti, a.k, a.idx + static_cast<size_t>(row) * a.k, a.w + static_cast<size_t>(row) * a.k);
+        topk_finish(tv, ti, a.k, a.idx + static_cast<size_t>(row) * a.k, a.w + static_cast<size_t>(row) * a.k, has_nan);
     } else {
       report_status(a.status, CCF_ERR_MBAR_TIMEOUT, 0x42);
     }
@@ -222,8 +226,13 @@ int ccf_router_select_host(const float* logits, int tokens, int e, int k, int* i
     float tv[kRtMaxK];
     int ti[kRtMaxK];
     for (int j = 0; j < kRtMaxK; ++j) { tv[j] = -INFINITY; ti[j] = -1; }
-    for (int i = 0; i < e; ++i) topk_offer(tv, ti, logits[static_cast<size_t>(t) * e + i], i);
-    topk_finish(tv, ti, k, idx + static_cast<size_t>(t) * k, w + static_cast<size_t>(t) * k);
+    bool has_nan = false;
+    for (int i = 0; i < e; ++i) {
+      float v = logits[static_cast<size_t>(t) * e + i];
+      if (v != v) { has_nan = true; v = -INFINITY; }
+      topk_offer(tv, ti, v, i);
+    }
+    topk_finish(tv, ti, k, idx + static_cast<size_t>(t) * k, w + static_cast<size_t>(t) * k, has_nan);
   }
   return 0;
 }
@@ -254,11 +263,13 @@ int ccf_router_topk(const void* x, const void* wg, const void* bias, int tokens,
   int rc;
   if ((rc = make_tmap(&tmx, x, tokens, d, 64, BM, fp16))) return rc;
   if ((rc = make_tmap(&tmw, wg, e, d, 64, a.n_pad, fp16))) return rc;
-  static int configured_bytes = 0;
-  if (smem_bytes > configured_bytes) {
+  static bool configured[64] = {};   // per device: the attribute belongs to the (function, device) pair
+  int cur = 0;
+  cudaGetDevice(&cur);
+  if (!configured[cur & 63]) {
     cudaError_t err = cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (err != cudaSuccess) return -static_cast<int>(err);
-    configured_bytes = 227 * 1024;
+    configured[cur & 63] = true;
   }
   const int grid = (tokens + BM - 1) / BM;
   router_topk_kernel<<<grid, kRtThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream_v)>>>(tmx, tmw, a);

@@ -53,16 +53,16 @@ def router_aux_loss(logits: torch.Tensor, idx: torch.Tensor, num_experts: int, b
 
     * load balance: ``balance_coef * E * sum_e (fraction of slots routed to e) * (mean router probability of e)``;
     * z-loss: ``z_coef * mean(logsumexp(logits)^2)``, which keeps the logits from drifting to large magnitudes.
-    Slots with a negative expert id are not counted. One definition for every backend."""
+    Slots whose expert id lies outside [0, num_experts) are not counted. One definition for every backend."""
     if not (balance_coef and balance_coef > 0) and not (z_coef and z_coef > 0):
         return None
     lg = logits.float()
     loss = lg.new_zeros(())
     if balance_coef and balance_coef > 0:
         flat = idx.reshape(-1).long()
-        valid = flat >= 0
+        valid = (flat >= 0) & (flat < num_experts)
         frac = torch.zeros(num_experts, device=lg.device, dtype=torch.float32)
-        frac.scatter_add_(0, flat.clamp_min(0), valid.float())
+        frac.scatter_add_(0, torch.where(valid, flat, torch.zeros_like(flat)), valid.float())
         frac = frac / valid.sum().clamp_min(1)
         loss = loss + balance_coef * num_experts * (frac * torch.softmax(lg, dim=-1).mean(0)).sum()
     if z_coef and z_coef > 0:

@@ -193,9 +193,12 @@ class MixMOE(MoELayer):
 
 class MixMOETransformerMLP(MixMOE):
     """``MixMOETransformerMLP(gate_type, experts, model_dim, expert_rank, world_size, ...)`` as in
-    mix_moe/mix_moe/transformer.py:435-448. ``experts`` is the reference's dict
-    (``count_per_node``, ``hidden_size_per_expert``, optional ``activation_fn``); unlike the reference
-    the activation named there is honoured (``'gelu' | 'relu' | 'swiglu'`` or an nn.Module)."""
+    mix_moe/mix_moe/transformer.py:435-448. ``experts`` is the reference's dict: ``num_local_expert`` (experts per
+    rank) and ``hidden_size`` (FFN width) as read at transformer.py:449-450 and passed by
+    examples/mix_moe_ddp.py:109, with the optional ``activation_fn``; Tutel's spelling of the same two entries
+    (``count_per_node``, ``hidden_size_per_expert``) is accepted as well. Both entries are required: a missing one
+    raises instead of silently building one expert of width 4 * model_dim. Unlike the reference the activation named
+    there is honoured (``'gelu' | 'relu' | 'swiglu'`` or an nn.Module)."""
 
     def __init__(self, gate_type=None, experts=None, model_dim=1024, expert_rank=0, world_size=1,
                  scan_expert_func=None, total_batch_size=4096, expert_dp_comm="none",
@@ -205,8 +208,15 @@ class MixMOETransformerMLP(MixMOE):
         gate_type = gate_type or {}
         k = top_k if top_k is not None else gate_type.get("k", 2)
         act = activation if activation is not None else experts.get("activation_fn", "gelu")
-        super().__init__(num_expert=experts.get("count_per_node", 1), d_model=model_dim,
-                         world_size=world_size, top_k=k, d_hidden=experts.get("hidden_size_per_expert", 4 * model_dim),
+
+        def entry(*names):
+            for n in names:
+                if n in experts:
+                    return int(experts[n])
+            raise KeyError(f"experts dict needs {names[0]!r} (or {names[1]!r}); got keys {sorted(experts)}")
+
+        super().__init__(num_expert=entry("num_local_expert", "count_per_node"), d_model=model_dim,
+                         world_size=world_size, top_k=k, d_hidden=entry("hidden_size", "hidden_size_per_expert"),
                          activation=act, moe_group=moe_group,
                          capacity_factor=capacity_factor if capacity_factor is not None else gate_type.get("capacity_factor"),
                          dtype=dtype, backend=backend, max_tokens=total_batch_size, device=device)

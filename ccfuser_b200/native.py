@@ -248,10 +248,12 @@ class record_launches:
 
 
 # Argument checks of the host launchers return small negative numbers before any CUDA call is made; failures of CUDA
-# calls come back as minus the cudaError_t value. The two ranges overlap for -2 ... -8, so a message names both readings.
+# calls come back as minus the cudaError_t value. The two ranges overlap for -2 ... -9, so a message names both readings.
 ARG_ERRORS = {-2: "argument out of range", -3: "n must be a multiple of 32", -4: "k-grouped GEMM needs m_per_group % 128 == 0",
               -5: "k must be a multiple of 8", -6: "no kernel for this combination of operand majors and epilogue",
-              -7: "cudaSetDevice failed", -8: "the CTA-pair kernel needs m_per_group % 256 == 0 in k-grouped mode"}
+              -7: "cudaSetDevice failed", -8: "the CTA-pair kernel needs m_per_group % 256 == 0 in k-grouped mode",
+              -9: "the dispatch role exists only in the kernels that read the receive buffer (forward: bias+activation / "
+                  "SwiGLU epilogues with backward=0, backward: activation-derivative epilogues with backward=1)"}
 
 
 def check(rc: int, what: str):

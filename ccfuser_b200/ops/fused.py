@@ -91,6 +91,7 @@ class CommContext:
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=device)
         self.device_epoch = bool(env_flag("DEVICE_EPOCH", 0))
         self.ws = G.Workspace.get(device)
+        self.users = 0          # fused layers currently attached (FusedMoE.__init__ / close)
         # scratch of the routing kernels
         s_max = max_slots
         nb = (s_max + 1023) // 1024
@@ -103,10 +104,16 @@ class CommContext:
 
     @classmethod
     def get(cls, group, world, rank, device, max_rows, max_slots, d_model, e_total, dtype) -> "CommContext":
-        key = (id(group) if group is not None else 0, world, str(device), d_model, e_total, dtype)
+        # keyed on the group's member ranks, not on the group object: object ids are reused after garbage collection
+        import torch.distributed as dist
+        members = tuple(dist.get_process_group_ranks(group)) if (group is not None and world > 1) else ()
+        key = (members, world, str(device), d_model, e_total, dtype)
         ctx = cls._instances.get(key)
         if ctx is None or ctx.max_rows < max_rows or ctx.max_slots < max_slots:
-            # (re)allocation is collective: every rank constructs its layers in the same order
+            # (re)allocation is collective: every rank constructs its layers in the same order. A superseded context
+            # that no layer uses any more is freed here; one that still has users is freed when its last layer closes.
+            if ctx is not None and ctx.users == 0:
+                ctx.close()
             ctx = cls(group, world, rank, device, max_rows, max_slots, d_model, e_total, dtype)
             cls._instances[key] = ctx
         return ctx
@@ -117,9 +124,12 @@ class CommContext:
     def close(self):
         """Free this context's symmetric buffers (collective over its group; call after the layers that use it have
         been released and their work has completed)."""
+        if self.buf is None:
+            return
         for name in ("grecv", "gcomb", "row_src", "row_gate", "tile_flags", "cnt_table", "cnt_flag", "done"):
             setattr(self, name, None)
         self.buf.close()
+        self.buf = None
         for k, v in list(self._instances.items()):
             if v is self:
                 del self._instances[k]
@@ -221,6 +231,7 @@ class FusedMoE:
         group = layer.ep_group if self.world > 1 else None
         self.ctx = CommContext.get(group, self.world, self.rank, self.device, self.max_rows, self.max_slots,
                                    cfg.d_model, cfg.num_experts, cfg.dtype)
+        self.ctx.users += 1
         # rows of the context may exceed this layer's bound (shared with bigger layers)
         self.max_rows = self.ctx.max_rows
         self.max_slots = self.ctx.max_slots
@@ -352,9 +363,16 @@ class FusedMoE:
         return L
 
     def close(self):
-        """Free this layer's symmetric buffers (collective: call on every rank)."""
+        """Free this layer's symmetric buffers (collective: call on every rank, in the same order of layers). The
+        group's shared context goes with its last layer."""
+        if self.buf is None:
+            return
         self.xrecv = self.comb = None
         self.buf.close()
+        self.buf = None
+        self.ctx.users -= 1
+        if self.ctx.users <= 0:
+            self.ctx.close()
 
     def routing_stats(self):
         """Device tensors describing the last forward call (no host synchronisation): slots per expert before and

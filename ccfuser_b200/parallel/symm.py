@@ -140,6 +140,11 @@ class SymmBuffer:
         return self.local[offset:offset + nbytes].view(dtype).view(*shape)
 
     def close(self):
+        """Unmap the peers' allocations and free this rank's own. Collective over the buffer's group: a rank may only
+        free memory that no peer still has mapped or still writes to (freeing an exported allocation under an importer is
+        undefined), so every rank first drains its own device work, then all meet, unmap, meet again, and only then
+        free. The group's host collectives are bounded by the process group's timeout, so a missing rank ends this with
+        an error instead of a hang."""
         if self.base is None:
             return
         if self._host:
@@ -147,9 +152,16 @@ class SymmBuffer:
             self.base = None
             return
         lib = N.load()
+        multi = self.world > 1 and dist.is_initialized()
+        if multi:
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize()          # my kernels that store into peers' memory have finished
+            dist.barrier(group=self.group)        # ... and so have everyone else's stores into mine
         for q in self._opened:
             lib.ccf_symm_close_handle(q)
         self._opened = []
+        if multi:
+            dist.barrier(group=self.group)        # nobody maps my allocation any more
         self.local = None
         lib.ccf_symm_free(self.base)
         self.base = None

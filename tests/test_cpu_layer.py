@@ -105,6 +105,23 @@ def test_single_process_and_compat_constructor():
     assert torch.allclose(y.reshape(-1, 32), ref, atol=1e-5)
 
 
+def test_compat_constructor_takes_the_reference_experts_dict():
+    # the dict exactly as the reference's scripts build it (mix_moe/mix_moe/examples/mix_moe_ddp.py:109,
+    # read at mix_moe/mix_moe/transformer.py:449-450), activation module included
+    import torch.nn as nn
+    layer = MixMOETransformerMLP(gate_type={"type": "top", "k": 2, "capacity_factor": 0.0, "fp32_gate": True},
+                                 experts={"type": "ffn", "num_local_expert": 3, "hidden_size": 48,
+                                          "activation_fn": nn.ReLU()},
+                                 model_dim=32, expert_rank=0, world_size=1, total_batch_size=64, backend="cpu",
+                                 capacity_factor=None)
+    assert layer.config.experts_per_rank == 3 and layer.config.d_ffn == 48 and layer.config.activation == "relu"
+    assert layer.experts.htoh4.weight.shape == (3, 48, 32)
+    y = layer(torch.randn(16, 32))
+    assert y.shape == (16, 32)
+    with pytest.raises(KeyError):
+        MixMOETransformerMLP(gate_type={"k": 2}, experts={"type": "ffn"}, model_dim=32, backend="cpu")
+
+
 def _empty_rank_fn(rank, world):
     cfg = MoEConfig(d_model=32, d_ffn=64, num_experts=4, top_k=2, capacity_factor=None, activation="gelu",
                     dtype=torch.float32, ep_size=world, backend="cpu", max_tokens=64)

@@ -55,12 +55,11 @@ def _use_grouped_mm(rows: torch.Tensor, experts) -> bool:
             and rows.shape[1] % 8 == 0 and experts.htoh4.weight.shape[1] % 8 == 0)
 
 
-def _experts_grouped_mm(rows: torch.Tensor, per_expert: List[int], experts) -> torch.Tensor:
-    """All local experts with the library grouped GEMM (one call per projection instead of a loop over experts)."""
+def _experts_grouped_mm(rows: torch.Tensor, offs: torch.Tensor, eid: torch.Tensor, experts) -> torch.Tensor:
+    """All local experts with the library grouped GEMM (one call per projection instead of a loop over experts).
+    ``offs`` [E_loc] int32: end row of each expert inside ``rows``; ``eid`` [R]: local expert of each row (for the
+    biases). Both are device tensors: nothing here touches the host."""
     import torch.nn.functional as F
-    offs = torch.tensor(per_expert, device=rows.device, dtype=torch.int32).cumsum(0).to(torch.int32)
-    eid = torch.repeat_interleave(torch.arange(len(per_expert), device=rows.device),
-                                  torch.tensor(per_expert, device=rows.device))
 
     def proj(x, lin):
         y = torch._grouped_mm(x, lin.weight.transpose(1, 2), offs=offs)
@@ -80,46 +79,55 @@ def moe_forward_a2a(x: torch.Tensor, topk_idx: torch.Tensor, topk_score: torch.T
                     *, num_experts: int, capacity: int, group, grouped_mm: bool = False,
                     stats: Optional[dict] = None) -> torch.Tensor:
     """x [T,d]; topk_idx/topk_score [T,k] (a negative expert id = slot not routed). Differentiable w.r.t. x,
-    topk_score and the expert params. ``stats`` (optional dict) receives the ``[rank, expert]`` count table."""
+    topk_score and the expert params. ``stats`` (optional dict) receives the ``[rank, expert]`` count table.
+
+    Host involvement per call: ONE device-to-host read (the 2 W row counts that ``all_to_all_single`` needs as Python
+    integers; a dropless exchange of variable size cannot do with less). Sorting, regrouping to expert-major order and
+    its inverse are index gathers computed on the device; on bf16 CUDA tensors the experts run as library grouped GEMMs
+    with device-side offsets."""
     world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
     e_loc = num_experts // world
     t, d = x.shape
     k = topk_idx.shape[1]
+    dev = x.device
     plan = route_local(topk_idx, num_experts, capacity)
-    kept = plan.keep.nonzero(as_tuple=True)[0]                     # slot ids, ascending
-    # order kept slots by (expert, position) == stable sort by expert
-    order = kept[torch.sort(plan.expert[kept], stable=True).indices]
-    send_rows = x[order // k]                                       # [S_kept, d]
     table = exchange_counts(plan.count, world, group)               # [W, E]
     if stats is not None:
         stats["count_table"] = table
-    # rows I send to owner o / rows I receive from source r (per local expert)
-    send_per_rank = plan.count.view(world, e_loc).sum(1).tolist()
     me = dist.get_rank(group) if world > 1 else 0
-    recv_cnt = table[:, me * e_loc:(me + 1) * e_loc]                # [W, e_loc]
-    recv_per_rank = recv_cnt.sum(1).tolist()
-    recv = all_to_all(send_rows, recv_per_rank, send_per_rank, group)   # grouped by (src, expert)
-    # regroup to expert-major: rows of (src r, expert e) are contiguous in `recv`
-    rc = recv_cnt.reshape(-1).tolist()
-    pieces = list(torch.split(recv, rc, 0))
-    seg_ids = [r * e_loc + e for e in range(e_loc) for r in range(world)]          # expert-major order of segments
-    rows = torch.cat([pieces[i] for i in seg_ids], 0) if pieces else recv
-    per_expert = [sum(rc[r * e_loc + e] for r in range(world)) for e in range(e_loc)]
+    recv_cnt = table[:, me * e_loc:(me + 1) * e_loc]                # [W, e_loc] rows of (source r, local expert e)
+    # the one host read: rows I send to each owner, rows I receive from each source
+    sizes = torch.cat([plan.count.view(world, e_loc).sum(1), recv_cnt.sum(1)]).tolist()
+    send_per_rank, recv_per_rank = [int(v) for v in sizes[:world]], [int(v) for v in sizes[world:]]
+    n_send, n_recv = sum(send_per_rank), sum(recv_per_rank)
+    # kept slots ordered by (expert, position): a stable sort by expert with the dropped slots keyed past the end
+    key = torch.where(plan.keep, plan.expert, torch.full_like(plan.expert, num_experts))
+    order = torch.sort(key, stable=True).indices[:n_send]
+    send_rows = x[order // k]                                       # [S_kept, d]
+    recv = all_to_all(send_rows, recv_per_rank, send_per_rank, group)   # segments ordered (source, expert)
+    # regroup to expert-major: row i of `recv` belongs to segment seg[i] = source * e_loc + expert
+    seg_len = recv_cnt.reshape(-1)
+    seg = torch.repeat_interleave(torch.arange(world * e_loc, device=dev), seg_len, output_size=n_recv)
+    row_expert = seg % e_loc
+    perm = torch.sort(row_expert * world + seg // e_loc, stable=True).indices     # expert-major, sources in rank order
+    rows = recv[perm]
+    per_expert = recv_cnt.sum(0)                                    # [e_loc] device
     if _use_grouped_mm(rows, experts):
-        out = _experts_grouped_mm(rows, per_expert, experts)
+        offs = per_expert.cumsum(0).to(torch.int32)
+        out = _experts_grouped_mm(rows, offs, row_expert[perm], experts)
     else:
+        counts = [int(v) for v in per_expert.tolist()]              # CPU / fp32 plumbing path: a per-expert loop
         outs_e = []
-        for e, rows_e in enumerate(torch.split(rows, per_expert, 0)):
+        for e, rows_e in enumerate(torch.split(rows, counts, 0)):
             outs_e.append(experts.expert_forward(e, rows_e) if rows_e.shape[0]
                           else rows_e.new_zeros(0, experts.h4toh.weight.shape[1]))
-        out = torch.cat(outs_e, 0)
-    # back to the (src, expert) order of the exchange
-    outs: List[Optional[torch.Tensor]] = [None] * len(pieces)
-    for i, piece in zip(seg_ids, torch.split(out, [rc[i] for i in seg_ids], 0)):
-        outs[i] = piece
-    back = torch.cat(outs, 0) if outs else recv.new_zeros(0, d)
+        out = torch.cat(outs_e, 0) if outs_e else rows.new_zeros(0, experts.h4toh.weight.shape[1])
+    # back to the (source, expert) order of the exchange: the inverse gather
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(n_recv, device=dev)
+    back = out[inv]
     ret = all_to_all(back, send_per_rank, recv_per_rank, group)     # same order as send_rows
     w = topk_score.reshape(-1)[order].to(ret.dtype).unsqueeze(1)
-    y = torch.zeros(t, ret.shape[1], dtype=ret.dtype, device=x.device)
+    y = torch.zeros(t, ret.shape[1], dtype=ret.dtype, device=dev)
     y = y.index_add(0, order // k, ret * w)
     return y

@@ -192,3 +192,25 @@ def test_shared_ffn_is_added_for_every_token_and_is_replicated():
     assert names and all(n.startswith("experts.") for n in names)
     layer(x).sum().backward()
     assert layer.shared.h4toh.weight.grad is not None
+
+
+def test_sampled_oracle_check_agrees_and_detects_errors():
+    """The sampled fp32 check used at benchmark sizes: zero error for the library path on CPU, and a visible error when
+    an output, an input gradient or a weight gradient is off."""
+    from ccfuser_b200.ops.reference import sampled_oracle_check
+    from ccfuser_b200.parallel.a2a import moe_forward_a2a
+    torch.manual_seed(0)
+    cfg = MoEConfig(d_model=32, d_ffn=64, num_experts=4, top_k=2, capacity_factor=1.0, activation="swiglu",
+                    dtype=torch.float32, backend="cpu", max_tokens=256)
+    layer = MoELayer(cfg)
+    x = torch.randn(200, 32, requires_grad=True)
+    idx, score = layer.gate(x)
+    score = score.detach().requires_grad_(True)
+    y = moe_forward_a2a(x, idx, score, layer.experts, num_experts=4, capacity=cfg.capacity(200), group=None)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    res = sampled_oracle_check(layer, x, idx, score, y, gy, x.grad, score.grad, n_sample=50, expert=1)
+    assert set(res) >= {"y", "dx", "dscore", "dw1", "dw2", "dwg"} and max(res.values()) < 1e-5
+    layer.experts.h4toh.weight.grad[1] *= 1.05
+    bad = sampled_oracle_check(layer, x, idx, score, y * 1.02, gy, x.grad * 0.9, score.grad, n_sample=50, expert=1)
+    assert bad["y"] > 1e-2 and bad["dx"] > 5e-2 and bad["dw2"] > 2e-2 and bad["dw1"] < 1e-5

@@ -36,7 +36,9 @@ def measured_sustained_tflops(default: float = 1400.0) -> float:
         return default
 
 
-def time_fn(fn, iters=10, warmup=3, flush_mb=256):
+def time_fn(fn, iters=10, warmup=3, flush_mb=256, back_to_back=0):
+    """Median and best time of one launch (L2 flushed before each). With ``back_to_back`` = n > 0 also the time per
+    launch of n launches issued without a gap (what the kernel sustains inside a long step under the power cap)."""
     flush = torch.empty(flush_mb * 1024 * 1024, dtype=torch.uint8, device="cuda")
     for _ in range(warmup):
         fn()
@@ -51,7 +53,16 @@ def time_fn(fn, iters=10, warmup=3, flush_mb=256):
         torch.cuda.synchronize()
         times.append(s.elapsed_time(e))
     times.sort()
-    return times[len(times) // 2], times[0]
+    b2b = None
+    if back_to_back > 0:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(back_to_back):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        b2b = s.elapsed_time(e) / back_to_back
+    return times[len(times) // 2], times[0], b2b
 
 
 def main():
@@ -65,7 +76,12 @@ def main():
     ap.add_argument("--trace", action="store_true",
                     help="add per-tile clock statistics (main-loop time against its ideal, accumulator wait, epilogue time)")
     ap.add_argument("--out", default="", help="optional JSON file for the records")
+    ap.add_argument("--back-to-back", type=int, default=0,
+                    help="also time this many launches of each case without gaps and report the SM clock seen meanwhile")
     args = ap.parse_args()
+    from ..utils.clocks import ClockSampler, visible_index
+    sampler = ClockSampler(visible_index(torch.cuda.current_device()), period=0.02)
+    sampler.start()
     peak, _, src = measured_peaks()
     dev = "cuda"
     e, d, f = args.experts, args.d, args.f
@@ -77,11 +93,20 @@ def main():
 
     def report(name, flops, fn, kblocks=0):
         """fn() launches the case; if it accepts ``trace=`` and --trace is given, one more launch records per-tile clocks."""
-        med, best = time_fn(fn, args.iters)
+        m0 = sampler.mark()
+        med, best, b2b = time_fn(fn, args.iters, back_to_back=args.back_to_back)
         G.Workspace.get(dev).check(name)
+        clk = sampler.summary_between(m0, sampler.mark())
         rec = {"case": name, "ms_median": round(med, 4), "ms_best": round(best, 4),
                "tflops_median": round(flops / med / 1e9, 1), "frac_of_" + src + "_cublas_peak": round(flops / med / 1e9 / peak, 3),
                "frac_of_" + src + "_cublas_sustained": round(flops / med / 1e9 / measured_sustained_tflops(), 3)}
+        rec["clocks"] = clk
+        if b2b is not None:
+            rec["ms_back_to_back"] = round(b2b, 4)
+            rec["tflops_back_to_back"] = round(flops / b2b / 1e9, 1)
+            if clk.get("sm_mhz"):
+                # tensor-pipe use implied by the clock that was seen: 148 SMs x 8192 dense bf16 FLOP per clock
+                rec["frac_of_pipe_at_seen_clock"] = round(flops / b2b / 1e9 / (148 * 8192 * clk["sm_mhz"] * 1e-6), 3)
         if args.trace and kblocks > 0:
             from .overlap_trace import analyze
             tr = torch.zeros(148, 128, 8, dtype=torch.int64, device=dev)
@@ -130,6 +155,7 @@ def main():
         report("wgrad2", 2 * r * d * f, gemm(
             a0=y, b0=h, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True, m_per_group=d,
             group_base=gb, group_rows=gr, num_groups=e, out0=dw, ld_out=f), kblocks=(rows_per + 63) // 64)
+    sampler.stop()
     if args.out:
         os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
         with open(args.out, "w") as fh:

@@ -214,6 +214,124 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Backward of the router without a GEMM. The gradient of the logits is non-zero only in the k selected columns,
+//   g[t, j] = w[t, j] * (dw[t, j] - sum_i w[t, i] dw[t, i])          (softmax over the selected logits),
+// so   dx[t, :]  = sum_j g[t, j] * Wg[idx[t, j], :]                  (k rows of the small router matrix per token)
+// and  dWg[e, :] = sum over the slots routed to e of g * x[t, :],   db[e] = sum of those g.
+// Both are bound by reading or writing one [T, d] matrix once; the dense [T, E] gradient is never formed. A slot whose
+// id lies outside [0, E) (masked token) contributes nothing.
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float slot_grad(const float* w, const float* dw, size_t base, int K, int j) {
+  float dot = 0.f;
+  for (int i = 0; i < K; ++i) dot += w[base + i] * dw[base + i];
+  return w[base + j] * (dw[base + j] - dot);
+}
+
+// one warp per token; every lane owns 16-byte pieces of the row
+__global__ void __launch_bounds__(256) router_bwd_dx_kernel(const int* __restrict__ idx, const float* __restrict__ w,
+                                                            const float* __restrict__ dw, const void* __restrict__ wg,
+                                                            void* __restrict__ dx, int T, int d, int E, int K, int fp16) {
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const size_t base = static_cast<size_t>(t) * K;
+  int e_j[kRtMaxK];
+  float g_j[kRtMaxK];
+#pragma unroll
+  for (int j = 0; j < kRtMaxK; ++j) {
+    e_j[j] = -1;
+    g_j[j] = 0.f;
+    if (j < K) {
+      const int e = idx[base + j];
+      if (e >= 0 && e < E) { e_j[j] = e; g_j[j] = slot_grad(w, dw, base, K, j); }
+    }
+  }
+  const int vecs = d >> 3;
+  const uint4* wv = reinterpret_cast<const uint4*>(wg);
+  uint4* out = reinterpret_cast<uint4*>(dx) + static_cast<size_t>(t) * vecs;
+  for (int v = lane; v < vecs; v += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < kRtMaxK; ++j) {
+      if (e_j[j] < 0) continue;
+      const uint4 r = __ldg(wv + static_cast<size_t>(e_j[j]) * vecs + v);
+      const uint32_t q[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2(q[i], fp16);
+        acc[2 * i] = fmaf(g_j[j], f.x, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(g_j[j], f.y, acc[2 * i + 1]);
+      }
+    }
+    out[v] = make_uint4(pack2(acc[0], acc[1], fp16), pack2(acc[2], acc[3], fp16), pack2(acc[4], acc[5], fp16),
+                        pack2(acc[6], acc[7], fp16));
+  }
+}
+
+// Block (cx, ty, ez): columns [256 cx, 256 cx + 256), tokens ty, ty + gridDim.y, ... (one warp each), experts
+// [64 ez, 64 ez + 64). Partial sums are kept in shared memory (64 x 256 fp32) and added to the fp32 result at the end,
+// so the global atomics number E x d per block, not one per slot.
+constexpr int kRtBwdCols = 256, kRtBwdExperts = 64;
+__global__ void __launch_bounds__(256) router_bwd_dw_kernel(const int* __restrict__ idx, const float* __restrict__ w,
+                                                            const float* __restrict__ dw, const void* __restrict__ x,
+                                                            float* __restrict__ dwg, float* __restrict__ db, int T, int d,
+                                                            int E, int K, int fp16) {
+  extern __shared__ float racc[];   // [kRtBwdExperts][kRtBwdCols] + [kRtBwdExperts]
+  float* bacc = racc + kRtBwdExperts * kRtBwdCols;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col0 = blockIdx.x * kRtBwdCols + lane * 8;
+  const int e0 = blockIdx.z * kRtBwdExperts;
+  for (int i = threadIdx.x; i < kRtBwdExperts * kRtBwdCols + kRtBwdExperts; i += blockDim.x) racc[i] = 0.f;
+  __syncthreads();
+  const int warps_total = gridDim.y * (blockDim.x >> 5);
+  for (int t = blockIdx.y * (blockDim.x >> 5) + warp; t < T; t += warps_total) {
+    const size_t base = static_cast<size_t>(t) * K;
+    bool any = false;
+    for (int j = 0; j < K; ++j) {
+      const int e = idx[base + j] - e0;
+      any |= (e >= 0 && e < kRtBwdExperts && e + e0 < E);
+    }
+    if (!any) continue;
+    float xf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (col0 < d) {
+      const uint4 r = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) +
+                                                           static_cast<size_t>(t) * d + col0));
+      const uint32_t q[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2(q[i], fp16);
+        xf[2 * i] = f.x;
+        xf[2 * i + 1] = f.y;
+      }
+    }
+    for (int j = 0; j < K; ++j) {
+      const int e = idx[base + j] - e0;
+      if (e < 0 || e >= kRtBwdExperts || e + e0 >= E) continue;
+      const float g = slot_grad(w, dw, base, K, j);
+      if (col0 < d) {
+        // element i of this lane's 8 columns lives at [e][32 i + lane]: the 32 lanes of an atomic hit 32 banks
+        float* row = racc + e * kRtBwdCols + lane;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) atomicAdd(row + 32 * i, g * xf[i]);
+      }
+      if (blockIdx.x == 0 && lane == 0 && db != nullptr) atomicAdd(bacc + e, g);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kRtBwdExperts * kRtBwdCols; i += blockDim.x) {
+    const int e = i / kRtBwdCols + e0, within = i % kRtBwdCols;
+    const int c = blockIdx.x * kRtBwdCols + (within & 31) * 8 + (within >> 5);
+    const float v = racc[i];
+    if (e < E && c < d && v != 0.f) atomicAdd(dwg + static_cast<size_t>(e) * d + c, v);
+  }
+  if (blockIdx.x == 0 && db != nullptr && threadIdx.x < kRtBwdExperts && e0 + threadIdx.x < E) {
+    const float v = bacc[threadIdx.x];
+    if (v != 0.f) atomicAdd(db + e0 + threadIdx.x, v);
+  }
+}
+
 }  // namespace ccf
 
 extern "C" {
@@ -273,6 +391,40 @@ int ccf_router_topk(const void* x, const void* wg, const void* bias, int tokens,
   }
   const int grid = (tokens + BM - 1) / BM;
   router_topk_kernel<<<grid, kRtThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream_v)>>>(tmx, tmw, a);
+  cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? 0 : -static_cast<int>(err);
+}
+
+// Backward of the router for the k selected columns (see the kernels above). idx [tokens, k], w and dw [tokens, k] fp32
+// (dw = gradient arriving for the weights); wg [e, d] and x [tokens, d] in the operand type. dx [tokens, d] (operand
+// type) is written when not null; dwg [e, d] and db [e] (fp32, zero on entry; db may be null) are accumulated into
+// when dwg is not null. Limits as in ccf_router_topk.
+int ccf_router_bwd(const int* idx, const float* w, const float* dw, const void* wg, const void* x, void* dx, float* dwg,
+                   float* db, int tokens, int d, int e, int k, int fp16, void* stream_v) {
+  using namespace ccf;
+  if (tokens < 1 || e < 1 || e > 256 || k < 1 || k > kRtMaxK || d < 8 || d % 8 != 0) return -2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
+  if (dx != nullptr) {
+    const int threads = 256, blocks = (tokens * 32 + threads - 1) / threads;
+    router_bwd_dx_kernel<<<blocks, threads, 0, st>>>(idx, w, dw, wg, dx, tokens, d, e, k, fp16);
+  }
+  if (dwg != nullptr) {
+    const int smem = (kRtBwdExperts * kRtBwdCols + kRtBwdExperts) * static_cast<int>(sizeof(float));
+    static bool configured[64] = {};
+    int cur = 0;
+    cudaGetDevice(&cur);
+    if (!configured[cur & 63]) {
+      cudaError_t err = cudaFuncSetAttribute(router_bwd_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (err != cudaSuccess) return -static_cast<int>(err);
+      configured[cur & 63] = true;
+    }
+    const int cx = (d + kRtBwdCols - 1) / kRtBwdCols, ez = (e + kRtBwdExperts - 1) / kRtBwdExperts;
+    int ty = (tokens + 63) / 64;                 // at least 64 tokens (8 per warp) per block
+    const int cap = (4 * 148 + cx * ez - 1) / (cx * ez);
+    if (ty > cap) ty = cap;
+    if (ty < 1) ty = 1;
+    router_bwd_dw_kernel<<<dim3(cx, ty, ez), 256, smem, st>>>(idx, w, dw, x, dwg, db, tokens, d, e, k, fp16);
+  }
   cudaError_t err = cudaGetLastError();
   return err == cudaSuccess ? 0 : -static_cast<int>(err);
 }

@@ -39,7 +39,6 @@ class GPTMoEConfig:
     backend: str = "auto"
     max_tokens: int = 8192        # tokens per rank per step (batch * seq_len)
     dtype: torch.dtype = torch.bfloat16
-    aux_loss_coef: float = 0.0
     recv_factor: float = 2.0      # receive-buffer size of a rank relative to the balanced load (no capacity factor)
 
     router_dtype: Optional[torch.dtype] = None

@@ -155,8 +155,8 @@ def load(build_if_missing: bool = True):
                     raise
         if not os.path.exists(path):
             raise RuntimeError(f"{path} is missing: run `python -m ccfuser_b200.build` (needs nvcc, sm_100a)")
-        lib = C.CDLL(path)
-        _declare(lib)
+        cdll = C.CDLL(path)
+        lib = _DeclaredOnly(cdll, _declare(cdll))
         for name, struct in (("gemm_args", GemmArgs), ("dispatch_args", DispatchArgs),
                              ("gemm_launch", GemmLaunch), ("plan_args", PlanArgs), ("layer", Layer),
                              ("layer_grads", LayerGrads), ("barrier_args", BarrierArgs)):
@@ -175,6 +175,7 @@ def _declare(lib):
         "ccf_debug_pair_tile_order": ([p, p, p, p, i, i, i, i, i, p, i], i),
         "ccf_router_topk": ([p, p, p, i, i, i, i, i, p, p, p, p, ull, i, p], i),
         "ccf_router_select_host": ([p, i, i, i, p, p], i),
+        "ccf_router_bwd": ([p, p, p, p, p, p, p, p, i, i, i, i, i, p], i),
         "ccf_topk_softmax": ([p, i, i, i, i, i, p, p, p], i),
         "ccf_topk_softmax_bwd": ([p, p, p, i, i, i, p, i, i, p], i),
         "ccf_route": ([p, i, i, i, p, p, p, p, p, p, p], i),
@@ -202,6 +203,21 @@ def _declare(lib):
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = restype
+    return set(sig)
+
+
+class _DeclaredOnly:
+    """The loaded library, restricted to the entry points whose signatures are declared above. ctypes would call any
+    other exported symbol with its default conversion (Python integers become 32-bit C ints), which silently truncates
+    device addresses; an undeclared name is therefore an error here, not a call."""
+
+    def __init__(self, cdll, declared):
+        self._cdll, self._declared = cdll, declared
+
+    def __getattr__(self, name):
+        if name.startswith("ccf_sizeof_") or name in self._declared:
+            return getattr(self._cdll, name)
+        raise AttributeError(f"{name}: no signature declared in ccfuser_b200/native.py (_declare)")
 
 
 class LaunchRecorder:

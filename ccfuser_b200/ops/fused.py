@@ -263,10 +263,10 @@ class FusedMoE:
         self.sent_rows = torch.zeros(N.MAX_RANKS, **i32)
         self.table_copy = torch.zeros(self.world, cfg.num_experts, **i32)
         self.check_every_call = bool(env_flag("CHECK_STATUS", 0))
-        self.fused_router = bool(env_flag("FUSED_ROUTER", 0))
+        self.fused_router = bool(env_flag("FUSED_ROUTER", 1))   # one-kernel router (ops/router.py) wherever it applies
         self._save_pre = True   # whether the next forward stores the pre-activations (set per call by run_experts)
-        # CCFUSER_NATIVE_RUNTIME=1: one C call per forward / backward (csrc/runtime.cu) instead of one per launch
-        self.native_runtime = bool(env_flag("NATIVE_RUNTIME", 0))
+        # one C call per forward / backward (csrc/runtime.cu); CCFUSER_NATIVE_RUNTIME=0: one Python call per launch
+        self.native_runtime = bool(env_flag("NATIVE_RUNTIME", 1))
         self._desc = None
         self._desc_key = None
 
@@ -285,12 +285,19 @@ class FusedMoE:
         coef = getattr(layer.gate, "aux_loss_coef", 0.0)
         zcoef = getattr(layer.gate, "z_loss_coef", 0.0)
         lin = getattr(layer.gate, "gate", None)
-        if (self.fused_router and not (coef and coef > 0) and not (zcoef and zcoef > 0) and isinstance(lin, torch.nn.Linear)
-                and R.supported(x, lin.weight, cfg.top_k)):
-            # linear layer + top-k + softmax in one kernel; the logits are never written
+        if self.fused_router and isinstance(lin, torch.nn.Linear) and R.supported(x, lin.weight, cfg.top_k):
+            # linear layer + top-k + softmax in one kernel. The logits are written (fp32) only when an auxiliary loss
+            # needs them; their gradient then returns through the same autograd node.
+            want = bool((coef and coef > 0) or (zcoef and zcoef > 0))
+            if want:
+                idx, w, logits = R.fused_router(x, lin.weight, lin.bias, cfg.top_k, want_logits=True)
+                loss = router_aux_loss(logits, idx, cfg.num_experts, coef, zcoef)
+            else:
+                idx, w = R.fused_router(x, lin.weight, lin.bias, cfg.top_k)
+                loss = None
             if hasattr(layer.gate, "set_loss"):
-                layer.gate.set_loss(None)
-            return R.fused_router(x, lin.weight, lin.bias, cfg.top_k)
+                layer.gate.set_loss(loss)
+            return idx, w
         logits = layer.gate.logits(x) if hasattr(layer.gate, "logits") else None
         if logits is None:
             raise TypeError("the fused backend needs a gate with a .logits(x) method (NaiveGate)")
@@ -566,7 +573,7 @@ class _FusedMoEFn(torch.autograd.Function):
                                                    y.data_ptr(), t, cfg.capacity(t), int(fm._save_pre),
                                                    -1 if cc.device_epoch else cc.epoch, N.stream_ptr(), None, 0, None),
                         "ccf_layer_forward")
-            N.count(8)   # route (2), plan, GEMM-1, GEMM-2, wait, reduce + the counter reset
+            N.count(7)   # kernels: route (2), plan, dispatch + GEMM-1, GEMM-2 + combine, wait, reduce
             ctx.fm = fm
             ctx.tokens = t
             ctx.save_for_backward(idx, gate_w, w1, wg, w2)
@@ -613,7 +620,8 @@ class _FusedMoEFn(torch.autograd.Function):
             g.dw1, g.db1, g.dwg, g.dbg, g.dw2, g.db2, g.dx = (N.ptr(v) for v in (dw1, db1, dwg, dbg, dw2, db2, dx))
             N.check(lib.ccf_layer_backward(C.byref(fm.native_desc()), dy.data_ptr(), idx.data_ptr(), gate_w.data_ptr(),
                                            C.byref(g), t, cfg.capacity(t), st, None, 0, None), "ccf_layer_backward")
-            N.count(9 + int(has_b1) + int(has_b2) + int(has_bg) + int(swiglu))
+            # kernels: dy dispatch + dgrad-2, wgrad-2, wgrad-1 (two for SwiGLU), dgrad-1 + combine, wait, reduce, column sums
+            N.count(6 + int(swiglu) + int(has_b1) + int(has_b2) + int(has_bg))
             if fm.check_every_call:
                 cc.check_status("fused MoE backward")
             return dx, dgate.view(t, cfg.top_k), None, dw1, db1, dwg, dbg, dw2, db2, None

@@ -8,9 +8,12 @@ from ccfuser_b200 import native as N
 
 
 @pytest.fixture(autouse=True)
-def _fresh_context():
-    """Layers of one process share their communication context; these tests change its mode, so each starts clean."""
+def _fresh_context(monkeypatch):
+    """Layers of one process share their communication context; these tests change its mode, so each starts clean.
+    They look at the launches one by one, so they use the launch-by-launch Python path (the default issues a whole
+    pass with one native call, which tests/test_native_runtime.py compares with this path)."""
     from ccfuser_b200.ops.fused import CommContext
+    monkeypatch.setenv("CCFUSER_NATIVE_RUNTIME", "0")
     CommContext._instances.clear()
     yield
     CommContext._instances.clear()

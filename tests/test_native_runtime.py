@@ -47,6 +47,7 @@ def _run_case(act, bias, tokens, world=1, rank=0):
                     ep_size=world, backend="fused", max_tokens=256, capacity_factor=1.5)
     layer = MoELayer(cfg, device="cpu")
     fm = layer._fused_impl()
+    fm.native_runtime = False
     real = N.load()
     x = torch.randn(tokens, 128).bfloat16().requires_grad_(True)
     # --- the Python path, launch by launch

@@ -171,6 +171,24 @@ def step_breakdown(torch, trainer, batch, c, tokens):
             table[cat] = table.get(cat, 0.0) + kern.duration / 1e3
             key = (cat, kern.name[:60])
             names[key] = names.get(key, 0.0) + kern.duration / 1e3
+    # kernels launched outside any recorded operator (library calls made through ctypes from plain Python code, e.g. the
+    # optimizer) have no launching event: they are found as the difference, per kernel name, between all device events
+    # and the attributed ones
+    from torch.autograd import DeviceType
+    seen, attributed = {}, {}
+    for ev in prof.events():
+        if getattr(ev, "device_type", None) == DeviceType.CUDA and not getattr(ev, "is_async", False):
+            seen[ev.name] = seen.get(ev.name, 0.0) + float(getattr(ev, "device_time_total", 0.0) or 0.0) / 1e3
+    for (cat, kname), v in list(names.items()):
+        attributed[kname] = attributed.get(kname, 0.0) + v
+    for kname_full, v in seen.items():
+        kname = kname_full[:60]
+        rest = v - attributed.get(kname, 0.0)
+        if rest > 1e-3 and not kname_full.lower().startswith(("memcpy", "memset")):
+            cat = classify_kernel(kname_full, "", "", vocab_padded, c.d_ffn, tokens)
+            table[cat] = table.get(cat, 0.0) + rest
+            names[(cat, kname)] = names.get((cat, kname), 0.0) + rest
+            attributed[kname] = attributed.get(kname, 0.0) + rest
     total = sum(table.values())
     top = sorted(names.items(), key=lambda kv: -kv[1])[:25]
     return {"kernel_ms_by_category": {k: round(v, 3) for k, v in sorted(table.items(), key=lambda kv: -kv[1])},

@@ -76,6 +76,7 @@ def main():
     ap.add_argument("--trace", action="store_true",
                     help="add per-tile clock statistics (main-loop time against its ideal, accumulator wait, epilogue time)")
     ap.add_argument("--out", default="", help="optional JSON file for the records")
+    ap.add_argument("--l2-prefetch", type=int, default=None, help="k-blocks of L2 prefetch ahead (default: the library's)")
     ap.add_argument("--back-to-back", type=int, default=0,
                     help="also time this many launches of each case without gaps and report the SM clock seen meanwhile")
     args = ap.parse_args()
@@ -117,7 +118,7 @@ def main():
         out.append(rec)
 
     def gemm(**kw):
-        return lambda trace=None: G.launch(trace=trace, **kw)
+        return lambda trace=None: G.launch(trace=trace, l2_prefetch=args.l2_prefetch, **kw)
 
     cases = args.cases.split(",")
     if "square" in cases:
@@ -136,6 +137,14 @@ def main():
         report("fwd1_gelu", 2 * r * d * f, gemm(
             a0=x, b0=w1.view(e * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT, n=f, k=d,
             group_base=gb, group_rows=gr, num_groups=e, b_group_rows=f, out0=h, out1=pre, act=N.ACT_GELU), kblocks=(d + 63) // 64)
+    # the same GEMM with parts of its epilogue taken away: which part costs the main loop its efficiency
+    if "fwd1_parts" in cases:
+        common = dict(a0=x, b0=w1.view(e * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_BIAS_ACT, n=f, k=d,
+                      group_base=gb, group_rows=gr, num_groups=e, b_group_rows=f, out0=h)
+        report("fwd1_one_output_no_act", 2 * r * d * f, gemm(act=N.ACT_NONE, **common), kblocks=(d + 63) // 64)
+        report("fwd1_one_output_gelu", 2 * r * d * f, gemm(act=N.ACT_GELU, **common), kblocks=(d + 63) // 64)
+        report("fwd1_two_outputs_no_act", 2 * r * d * f, gemm(act=N.ACT_NONE, out1=pre, **common), kblocks=(d + 63) // 64)
+        report("fwd1_two_outputs_relu", 2 * r * d * f, gemm(act=N.ACT_RELU, out1=pre, **common), kblocks=(d + 63) // 64)
     w2 = torch.randn(e, d, f, device=dev, dtype=torch.bfloat16) * 0.02
     y = torch.empty(r, d, device=dev, dtype=torch.bfloat16)
     if "fwd2" in cases:

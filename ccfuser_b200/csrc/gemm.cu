@@ -28,6 +28,8 @@
 #include <cuda_runtime.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "gemm_common.cuh"
 
 namespace ccf {
@@ -412,9 +414,49 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D row-major view [rows, cols] of 2-byte elements, box = {box_cols, box_rows}, 128-byte swizzle
+// 2-D row-major view [rows, cols] of 2-byte elements, box = {box_cols, box_rows}, 128-byte swizzle.
+// A tensor map is a pure function of (address, extents, box, type), so encoded maps are kept in a small direct-mapped
+// cache: a layer launches the same few operands every step, and in the latency-bound regime four driver calls per
+// launch cost as much as a small kernel.
+namespace {
+struct TmapKey {
+  const void* base;
+  long long rows, cols;
+  int box_cols, box_rows, fp16;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && box_cols == o.box_cols && box_rows == o.box_rows &&
+           fp16 == o.fp16;
+  }
+};
+struct TmapEntry {
+  TmapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kTmapCacheSize = 512;
+TmapEntry g_tmap_cache[kTmapCacheSize];
+std::mutex g_tmap_mutex;
+size_t tmap_hash(const TmapKey& k) {
+  size_t h = reinterpret_cast<size_t>(k.base) >> 8;
+  h = h * 1000003u ^ static_cast<size_t>(k.rows);
+  h = h * 1000003u ^ static_cast<size_t>(k.cols);
+  h = h * 1000003u ^ static_cast<size_t>((k.box_cols << 12) ^ (k.box_rows << 1) ^ k.fp16);
+  return h % kTmapCacheSize;
+}
+}  // namespace
+
 int make_tmap(CUtensorMap* m, const void* base, long long rows, long long cols, int box_cols, int box_rows,
                      int fp16) {
+  const TmapKey key = {base, rows, cols, box_cols, box_rows, fp16};
+  const size_t slot = tmap_hash(key);
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    const TmapEntry& e = g_tmap_cache[slot];
+    if (e.valid && e.key == key) {
+      *m = e.map;
+      return 0;
+    }
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -425,7 +467,15 @@ int make_tmap(CUtensorMap* m, const void* base, long long rows, long long cols, 
                   const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
+  if (r != CUDA_SUCCESS) return -static_cast<int>(r) - 1000;
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    TmapEntry& e = g_tmap_cache[slot];
+    e.key = key;
+    e.map = *m;
+    e.valid = true;
+  }
+  return 0;
 }
 
 template <int A, int B, int E, bool KG>

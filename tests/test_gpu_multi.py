@@ -33,7 +33,6 @@ def test_fused_layer_multi_gpu(world):
     _run(world, 29600 + world)
 
 
-@pytest.mark.xfail(strict=False, reason="shadow experts / re-placement on NCCL ranks: tolerances are provisional")
 @pytest.mark.parametrize("world", [2, 4])
 def test_shadow_and_rebalance_multi_gpu(world):
     if torch.cuda.device_count() < world:

@@ -20,7 +20,7 @@ from .experts import Experts, scan_expert_params
 from .gates import NaiveGate
 from .parallel.a2a import moe_forward_a2a
 from .parallel.placement import placement_cost, plan_placement, rebalance_experts
-from .parallel.shadow import gather_shadow_params, select_popular, shadow_forward, split_shadow_slots
+from .parallel.shadow import ShadowFused, gather_shadow_params, select_popular, shadow_forward, split_shadow_slots
 
 
 class MoELayer(nn.Module):
@@ -57,6 +57,7 @@ class MoELayer(nn.Module):
             self.shared = Experts(1, config.d_model, config.shared_ffn, config.activation, config.bias,
                                   dtype=config.dtype, device=device)
         self._fused = None
+        self._shadow_fused = None
         self.last_stats = {}
 
     # ---- backend selection -------------------------------------------------------------------
@@ -97,7 +98,12 @@ class MoELayer(nn.Module):
             shadow_ids = select_popular(idx, cfg.num_experts, cfg.shadow_experts, group)
             params = gather_shadow_params(self.experts, shadow_ids, self.ep_rank, group)
             idx, which = split_shadow_slots(idx, shadow_ids)
-            y_shadow = shadow_forward(x, which, score, params, cfg.activation)
+            if backend == "fused":
+                if self._shadow_fused is None:
+                    self._shadow_fused = ShadowFused(self, cfg.shadow_experts)
+                y_shadow = self._shadow_fused(x, which, score, params, cfg.activation)
+            else:
+                y_shadow = shadow_forward(x, which, score, params, cfg.activation)
             self.last_stats["shadow_ids"] = shadow_ids
         if backend == "fused":
             y = fused.run_experts(x, idx, score)
@@ -153,6 +159,9 @@ class MoELayer(nn.Module):
 
     def release(self):
         """Free the symmetric buffers of the fused path (collective)."""
+        if self._shadow_fused is not None:
+            self._shadow_fused.close()
+            self._shadow_fused = None
         if self._fused is not None:
             self._fused.close()
             self._fused = None

@@ -14,7 +14,10 @@ the feature only works as a timing experiment. Here the replicas are real:
 * gradients: the all-reduce is an autograd function whose backward is again a sum all-reduce, so the owner's
   parameter receives the sum of the replicas' gradients and the parameters stay single-copy;
 * the selected experts' slots are taken out of the expert-parallel path (expert id -1 = not routed) and computed
-  locally with library GEMMs; they are not subject to the capacity factor, since they draw on no shared buffer.
+  locally: on the fused backend by the same tcgen05 grouped GEMM kernels, as a second, single-rank instance of the
+  fused path whose "experts" are the replicas (``ShadowFused``: no host synchronisation, no library GEMM); on the other
+  backends with library GEMMs (``shadow_forward``). They are not subject to the capacity factor, since they draw on
+  no shared buffer.
 
 Cost model: replicating one expert moves its weights once per step (forward) and its gradients once (backward),
 ``2 x 3 x d_model x d_ffn x 2`` bytes for SwiGLU in bf16, instead of its tokens twice in each direction; it pays
@@ -116,6 +119,54 @@ def shadow_forward(x: torch.Tensor, which: torch.Tensor, score: torch.Tensor, pa
                        opt("htoh4_gate.bias") if activation == "swiglu" else None)
         y = y.index_add(0, tok, o * score[tok, slot].to(o.dtype).unsqueeze(1))
     return y
+
+
+class _ReplicaLayerView:
+    """What the fused path reads from a layer, for the replicas: a single-rank configuration with one expert per replica
+    and a receive buffer that holds every slot of the rank (a replica takes whatever its rank routes to it)."""
+
+    def __init__(self, layer, n: int):
+        cfg = layer.config
+        import copy
+        c = copy.copy(cfg)
+        # set field by field: with fewer replicas than top_k the public constructor's "top_k <= num_experts" check does
+        # not apply here (k is only the number of slots per token, most of them not shadowed)
+        for key, val in dict(num_experts=n, ep_size=1, shadow_experts=0, capacity_factor=None, backend="fused",
+                             recv_factor=1.0).items():
+            object.__setattr__(c, key, val)
+        self.config = c
+        self.experts = layer.experts          # only its device is used
+        self.gate = None
+        self.ep_rank, self.ep_group = 0, None
+
+
+class ShadowFused:
+    """The replicas' FFN on the fused kernels: ``y = sum over this rank's shadowed slots of score * FFN_replica(x)``
+    with routing ``which [T, k]`` (replica index, -1 = not shadowed). Differentiable with respect to x, score and the
+    gathered replica parameters (whose gradients return to the owners through ``gather_shadow_params``). The kernels
+    push the rows into this rank's own buffers (the dispatch role with one rank), so there is no index list built on the
+    host and nothing synchronises."""
+
+    def __init__(self, layer, n: int):
+        from ..ops.fused import FusedMoE
+        self.fm = FusedMoE(_ReplicaLayerView(layer, n))
+        self.fm.native_runtime = False        # parameters are fresh tensors every step: launch with the tensors passed in
+
+    def __call__(self, x, which, score, params, activation):
+        from ..ops.fused import _FusedMoEFn
+        swiglu = activation == "swiglu"
+        tensors = (x, score) + tuple(v for v in params.values() if v is not None)
+        self.fm._save_pre = torch.is_grad_enabled() and any(t.requires_grad for t in tensors)
+        try:
+            return _FusedMoEFn.apply(x.contiguous(), score.float(), which.to(torch.int32), params["htoh4.weight"],
+                                     params["htoh4.bias"], params["htoh4_gate.weight"] if swiglu else None,
+                                     params["htoh4_gate.bias"] if swiglu else None, params["h4toh.weight"],
+                                     params["h4toh.bias"], self.fm)
+        finally:
+            self.fm._save_pre = True
+
+    def close(self):
+        self.fm.close()
 
 
 def shadow_what_if(count_table: torch.Tensor, n: int, d_model: int, d_ffn: int, activation: str = "gelu",

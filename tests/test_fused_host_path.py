@@ -149,8 +149,9 @@ def test_two_rank_peer_pointers_line_up():
 
 
 def test_shadow_experts_on_the_fused_host_path():
-    """Replicated experts with the fused backend: their slots reach the kernels as expert id -1, the replicas run in
-    torch, and both parts receive gradients (kernels recorded, so only shapes, dtypes and wiring are checked)."""
+    """Replicated experts with the fused backend: their slots reach the expert-parallel kernels as expert id -1, the
+    replicas run as a second, single-rank instance of the same kernels (six more GEMM launches, whose operands are the
+    gathered replica weights), and both parts receive gradients (kernels recorded: shapes, dtypes and wiring only)."""
     cfg, layer = _layer("gelu", shadow_experts=1)
     x = torch.randn(120, cfg.d_model).bfloat16().requires_grad_(True)
     captured = {}
@@ -170,7 +171,13 @@ def test_shadow_experts_on_the_fused_host_path():
     shadow = layer.last_stats["shadow_ids"].tolist()
     idx = captured["idx"]
     assert idx.dtype == torch.int32 and (idx == shadow[0]).sum() == 0 and (idx == -1).sum() == 120 * 2 // cfg.num_experts
-    assert rec.names().count("ccf_gemm_launch") == 6
+    assert rec.names().count("ccf_gemm_launch") == 12
+    gemms = _gemms(rec)
+    own = {layer.experts.htoh4.weight.data_ptr(), layer.experts.h4toh.weight.data_ptr()}
+    assert sum(1 for g in gemms if g.b0 in own) == 4          # GEMM-1, GEMM-2, dgrad-2, dgrad-1 of the owners' path
+    replica = [g for g in gemms if g.args.num_groups == 1]
+    assert len(replica) == 6 and all(g.b0 not in own for g in replica)
+    assert "ccf_topk_softmax" not in rec.names() and rec.names().count("ccf_plan") == 2
     assert y.shape == x.shape and y.dtype == torch.bfloat16
     assert layer.experts.htoh4.weight.grad is not None and x.grad is not None
 

@@ -176,8 +176,11 @@ def step_breakdown(torch, trainer, batch, c, tokens):
     # and the attributed ones
     from torch.autograd import DeviceType
     seen, attributed = {}, {}
+    cpu_names = {ev.name for ev in prof.events() if getattr(ev, "device_type", None) == DeviceType.CPU}
     for ev in prof.events():
-        if getattr(ev, "device_type", None) == DeviceType.CUDA and not getattr(ev, "is_async", False):
+        # device-side copies of host annotations (record_function ranges shown on the GPU timeline) are not kernels
+        if (getattr(ev, "device_type", None) == DeviceType.CUDA and not getattr(ev, "is_async", False)
+                and ev.name not in cpu_names):
             seen[ev.name] = seen.get(ev.name, 0.0) + float(getattr(ev, "device_time_total", 0.0) or 0.0) / 1e3
     for (cat, kname), v in list(names.items()):
         attributed[kname] = attributed.get(kname, 0.0) + v

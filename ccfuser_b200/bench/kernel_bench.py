@@ -227,7 +227,8 @@ def main():
     args = ap.parse_args()
     rank, _, world = init_distributed()
     if args.sweep == "remote":
-        grid = [(args.experts_per_gpu, rf) for rf in (0.45, 0.25, 0.10, 0.0)]
+        # the reference sweeps the locality 0.55, 0.60, ... 1.0 (mix_moe/mix_moe/kernel_evaluation.py:366-369)
+        grid = [(args.experts_per_gpu, round(0.45 - 0.05 * i, 2)) for i in range(10)]
     elif args.sweep == "experts":
         grid = [(e, args.remote_frac) for e in (2, 4, 8, 16, 32, 64)]
     else:

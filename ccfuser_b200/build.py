@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libccfuser_b200.so")
-SOURCES = ["gemm.cu", "gemm2.cu", "moe_kernels.cu", "router.cu", "runtime.cu", "no_alloc.cu"]
+SOURCES = ["gemm.cu", "gemm2.cu", "moe_kernels.cu", "router.cu", "runtime.cu", "no_alloc.cu", "norm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -306,65 +306,78 @@ __global__ void combine_wait_kernel(const int* done, int* cum, const int* sent_r
   cum[o] = target;
 }
 
-// y[t, :] = sum_j keep(t, j) * comb[t * k + j, :]; one warp per token, 16-byte vectors, fp32 accumulate.
+// y[t, :] = sum_j keep(t, j) * comb[t * k + j, :]; one thread per 16-byte piece of an output row, fp32 accumulate.
+// (A warp per token made the kernel latency-bound for small batches: d / 256 dependent iterations per warp.)
 __global__ void combine_reduce_kernel(const void* comb, const int* slot_row, void* y, int T, int K, int d, int fp16) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= T) return;
   const int vecs = d >> 3;
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= static_cast<long long>(T) * vecs) return;
+  const int t = static_cast<int>(gid / vecs), v = static_cast<int>(gid - static_cast<long long>(t) * vecs);
   const uint4* c = reinterpret_cast<const uint4*>(comb);
-  uint4* out = reinterpret_cast<uint4*>(y) + static_cast<size_t>(warp) * vecs;
-  for (int v = lane; v < vecs; v += 32) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int j = 0; j < K; ++j) {
-      const int s = warp * K + j;
-      if (slot_row[s] < 0) continue;
-      const uint4 x = c[static_cast<size_t>(s) * vecs + v];
-      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int j = 0; j < K; ++j) {
+    const int s = t * K + j;
+    if (__ldg(slot_row + s) < 0) continue;
+    const uint4 x = c[static_cast<size_t>(s) * vecs + v];
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 f = unpack2(w[q], fp16);
-        acc[2 * q] += f.x;
-        acc[2 * q + 1] += f.y;
-      }
+    for (int q = 0; q < 4; ++q) {
+      const float2 f = unpack2(w[q], fp16);
+      acc[2 * q] += f.x;
+      acc[2 * q + 1] += f.y;
     }
-    uint4 o;
-    o.x = pack2(acc[0], acc[1], fp16);
-    o.y = pack2(acc[2], acc[3], fp16);
-    o.z = pack2(acc[4], acc[5], fp16);
-    o.w = pack2(acc[6], acc[7], fp16);
-    out[v] = o;
   }
+  uint4 o;
+  o.x = pack2(acc[0], acc[1], fp16);
+  o.y = pack2(acc[2], acc[3], fp16);
+  o.z = pack2(acc[4], acc[5], fp16);
+  o.w = pack2(acc[6], acc[7], fp16);
+  reinterpret_cast<uint4*>(y)[static_cast<size_t>(t) * vecs + v] = o;
 }
 
 // ---------------------------------------------------------------------------------------------------
-// bias gradients: out[g, n] = sum over the rows of group g of x[r, n]. Block = 128 columns x 8 row lanes.
+// bias gradients: out[g, n] = sum over the rows of group g of x[r, n]. Block = 128 columns (16 lanes x 16 bytes) x 16
+// row lanes, four rows in flight per thread: the kernel streams the matrix once and has to keep enough loads in
+// flight to do so at the memory rate.
 // ---------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) colsum_grouped_kernel(const void* x, long long ld, int n, const int* group_base,
                                                              const int* group_rows, void* out, int fp16) {
-  __shared__ float red[8][128];
+  __shared__ float red[16][128];
   const int g = blockIdx.y;
-  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-  const int col = blockIdx.x * 128 + cx * 4;
-  float acc[4] = {0, 0, 0, 0};
+  const int cx = threadIdx.x & 15, ry = threadIdx.x >> 4;
+  const int col = blockIdx.x * 128 + cx * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col < n) {
     const int r0 = group_base[g], nr = group_rows[g];
-    const uint16_t* base = reinterpret_cast<const uint16_t*>(x);
-    for (int r = ry; r < nr; r += 8) {
-      const uint2 v = *reinterpret_cast<const uint2*>(base + static_cast<size_t>(r0 + r) * ld + col);
-      const float2 a = unpack2(v.x, fp16), b = unpack2(v.y, fp16);
-      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+    const uint16_t* base = reinterpret_cast<const uint16_t*>(x) + static_cast<size_t>(r0) * ld + col;
+    for (int r = ry; r < nr; r += 64) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + 16 * u;
+        v[u] = rr < nr ? __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(rr) * ld)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = unpack2(w[q], fp16);
+          acc[2 * q] += f.x;
+          acc[2 * q + 1] += f.y;
+        }
+      }
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) red[ry][cx * 4 + i] = acc[i];
+  for (int i = 0; i < 8; ++i) red[ry][cx * 8 + i] = acc[i];
   __syncthreads();
   if (threadIdx.x < 128) {
     const int c = blockIdx.x * 128 + threadIdx.x;
     if (c < n) {
       float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s += red[i][threadIdx.x];
+      for (int i = 0; i < 16; ++i) s += red[i][threadIdx.x];
       if (fp16) reinterpret_cast<__half*>(out)[static_cast<size_t>(g) * n + c] = __float2half(s);
       else reinterpret_cast<__nv_bfloat16*>(out)[static_cast<size_t>(g) * n + c] = __float2bfloat16(s);
     }
@@ -534,15 +547,18 @@ int ccf_combine_wait(const int* done, int* cum, const int* sent_rows, int n_tile
 int ccf_combine_reduce(const void* comb, const int* slot_row, void* y, int T, int K, int d, int fp16, void* stream) {
   if (d % 8 != 0) return -2;
   if (T == 0) return 0;
-  const int threads = 256, blocks = (T * 32 + threads - 1) / threads;
-  ccf::combine_reduce_kernel<<<blocks, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(comb, slot_row, y, T, K,
-                                                                                             d, fp16);
+  const long long pieces = static_cast<long long>(T) * (d >> 3);
+  const int threads = 256;
+  const long long blocks = (pieces + threads - 1) / threads;
+  if (blocks > 0x7fffffffLL) return -2;
+  ccf::combine_reduce_kernel<<<static_cast<unsigned>(blocks), threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      comb, slot_row, y, T, K, d, fp16);
   return last_err();
 }
 
 int ccf_colsum_grouped(const void* x, long long ld, int n, int groups, const int* group_base, const int* group_rows,
                        void* out, int fp16, void* stream) {
-  if (n % 4 != 0) return -2;
+  if (n % 8 != 0 || ld % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;   // 16-byte loads
   dim3 grid((n + 127) / 128, groups);
   ccf::colsum_grouped_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, ld, n, group_base,
                                                                                         group_rows, out, fp16);

@@ -17,6 +17,7 @@ import torch.nn.functional as F
 
 from ..config import MoEConfig
 from ..layers import MoELayer
+from ..ops.norm import LayerNorm
 
 
 @dataclasses.dataclass
@@ -82,10 +83,10 @@ class BertLayer(nn.Module):
     def __init__(self, c: BertMoEConfig, moe: bool, ep_group=None, device=None):
         super().__init__()
         self.attention = BertSelfAttention(c, device)
-        self.ln_attn = nn.LayerNorm(c.d_model, eps=c.layer_norm_eps, device=device, dtype=c.dtype)
+        self.ln_attn = LayerNorm(c.d_model, eps=c.layer_norm_eps, device=device, dtype=c.dtype)
         self.is_moe = moe
         self.ffn = MoELayer(c.moe_config(), ep_group=ep_group, device=device) if moe else FFN(c, device)
-        self.ln_ffn = nn.LayerNorm(c.d_model, eps=c.layer_norm_eps, device=device, dtype=c.dtype)
+        self.ln_ffn = LayerNorm(c.d_model, eps=c.layer_norm_eps, device=device, dtype=c.dtype)
 
     def forward(self, x, mask, token_mask=None):
         x = self.ln_attn(x + self.attention(x, mask))
@@ -104,7 +105,7 @@ class BertMoEForQuestionAnswering(nn.Module):
         self.word = nn.Embedding(c.vocab_size, c.d_model, device=device, dtype=c.dtype)
         self.position = nn.Embedding(c.max_position, c.d_model, device=device, dtype=c.dtype)
         self.token_type = nn.Embedding(c.type_vocab_size, c.d_model, device=device, dtype=c.dtype)
-        self.ln_emb = nn.LayerNorm(c.d_model, eps=c.layer_norm_eps, device=device, dtype=c.dtype)
+        self.ln_emb = LayerNorm(c.d_model, eps=c.layer_norm_eps, device=device, dtype=c.dtype)
         self.layer = nn.ModuleList([BertLayer(c, i in set(c.moe_layers), ep_group, device) for i in range(c.n_layer)])
         self.qa_outputs = nn.Linear(c.d_model, 2, device=device, dtype=c.dtype)
         for m in self.modules():

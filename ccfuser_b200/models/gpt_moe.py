@@ -18,6 +18,7 @@ import torch.nn.functional as F
 
 from ..config import MoEConfig
 from ..layers import MoELayer
+from ..ops.norm import LayerNorm
 
 
 @dataclasses.dataclass
@@ -113,9 +114,9 @@ class Block(nn.Module):
     """Pre-LN transformer block: attention, then a dense FFN or an MoE layer."""
     def __init__(self, c: GPTMoEConfig, moe: bool, ep_group=None, device=None):
         super().__init__()
-        self.ln_1 = nn.LayerNorm(c.d_model, device=device, dtype=c.dtype)
+        self.ln_1 = LayerNorm(c.d_model, device=device, dtype=c.dtype)
         self.attn = CausalSelfAttention(c, device)
-        self.ln_2 = nn.LayerNorm(c.d_model, device=device, dtype=c.dtype)
+        self.ln_2 = LayerNorm(c.d_model, device=device, dtype=c.dtype)
         self.is_moe = moe
         self.mlp = MoELayer(c.moe_config(), ep_group=ep_group, device=device) if moe else DenseFFN(c, device)
 
@@ -136,7 +137,7 @@ class GPTMoE(nn.Module):
         self.wte = nn.Embedding(self.vocab_padded, c.d_model, device=device, dtype=c.dtype)
         self.wpe = nn.Embedding(c.seq_len, c.d_model, device=device, dtype=c.dtype)
         self.h = nn.ModuleList([Block(c, c.is_moe(i), ep_group, device) for i in range(c.n_layer)])
-        self.ln_f = nn.LayerNorm(c.d_model, device=device, dtype=c.dtype)
+        self.ln_f = LayerNorm(c.d_model, device=device, dtype=c.dtype)
         self.apply(self._init)
         for name, p in self.named_parameters():
             if name.endswith("c_proj.weight"):

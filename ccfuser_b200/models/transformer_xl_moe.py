@@ -20,6 +20,7 @@ import torch.nn.functional as F
 
 from ..config import MoEConfig
 from ..layers import MoELayer
+from ..ops.norm import LayerNorm
 
 
 @dataclasses.dataclass
@@ -122,8 +123,8 @@ class DecoderLayer(nn.Module):
     def __init__(self, c: TransformerXLMoEConfig, ep_group=None, device=None):
         super().__init__()
         self.attn = RelPartialLearnableAttention(c, device)
-        self.ln1 = nn.LayerNorm(c.d_model, device=device, dtype=c.dtype)
-        self.ln2 = nn.LayerNorm(c.d_model, device=device, dtype=c.dtype)
+        self.ln1 = LayerNorm(c.d_model, device=device, dtype=c.dtype)
+        self.ln2 = LayerNorm(c.d_model, device=device, dtype=c.dtype)
         self.is_moe = c.moe
         self.pos_ff = MoELayer(c.moe_config(), ep_group=ep_group, device=device) if c.moe else PositionwiseFF(c, device)
         self.pre_lnorm = c.pre_lnorm

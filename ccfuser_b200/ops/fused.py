@@ -269,6 +269,7 @@ class FusedMoE:
         self.native_runtime = bool(env_flag("NATIVE_RUNTIME", 1))
         self._desc = None
         self._desc_key = None
+        self._owed = None       # weak reference to the autograd node whose backward still needs this layer's buffers
 
     # ------------------------------------------------------------------------------------------
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
@@ -369,6 +370,28 @@ class FusedMoE:
             torch.cuda.current_device() if self.device.type == "cuda" else -1)
         self._desc, self._desc_key = L, key
         return L
+
+    # ---- one outstanding forward per layer ----------------------------------------------------------
+    def claim_buffers(self, fn_ctx):
+        """The saved activations of a forward pass (received rows, pre-activations, activations, routing arrays) live
+        in this layer's buffers until its backward pass has run. A second forward in between (an evaluation inside a
+        training step, activation checkpointing's recomputation, two micro-batches before one backward) would
+        overwrite them and the first backward would silently use the wrong data: raise instead. The claim ends when the
+        backward runs or when the autograd graph that holds it is freed."""
+        import weakref
+        owner = self._owed() if self._owed is not None else None
+        if owner is not None and not getattr(owner, "ccf_backward_done", False):
+            raise RuntimeError(
+                "ccfuser_b200: this MoE layer was called again while the activations saved by its previous forward pass "
+                "are still needed by a backward pass that has not run. The fused backend keeps one set of saved "
+                "activations per layer: run backward first, call the second forward under torch.no_grad() after it, or "
+                "drop the first result (del loss) if no backward will follow.")
+        self._owed = weakref.ref(fn_ctx) if self._save_pre else None
+
+    def release_buffers(self, fn_ctx):
+        fn_ctx.ccf_backward_done = True
+        if self._owed is not None and self._owed() is fn_ctx:
+            self._owed = None
 
     def close(self):
         """Free this layer's symmetric buffers (collective: call on every rank, in the same order of layers). The
@@ -524,13 +547,16 @@ class GraphedForward:
         self._rows = torch.arange(tokens, device=fm.device)
         side = torch.cuda.Stream(device=fm.device)
         side.wait_stream(torch.cuda.current_stream(fm.device))
+        fm.ctx.ws.ordered_after()                     # the side stream is ordered after everything issued so far
         with torch.cuda.stream(side), torch.no_grad():
             for _ in range(max(1, warmup)):           # first-use set-up (attributes, driver entry points) outside capture
                 layer(self.x, token_mask=self.valid)
         torch.cuda.current_stream(fm.device).wait_stream(side)
+        fm.ctx.ws.ordered_after()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph), torch.no_grad():
             self.y = layer(self.x, token_mask=self.valid)
+        fm.ctx.ws.ordered_after()                     # capture ran on torch's capture stream; replays follow the caller's
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         x = x.reshape(-1, self.x.shape[1])
@@ -564,6 +590,8 @@ class _FusedMoEFn(torch.autograd.Function):
         t, d = x.shape
         idx = idx.contiguous()
         gate_w = gate_w.contiguous()
+        fm.ctx.ws.enter()
+        fm.claim_buffers(ctx)
         if fm.native_runtime:
             y = torch.empty(t, d, dtype=x.dtype, device=x.device)
             cc = fm.ctx
@@ -600,6 +628,8 @@ class _FusedMoEFn(torch.autograd.Function):
         lib = N.load()
         fm: FusedMoE = ctx.fm
         cfg, cc = fm.cfg, fm.ctx
+        cc.ws.enter()
+        fm.release_buffers(ctx)
         idx, gate_w, w1, wg, w2 = ctx.saved_tensors
         st = N.stream_ptr()
         t, d, f, e_loc = ctx.tokens, cfg.d_model, cfg.d_ffn, cfg.experts_per_rank

@@ -25,6 +25,7 @@ class Workspace:
     def __init__(self, device):
         self.sched = torch.zeros(8, dtype=torch.int32, device=device)
         self.status = torch.zeros(2, dtype=torch.int32, device=device)  # [first hard error, overflow count]
+        self._last_stream = None
 
     @classmethod
     def get(cls, device) -> "Workspace":
@@ -37,6 +38,27 @@ class Workspace:
         if ws is None:
             ws = cls._by_device[key] = Workspace(device)
         return ws
+
+    def enter(self):
+        """Called by every launcher with the stream it is about to launch on. The kernels of one device share this
+        workspace's scheduler words, so two calls may only follow each other on different streams if the earlier
+        stream has drained (or the caller ordered the streams and says so with ``ordered_after``); work still pending
+        on another stream means the two could run concurrently and corrupt each other's tile counters: that raises."""
+        if self.sched.device.type != "cuda":
+            return
+        cur = torch.cuda.current_stream(self.sched.device)
+        last = self._last_stream
+        if last is not None and last != cur and not torch.cuda.is_current_stream_capturing() and not last.query():
+            raise RuntimeError(
+                "ccfuser_b200: a fused kernel is being launched on a different CUDA stream while earlier fused work is "
+                "still pending on another stream of the same device. The kernels of one device share scheduler words: "
+                "issue them on one stream, or order the streams (wait_stream / events) and call "
+                "Workspace.get(device).ordered_after() before switching.")
+        self._last_stream = cur
+
+    def ordered_after(self):
+        """The caller has ordered its next stream after all fused work issued so far (event or wait_stream)."""
+        self._last_stream = None
 
     def check(self, what: str = "kernel"):
         """Host read of the status word; raises if a kernel recorded an error, then clears it."""
@@ -113,6 +135,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     """Fill a CcfGemmLaunch and launch on the current stream. a0/b0 are 2-D contiguous views."""
     lib = N.load()
     ws = workspace or Workspace.get(a0.device)
+    ws.enter()
     L = N.GemmLaunch()
     g = L.args
     g.group_base, g.group_rows = N.ptr(group_base), N.ptr(group_rows)

@@ -302,3 +302,26 @@ def test_token_mask_reaches_the_kernels_as_unrouted_slots():
     with N.record_launches(), torch.no_grad():
         layer(torch.randn(40, cfg.d_model).bfloat16(), token_mask=mask)
     assert seen["idx"].dtype == torch.int32 and (seen["idx"][30:] == -1).all() and (seen["idx"][:30] == 1).all()
+
+
+def test_second_forward_before_backward_raises_instead_of_corrupting():
+    """One set of saved activations per layer: a forward while a backward is still owed raises; after the backward, or
+    once the first result has been dropped, the layer can be called again."""
+    cfg, layer = _layer("gelu")
+    x = torch.randn(100, cfg.d_model).bfloat16().requires_grad_(True)
+    with N.record_launches():
+        y1 = layer(x)
+        with pytest.raises(RuntimeError, match="previous forward"):
+            layer(x)
+        with pytest.raises(RuntimeError, match="previous forward"), torch.no_grad():
+            layer(x)                                   # an evaluation pass in between would overwrite them as well
+        y1.float().sum().backward()
+        y2 = layer(x)                                  # backward has run: fine
+        del y2                                         # dropped without a backward: the claim ends with its graph
+        import gc
+        gc.collect()
+        y3 = layer(x)
+        y3.float().sum().backward()
+        with torch.no_grad():
+            layer(x)
+            layer(x)                                   # inference calls never hold a claim

@@ -76,7 +76,6 @@ def main():
     ap.add_argument("--trace", action="store_true",
                     help="add per-tile clock statistics (main-loop time against its ideal, accumulator wait, epilogue time)")
     ap.add_argument("--out", default="", help="optional JSON file for the records")
-    ap.add_argument("--l2-prefetch", type=int, default=None, help="k-blocks of L2 prefetch ahead (default: the library's)")
     ap.add_argument("--back-to-back", type=int, default=0,
                     help="also time this many launches of each case without gaps and report the SM clock seen meanwhile")
     args = ap.parse_args()
@@ -118,7 +117,7 @@ def main():
         out.append(rec)
 
     def gemm(**kw):
-        return lambda trace=None: G.launch(trace=trace, l2_prefetch=args.l2_prefetch, **kw)
+        return lambda trace=None: G.launch(trace=trace, **kw)
 
     cases = args.cases.split(",")
     if "square" in cases:

@@ -65,7 +65,14 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fp16) {
 template <int kChunk, bool kBackward>
 __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status) {
   static_assert(kChunk <= 16, "one lane per row of a chunk; rows of a chunk are held in registers");
+  // Scalars used inside the copy loops are read once: `a` arrives by reference, so the compiler must assume that the
+  // row stores below may alias it and would otherwise reload them after every store.
   const int e_total = a.e_total;
+  const int fp16 = a.fp16, top_k = a.top_k, my_rank = a.my_rank, experts_per_rank = a.experts_per_rank;
+  const int capacity = a.capacity, max_rows = a.max_rows, total_index = a.total_index;
+  float* const dgate = a.dgate;
+  const void* const saved_comb = a.saved_comb;
+  const void* const x_rows = a.x;
   const int kept = a.order_off[e_total];   // rows to push
   const int lane = threadIdx.x & 31;
   const int vecs = a.d >> 3;  // 16-byte vectors per row
@@ -87,19 +94,19 @@ __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status
       const int e = a.slot_expert[s];
       const int p = a.slot_pos[s];
       my_gate = a.slot_gate[s];
-      my_owner = e / a.experts_per_rank;
+      my_owner = e / experts_per_rank;
       my_row = a.dst_base[e] + p;
-      if (my_row < 0 || my_row >= a.max_rows || my_owner >= CCF_MAX_RANKS || p >= a.capacity) {
+      if (my_row < 0 || my_row >= max_rows || my_owner >= CCF_MAX_RANKS || p >= capacity) {
         // beyond the owner's buffer: dropped on both sides (the plan did not count it)
-        if (p < a.capacity) report_status(status, CCF_ERR_OVERFLOW, s & 0xffffff);
+        if (p < capacity) report_status(status, CCF_ERR_OVERFLOW, s & 0xffffff);
         my_row = -1;
       }
       if (a.slot_row) a.slot_row[s] = my_row;
       if (my_row >= 0) {
-        a.peer_row_src[my_owner][my_row] = (a.my_rank << 24) | s;
+        a.peer_row_src[my_owner][my_row] = (my_rank << 24) | s;
         a.peer_row_gate[my_owner][my_row] = my_gate;
-      } else if (kBackward && a.dgate) {
-        a.dgate[s] = 0.f;
+      } else if (kBackward && dgate) {
+        dgate[s] = 0.f;
       }
     }
     // Source and destination of the chunk's rows (null = dropped or past the end). All kChunk rows are
@@ -112,8 +119,8 @@ __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status
       const int row = __shfl_sync(0xffffffffu, my_row, i);
       const int owner = __shfl_sync(0xffffffffu, my_owner, i);
       const bool on = i < ns && row >= 0;
-      const int t = __shfl_sync(0xffffffffu, my_slot, i) / a.top_k;
-      src[i] = on ? reinterpret_cast<const uint4*>(a.x) + static_cast<size_t>(t) * vecs : nullptr;
+      const int t = __shfl_sync(0xffffffffu, my_slot, i) / top_k;
+      src[i] = on ? reinterpret_cast<const uint4*>(x_rows) + static_cast<size_t>(t) * vecs : nullptr;
       dst[i] = on ? reinterpret_cast<uint4*>(a.peer_recv[owner]) + static_cast<size_t>(row) * vecs : nullptr;
     }
     if constexpr (!kBackward) {
@@ -136,8 +143,8 @@ __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status
         dot[i] = 0.f;
         g[i] = __shfl_sync(0xffffffffu, my_gate, i);
         slot[i] = __shfl_sync(0xffffffffu, my_slot, i);
-        sv[i] = (src[i] && a.saved_comb)
-                    ? reinterpret_cast<const uint4*>(a.saved_comb) + static_cast<size_t>(slot[i]) * vecs
+        sv[i] = (src[i] && saved_comb)
+                    ? reinterpret_cast<const uint4*>(saved_comb) + static_cast<size_t>(slot[i]) * vecs
                     : nullptr;
       }
       for (int v = lane; v < vecs; v += 32) {
@@ -155,10 +162,10 @@ __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status
           uint32_t o[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const float2 xf = unpack2(xi[q], a.fp16);
-            const float2 cf = unpack2(ci[q], a.fp16);
+            const float2 xf = unpack2(xi[q], fp16);
+            const float2 cf = unpack2(ci[q], fp16);
             dot[i] += xf.x * cf.x + xf.y * cf.y;
-            o[q] = pack2(xf.x * g[i], xf.y * g[i], a.fp16);
+            o[q] = pack2(xf.x * g[i], xf.y * g[i], fp16);
           }
           dst[i][v] = make_uint4(o[0], o[1], o[2], o[3]);
         }
@@ -167,7 +174,7 @@ __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status
       for (int i = 0; i < kChunk; ++i) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], off);
-        if (lane == 0 && dst[i] && a.dgate) a.dgate[slot[i]] = (g[i] != 0.f) ? dot[i] / g[i] : 0.f;
+        if (lane == 0 && dst[i] && dgate) dgate[slot[i]] = (g[i] != 0.f) ? dot[i] / g[i] : 0.f;
       }
     }
     // The counters move with release semantics at system scope after a warp barrier: the barrier orders the other
@@ -176,7 +183,7 @@ __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status
     // Rows that stay on this GPU only need device scope (the consumer is a CTA of this GPU); a system-scope
     // release costs several microseconds more per chunk.
     const bool sent = lane < ns && my_row >= 0;
-    const bool all_local = __all_sync(0xffffffffu, !sent || my_owner == a.my_rank);
+    const bool all_local = __all_sync(0xffffffffu, !sent || my_owner == my_rank);
     // rows of a chunk mostly share one tile: one counter update per distinct (owner, tile)
     const int key = sent ? ((my_owner << 24) | (my_row >> 7)) : -1;
     const unsigned same_tile = __match_any_sync(0xffffffffu, key);
@@ -184,11 +191,11 @@ __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status
       int* flag = a.peer_tile_flags[my_owner] + (my_row >> 7);
       if (all_local) red_release_gpu_add(flag, __popc(same_tile)); else red_release_sys_add(flag, __popc(same_tile));
     }
-    if (a.total_index >= 0) {
+    if (total_index >= 0) {
       // one add per distinct owner of the chunk to that owner's count of all arrived rows
       const unsigned same = __match_any_sync(0xffffffffu, sent ? my_owner : -1);
       if (sent && lane == __ffs(same) - 1) {
-        int* tot = a.peer_tile_flags[my_owner] + a.total_index;
+        int* tot = a.peer_tile_flags[my_owner] + total_index;
         if (all_local) red_release_gpu_add(tot, __popc(same)); else red_release_sys_add(tot, __popc(same));
       }
     }

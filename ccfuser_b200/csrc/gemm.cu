@@ -316,12 +316,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       }
       if (++as == 2) { as = 0; aphase ^= 1; }
     }
+  } else if (warp >= 2 + kEpiWarps) {
+    // ======================= dispatch warps =======================
+    dispatch_role<kEpi>(args, true);
+    if (warp == 2 + kEpiWarps && lane == 0 && args.trace != nullptr && args.comm_warps) trace_ev(args, args.trace_tiles - 1, 1);
   } else {
     // ======================= epilogue (warps 2..9) =======================
     const int q = warp & 3;               // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
-    dispatch_role<kEpi>(args);
-    if (warp == 2 && lane == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
+    dispatch_role<kEpi>(args, false);
+    if (warp == 2 && lane == 0 && args.trace != nullptr && !args.comm_warps) trace_ev(args, args.trace_tiles - 1, 1);
     int ss = 0, sphase = 0, as = 0, aphase = 0, seq = -1;
     while (true) {
       ++seq;

@@ -341,34 +341,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
             tma_load_2d_pair(sb + 8192, mb, full_leader, ti.n0 + nh + 64, r);
           }
         }
-        if (lane == 1 && args.l2_prefetch > 0 && kb + args.l2_prefetch < ti.kblocks) {
-          // the same boxes, args.l2_prefetch k-blocks further on, into L2 only (a second lane, so that the loads above
-          // and these do not queue behind each other in one thread)
-          const int kp = kb + args.l2_prefetch;
-          const int seg = kKGroup ? 0 : kp / kb_per_seg;
-          const int kk = kKGroup ? 0 : (kp - seg * kb_per_seg) * BK;
-          const CUtensorMap* ma = seg ? &tmA1 : &tmA0;
-          const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
-          if constexpr (kAMajor == MAJ_K) {
-            tma_prefetch_2d(ma, kk, my_row0);
-          } else {
-            const int r = ti.krow0 + kp * BK;
-            tma_prefetch_2d(ma, my_row0, r);
-            tma_prefetch_2d(ma, my_row0 + 64, r);
-          }
-          const int nh = static_cast<int>(cta) * (BN / 2);
-          if constexpr (kBMajor == MAJ_K) {
-            if constexpr (kEpi == CCF_EPI_SWIGLU) {
-              tma_prefetch_2d(cta == 0 ? &tmB1 : &tmB0, kk, ti.g * args.b_group_rows + ti.n0);
-            } else {
-              tma_prefetch_2d(mb, kk, ti.g * args.b_group_rows + ti.n0 + nh);
-            }
-          } else {
-            const int r = kKGroup ? ti.krow0 + kp * BK : ti.g * args.b_group_rows + kk;
-            tma_prefetch_2d(mb, ti.n0 + nh, r);
-            tma_prefetch_2d(mb, ti.n0 + nh + 64, r);
-          }
-        }
         __syncwarp();
         if (++stage == k2Stages) { stage = 0; phase ^= 1; }
       }
@@ -426,12 +398,16 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
         if (++as == 2) { as = 0; aphase ^= 1; }
       }
     }
+  } else if (warp >= 2 + kEpiWarps) {
+    // ======================= dispatch warps =======================
+    dispatch_role<kEpi>(args, true);
+    if (warp == 2 + kEpiWarps && lane == 0 && args.trace != nullptr && args.comm_warps) trace_ev(args, args.trace_tiles - 1, 1);
   } else {
     // ======================= epilogue (warps 2..9, both CTAs) =======================
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
-    dispatch_role<kEpi>(args);
-    if (warp == 2 && lane == 0 && args.trace != nullptr) trace_ev(args, args.trace_tiles - 1, 1);
+    dispatch_role<kEpi>(args, false);
+    if (warp == 2 && lane == 0 && args.trace != nullptr && !args.comm_warps) trace_ev(args, args.trace_tiles - 1, 1);
     int as = 0, aphase = 0, seq = 0;
     for (int t = pair; t < total_tiles; t += n_pairs, ++seq) {
       const PairTile ti = decode_pair_tile<kKGroup, kEpi>(t, args, ctrl);

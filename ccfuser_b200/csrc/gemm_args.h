@@ -99,7 +99,9 @@ struct CcfGemmArgs {
   int max_slots;            // COMBINE: rows of a combine buffer (bounds check)
   int trace_tiles;          // tiles per CTA recorded in `trace`
   int total_index;          // element of tile_flags that counts all arrived rows (-1 = none); lets late tiles skip their flag
-  int l2_prefetch;          // CTA-pair kernel: operand boxes are prefetched into L2 this many k-blocks ahead (0 = off)
+  int pad1;
+  int comm_warps;           // 1: the CTA's two dedicated warps run the dispatch role; 0: its epilogue warps do, before their first tile
+  int pad2;
   CcfDispatchArgs disp;
 };
 

@@ -13,7 +13,10 @@ namespace ccf {
 
 constexpr int BM = 128, BN = 256, BK = 64, UK = 16;
 constexpr int kEpiWarps = 8;            // two per TMEM lane quarter, each takes half of the columns
-constexpr int kThreads = 64 + 32 * kEpiWarps;
+// Two more warps per CTA exist only for the dispatch role: with them the row push runs next to the MMA and epilogue warps
+// (which start on the tiles made of this rank's own rows) instead of in front of the epilogue.
+constexpr int kCommWarps = 2;
+constexpr int kThreads = 64 + 32 * kEpiWarps + 32 * kCommWarps;
 constexpr int kTmemCols = 512;
 constexpr int MAJ_K = 0, MAJ_MN = 1;
 constexpr int kEpiStageBytes = 2048;  // per epilogue warp: 32 rows x 64 bytes, XOR-swizzled
@@ -423,8 +426,11 @@ __device__ __forceinline__ void combine_signal(const CcfGemmArgs& args, const Co
 // The dispatch role as the epilogue warps of a GEMM kernel run it before their first accumulator is due. Only the
 // kernels whose A operand is the receive buffer carry it: the forward ones (bias + activation, SwiGLU) push x rows, the
 // backward ones (activation derivative) push g * dy rows; every other epilogue compiles to nothing here.
+// `comm_warp`: the caller is one of the CTA's dedicated dispatch warps (else an epilogue warp); args.comm_warps says
+// which of the two kinds carries the role in this launch.
 template <int kEpi>
-__device__ __forceinline__ void dispatch_role(const CcfGemmArgs& args) {
+__device__ __forceinline__ void dispatch_role(const CcfGemmArgs& args, bool comm_warp) {
+  if (comm_warp != (args.comm_warps != 0)) return;
   if constexpr (kEpi == CCF_EPI_BIAS_ACT || kEpi == CCF_EPI_SWIGLU) {
     if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8, false>(args.disp, args.status);
   } else if constexpr (kEpi == CCF_EPI_DACT || kEpi == CCF_EPI_DSWIGLU) {

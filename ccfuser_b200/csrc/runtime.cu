@@ -49,7 +49,7 @@ CcfGemmLaunch base_launch(const CcfLayer* L) {
   g.args.fp16 = L->fp16;
   g.args.world = 1;
   g.args.total_index = -1;
-  g.args.l2_prefetch = L->l2_prefetch;
+  g.args.comm_warps = L->comm_warps;
   g.device = L->device;
   g.two_cta = L->two_cta;
   return g;

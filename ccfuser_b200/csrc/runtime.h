@@ -67,7 +67,9 @@ struct CcfLayer {
   int n_comm_ctas;  // CTAs whose epilogue warps run the dispatch role
   int two_cta;      // default GEMM kernel: 1 = CTA pairs
   int device;       // CUDA device (-1: leave the calling thread's device alone)
-  int l2_prefetch;  // CTA-pair kernel: k-blocks of L2 prefetch ahead of the operand loads (0 = off)
+  int pad0;
+  int comm_warps;   // 1: dedicated dispatch warps carry the row push, 0: the epilogue warps do
+  int pad1;
 };
 
 // Per-call tensors of the backward pass (all allocated by the caller; null where the layer has no such parameter).

@@ -365,7 +365,7 @@ class FusedMoE:
         L.max_rows, L.max_slots = self.max_rows, self.max_slots
         L.n_comm_ctas = min(int(cc.n_comm), 1 << 30)
         L.two_cta = int(G.TWO_CTA_DEFAULT)
-        L.l2_prefetch = int(G.L2_PREFETCH_DEFAULT)
+        L.comm_warps = int(G.COMM_WARPS_DEFAULT)
         L.device = self.device.index if (self.device.type == "cuda" and self.device.index is not None) else (
             torch.cuda.current_device() if self.device.type == "cuda" else -1)
         self._desc, self._desc_key = L, key

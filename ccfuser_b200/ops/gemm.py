@@ -113,8 +113,9 @@ def describe_status(code: int, detail: int) -> str:
 DEFAULT_WAIT_NS = 5_000_000_000
 # 256x256 tiles on CTA pairs (tcgen05 cta_group::2) by default; CCFUSER_TWO_CTA=0 selects the one-CTA 128x256 kernel
 TWO_CTA_DEFAULT = bool(int(__import__('os').environ.get('CCFUSER_TWO_CTA', '1')))
-# the CTA-pair kernel prefetches its operand boxes into L2 this many 64-deep k-blocks ahead of the loads (0 = off)
-L2_PREFETCH_DEFAULT = int(__import__('os').environ.get('CCFUSER_L2_PREFETCH', '0'))
+# 1: the two dedicated dispatch warps of every CTA push the rows (next to the MMA and epilogue warps); 0: the epilogue
+# warps push them before their first tile
+COMM_WARPS_DEFAULT = int(__import__('os').environ.get('CCFUSER_COMM_WARPS', '1'))
 
 
 def _is_fp16(t: torch.Tensor) -> int:
@@ -131,7 +132,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
            act=N.ACT_NONE, out_fp32=False, tile_flags=None, local_begin=None, local_rows=None, row_src=None, row_gate=None,
            peer_comb=None, peer_done=None, world=1, send_finish=0, max_slots=0,
            dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, total_index=-1, two_cta=None, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
-           workspace: Optional[Workspace] = None, l2_prefetch: Optional[int] = None):
+           workspace: Optional[Workspace] = None, comm_warps: Optional[int] = None):
     """Fill a CcfGemmLaunch and launch on the current stream. a0/b0 are 2-D contiguous views."""
     lib = N.load()
     ws = workspace or Workspace.get(a0.device)
@@ -161,7 +162,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     g.b_group_rows, g.act, g.fp16, g.out_fp32 = int(b_group_rows), int(act), _is_fp16(a0), int(bool(out_fp32))
     g.world, g.send_finish, g.n_comm_ctas, g.max_slots = int(world), int(send_finish), int(n_comm_ctas), int(max_slots)
     g.total_index = int(total_index)
-    g.l2_prefetch = int(L2_PREFETCH_DEFAULT if l2_prefetch is None else l2_prefetch)
+    g.comm_warps = int(COMM_WARPS_DEFAULT if comm_warps is None else comm_warps)
     if dispatch is not None:
         g.disp = dispatch
         g.disp.work_counter = ws.sched.data_ptr() + 4 * Workspace.DISPATCH_WORK

@@ -61,14 +61,27 @@ class _FusedRouter(torch.autograd.Function):
         need_b = ctx.has_bias and ctx.needs_input_grad[2]
         gw = torch.zeros_like(w) if gw is None else gw.contiguous().float()
         if glogits is None:
-            # only the k selected columns carry a gradient: no [T, E] matrix, no GEMM
+            # only the k selected columns carry a gradient: dx needs no [T, E] matrix and no GEMM
             dx = torch.empty_like(x) if need_x else None
-            dw32 = torch.zeros(e, d, dtype=torch.float32, device=x.device) if (need_w or need_b) else None
-            db32 = torch.zeros(e, dtype=torch.float32, device=x.device) if need_b else None
-            N.check(lib.ccf_router_bwd(idx.data_ptr(), w.data_ptr(), gw.data_ptr(), wt.data_ptr(), x.data_ptr(), N.ptr(dx),
-                                       N.ptr(dw32), N.ptr(db32), t, d, e, k, fp16, N.stream_ptr()), "ccf_router_bwd")
-            N.count(int(need_x) + int(dw32 is not None))
-            return (dx, dw32.to(wt.dtype) if need_w else None, db32.to(wt.dtype) if need_b else None, None, None, None)
+            big = t >= 4096 and (need_w or need_b)
+            dw32 = torch.zeros(e, d, dtype=torch.float32, device=x.device) if ((need_w or need_b) and not big) else None
+            db32 = torch.zeros(e, dtype=torch.float32, device=x.device) if (need_b and not big) else None
+            if dx is not None or dw32 is not None:
+                N.check(lib.ccf_router_bwd(idx.data_ptr(), w.data_ptr(), gw.data_ptr(), wt.data_ptr(), x.data_ptr(), N.ptr(dx),
+                                           N.ptr(dw32), N.ptr(db32), t, d, e, k, fp16, N.stream_ptr()), "ccf_router_bwd")
+                N.count(int(need_x) + int(dw32 is not None))
+            if not big:
+                return (dx, dw32.to(wt.dtype) if need_w else None, db32.to(wt.dtype) if need_b else None, None, None, None)
+            # many tokens: the scatter-add of token rows into E weight rows is a [E, T] x [T, d] product with a sparse
+            # left factor; on the tensor cores (own grouped GEMM, reduction over the tokens) it beats atomics
+            ep = 128 if e <= 128 else 256
+            dlp = torch.zeros(t, ep, dtype=x.dtype, device=x.device)
+            N.check(lib.ccf_topk_softmax_bwd(idx.data_ptr(), w.data_ptr(), gw.data_ptr(), t, ep, k, dlp.data_ptr(), fp16, 0,
+                                             N.stream_ptr()), "ccf_topk_softmax_bwd")
+            N.count(1)
+            dw = _dw_by_gemm(dlp, x, e, d, wt.dtype) if need_w else None
+            db = dlp[:, :e].float().sum(0).to(wt.dtype) if need_b else None
+            return dx, dw, db, None, None, None
         # dense gradient of the logits (auxiliary losses) + the selected columns' part, then two products on the
         # tcgen05 grouped GEMM: [T, Ep] x [Ep, d] and [Ep, T] x [T, d], Ep = E padded to the 128-row tile
         dl = torch.zeros(t, e, dtype=torch.float32, device=x.device)
@@ -86,12 +99,20 @@ class _FusedRouter(torch.autograd.Function):
             G.launch(a0=dlp, b0=wt, a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, k=ep, group_base=gb,
                      group_rows=gr, num_groups=1, b_group_rows=0, out0=dx)
         if need_w:
-            dwp = torch.empty(ep, d, dtype=torch.float32, device=x.device)
-            G.launch(a0=dlp, b0=x, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True, m_per_group=ep,
-                     group_base=gb, group_rows=gr, num_groups=1, out0=dwp, ld_out=d, out_fp32=True)
-            dw = dwp[:e].to(wt.dtype)
+            dw = _dw_by_gemm(dlp, x, e, d, wt.dtype)
         db = dl.sum(0).to(wt.dtype) if need_b else None
         return dx, dw, db, None, None, None
+
+
+def _dw_by_gemm(dlp: torch.Tensor, x: torch.Tensor, e: int, d: int, dtype) -> torch.Tensor:
+    """dW [e, d] = dlp[:, :e]^T x on the library's k-grouped GEMM (one group whose reduction runs over the tokens);
+    ``dlp [T, 128 or 256]`` is the logits' gradient, zero-padded to the kernel's tile height."""
+    t, ep = dlp.shape
+    gb, gr = G.single_group(t, x.device)
+    dwp = torch.empty(ep, d, dtype=torch.float32, device=x.device)
+    G.launch(a0=dlp, b0=x, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True, m_per_group=ep,
+             group_base=gb, group_rows=gr, num_groups=1, out0=dwp, ld_out=d, out_fp32=True)
+    return dwp[:e].to(dtype)
 
 
 def fused_router(x: torch.Tensor, weight: torch.Tensor, bias, k: int, want_logits: bool = False, path: int = 0):

@@ -20,6 +20,7 @@ run library_router     CCFUSER_FUSED_ROUTER=0    -- tests/test_gpu_fused.py test
 run one_cta_kernel     CCFUSER_TWO_CTA=0         -- tests/test_gpu_fused.py tests/test_gpu_bench_shapes.py -x
 run canary             CCFUSER_CANARY=1          -- tests/test_gpu_fused.py -x -k "forward_backward or module_api"
 run few_comm_ctas      CCFUSER_COMM_CTAS=16      -- tests/test_gpu_fused.py -x -k "forward_backward or module_api"
+run epilogue_warps_push CCFUSER_COMM_WARPS=0     -- tests/test_gpu_fused.py tests/test_gpu_bench_shapes.py -x
 if [ "$(python -c 'import torch; print(torch.cuda.device_count())')" -ge 2 ]; then
   run python_launch_path_2gpu CCFUSER_NATIVE_RUNTIME=0 -- tests/test_gpu_multi.py -x -k "fused_layer_multi_gpu and 2"
 fi

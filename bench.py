@@ -34,6 +34,9 @@ def parse():
                     help="1 (default): after the warm-up, every MoE layer moves experts between GPUs to the placement planned "
                          "from its observed routing counts, if that lowers the busiest GPU's load by at least 5 %% (same "
                          "model function; outside the timed region; needs more than one GPU). 0: keep the initial placement")
+    ap.add_argument("--fuse-expert-sgd", type=int, default=1,
+                    help="1 (default): on one GPU the expert weights' SGD update runs in the epilogue of the weight-gradient "
+                         "GEMMs (MoELayer.fuse_sgd; needs ep_size 1). 0: separate optimizer pass")
     ap.add_argument("--no-baseline", action="store_true",
                     help="skip the repository's own baseline arm (same model on the all_to_all_single + library "
                          "grouped-GEMM backend), against which vs_baseline is reported")
@@ -243,8 +246,11 @@ def run_arm(torch, dist, args, backend, steps, warmup, rank, local_rank, world, 
     c = GPTMoEConfig(n_layer=args.layers, ep_size=world, backend=backend, max_tokens=args.batch * seq, seq_len=seq,
                      recv_factor=4.0)
     model = GPTMoE(c, device=dev)
-    trainer = TrainStep(model, lr=1e-4, optimizer="sgd")
     fused = backend == "fused"
+    # one GPU holds all 64 experts of every MoE layer: the step is bound by expert-weight traffic there, and the fused
+    # backend applies the experts' SGD update inside the weight-gradient GEMMs (same update, no gradient round trip)
+    fuse_sgd = fused and world == 1 and bool(args.fuse_expert_sgd)
+    trainer = TrainStep(model, lr=1e-4, optimizer="sgd", fuse_expert_sgd=fuse_sgd)
 
     def sync():
         if world > 1:
@@ -306,7 +312,7 @@ def run_arm(torch, dist, args, backend, steps, warmup, rank, local_rank, world, 
     rec = {"backend": backend, "ms": float(t[0]), "ms_e2e": float(t[1]), "steps": steps, "launches": launches,
            "clocks": clocks, "first_loss": first_loss, "loss": float(loss.detach()), "last_loss": last, "moved": moved,
            "imbalance_before": imbalance_before, "imbalance": None, "overflow": None,
-           "flops_per_token": c.flops_per_token(), "vocab": c.vocab_size}
+           "flops_per_token": c.flops_per_token(), "vocab": c.vocab_size, "fuse_sgd": fuse_sgd}
     if fused:
         from ccfuser_b200 import MoEOverflow
         for m in model.moe_layers():
@@ -407,6 +413,8 @@ def main():
                        "optimizer": "sgd", "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2",
                        "loss": round(ours["loss"], 4), "first_loss": ours["first_loss"], "capacity_factor": None,
                        "mean_expert_grads": False,
+                       "expert_sgd": ("applied in the weight-gradient GEMM epilogue (MoELayer.fuse_sgd)" if ours.get("fuse_sgd")
+                                      else "separate optimizer pass"),
                        "expert_placement": ("re-planned once from the routing counts of the last warm-up step, outside the "
                                             "timed region" if (args.rebalance and world > 1 and args.impl == "ours") else "initial"),
                        "max_rank_load_over_balanced": ours["imbalance"],

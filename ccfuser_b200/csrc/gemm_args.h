@@ -99,9 +99,9 @@ struct CcfGemmArgs {
   int max_slots;            // COMBINE: rows of a combine buffer (bounds check)
   int trace_tiles;          // tiles per CTA recorded in `trace`
   int total_index;          // element of tile_flags that counts all arrived rows (-1 = none); lets late tiles skip their flag
-  int pad1;
+  float sgd_lr;             // EPI_STORE, non-zero: out0 holds parameters and is updated in place, out0 -= lr * (acc + wd * out0)
   int comm_warps;           // 1: the CTA's two dedicated warps run the dispatch role; 0: its epilogue warps do, before their first tile
-  int pad2;
+  float sgd_wd;             // weight decay of that update
   CcfDispatchArgs disp;
 };
 

@@ -186,6 +186,9 @@ __device__ __forceinline__ void staged_store64(uint32_t stage, int lane, const u
   __syncwarp();
 }
 
+// kReadOnly = false: the rows are rewritten by this kernel (in-place update), so they are read with ordinary loads
+// instead of through the read-only path.
+template <bool kReadOnly = true>
 __device__ __forceinline__ void staged_load64(uint32_t stage, int lane, uint32_t (&w)[16],
                                               unsigned long long row_ptr) {
 #pragma unroll
@@ -193,7 +196,10 @@ __device__ __forceinline__ void staged_load64(uint32_t stage, int lane, uint32_t
     const int row = 8 * i + (lane >> 2), piece = lane & 3;
     const unsigned long long p = __shfl_sync(0xffffffffu, row_ptr, row);
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (p != 0ull) v = __ldg(reinterpret_cast<const uint4*>(p + piece * 16));
+    if (p != 0ull) {
+      if constexpr (kReadOnly) v = __ldg(reinterpret_cast<const uint4*>(p + piece * 16));
+      else v = *reinterpret_cast<const uint4*>(p + piece * 16);
+    }
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + stage_off(row, piece)), "r"(v.x), "r"(v.y),
                  "r"(v.z), "r"(v.w)
                  : "memory");
@@ -353,6 +359,17 @@ __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, co
         if (has_b0) add_bias_raw(f, bcur, fp16);
         if (args.out_fp32) {
           if (valid) store32_f32(reinterpret_cast<float*>(args.out0) + orow * args.ld_out + n, f);
+        } else if (args.sgd_lr != 0.f) {
+          // the accumulator is a weight gradient and out0 the weights themselves: plain SGD applied here saves writing
+          // the gradient, and the optimizer's pass that would read it and the weights again
+          staged_load64<false>(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);
+          const float lr = args.sgd_lr, wd = args.sgd_wd;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float2 p = unpack2(w[j], fp16);
+            w[j] = pack2(p.x - lr * fmaf(wd, p.x, f[2 * j]), p.y - lr * fmaf(wd, p.y, f[2 * j + 1]), fp16);
+          }
+          staged_store64(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);
         } else {
           pack32(f, w, fp16);
           staged_store64(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);

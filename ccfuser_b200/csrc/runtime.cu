@@ -162,6 +162,10 @@ int ccf_layer_forward(const CcfLayer* L, const void* x, const int* idx, const fl
   Dry* dry = dry_gemms != nullptr ? &dry_state : nullptr;
   const int d = L->d_model, f = L->d_ffn, e_loc = L->e_loc;
   int rc = 0;
+  // An expert that receives about one 256-row pair tile's worth of rows fills most second tiles with padding: such
+  // calls run on 128-row tiles (one-CTA kernel).
+  const long long rows_per_expert = static_cast<long long>(tokens) * L->top_k * L->world / (L->e_total > 0 ? L->e_total : 1);
+  const int row_two_cta = rows_per_expert > L->small_rows ? L->two_cta : 0;
   if (dry == nullptr) {
     if (L->device >= 0 && cudaSetDevice(L->device) != cudaSuccess) return -7;
     // 1. positions, kept counts, destination order of this rank's slots
@@ -216,6 +220,7 @@ int ccf_layer_forward(const CcfLayer* L, const void* x, const int* idx, const fl
       g.args.act = L->act;
     }
     set_dispatch(g, L, x, idx, gate_w, tokens, capacity, 0, nullptr);
+    g.two_cta = row_two_cta;
     if ((rc = issue(g, dry, stream))) return rc;
     if ((rc = zero_tile_flags(L, dry, stream))) return rc;
   }
@@ -231,6 +236,7 @@ int ccf_layer_forward(const CcfLayer* L, const void* x, const int* idx, const fl
     g.args.bias0 = L->b2;
     g.args.ld_out = d;
     set_combine(g, L, L->peer_comb, L->row_gate);
+    g.two_cta = row_two_cta;
     if ((rc = issue(g, dry, stream))) return rc;
   }
   // 5. wait for every owner, sum the k slots of each token
@@ -251,6 +257,9 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
   // decides: there the one-CTA kernel is faster than CTA pairs.
   const long long rows_per_expert = static_cast<long long>(tokens) * L->top_k * L->world / (L->e_total > 0 ? L->e_total : 1);
   const int wgrad_two_cta = rows_per_expert > 512 ? L->two_cta : 0;
+  const int row_two_cta = rows_per_expert > L->small_rows ? L->two_cta : 0;
+  const bool sgd = G->sgd_lr != 0.f;
+  if (sgd && L->world != 1) return -2;   // with peers the input-gradient GEMM has to stay the last owner-side kernel
   // 1 + 2. push g * dy rows + dgrad-2 with the activation derivative
   {
     CcfGemmLaunch g = base_launch(L);
@@ -270,6 +279,7 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
       g.args.act = L->act;
     }
     set_dispatch(g, L, dy, idx, gate_w, tokens, capacity, 1, G->dgate);
+    g.two_cta = row_two_cta;
     if ((rc = issue(g, dry, stream))) return rc;
     if ((rc = zero_tile_flags(L, dry, stream))) return rc;
   }
@@ -282,7 +292,9 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
     g.kgroup = 1;
     g.args.n = f;
     g.args.m_per_group = d;
-    g.args.out0 = G->dw2;
+    g.args.out0 = sgd ? const_cast<void*>(L->w2) : G->dw2;   // dgrad-2 above was the last reader of the old w2
+    g.args.sgd_lr = G->sgd_lr;
+    g.args.sgd_wd = G->sgd_wd;
     g.args.ld_out = f;
     g.two_cta = wgrad_two_cta;
     if ((rc = issue(g, dry, stream))) return rc;
@@ -300,29 +312,16 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
     g.args.n = d;
     g.args.m_per_group = f;
     g.args.out0 = out;
+    g.args.sgd_lr = G->sgd_lr;
+    g.args.sgd_wd = G->sgd_wd;
     g.args.ld_out = d;
     g.two_cta = wgrad_two_cta;
     return issue(g, dry, stream);
   };
-  if (L->swiglu) {
-    if ((rc = wgrad1(G->dh, G->dwg))) return rc;
-    if ((rc = wgrad1(G->dh2, G->dw1))) return rc;
-    if (dry == nullptr) {
-      if (G->db1 != nullptr &&
-          (rc = ccf_colsum_grouped(G->dh2, f, f, e_loc, L->group_base, L->group_rows, G->db1, L->fp16, stream)))
-        return rc;
-      if (G->dbg != nullptr &&
-          (rc = ccf_colsum_grouped(G->dh, f, f, e_loc, L->group_base, L->group_rows, G->dbg, L->fp16, stream)))
-        return rc;
-    }
-  } else {
-    if ((rc = wgrad1(G->dh, G->dw1))) return rc;
-    if (dry == nullptr && G->db1 != nullptr &&
-        (rc = ccf_colsum_grouped(G->dh, f, f, e_loc, L->group_base, L->group_rows, G->db1, L->fp16, stream)))
-      return rc;
-  }
-  // 5. dgrad-1 + combine: dx rows go back to the ranks the tokens came from
-  {
+  // 5. dgrad-1 + combine: dx rows go back to the ranks the tokens came from. Issued after the weight gradients (its
+  // finish token then tells the sources that every buffer of this call is free), except when those update w1 / wg in
+  // place: then it must read them first.
+  auto dgrad1 = [&]() {
     CcfGemmLaunch g = base_launch(L);
     set_a(g, G->dh, L->max_rows, f, kMajK);
     g.epi = CCF_EPI_COMBINE;
@@ -339,8 +338,28 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
       set_b(g, L->w1, static_cast<long long>(e_loc) * f, d, kMajMN);
     }
     set_combine(g, L, L->peer_gcomb, nullptr);
-    if ((rc = issue(g, dry, stream))) return rc;
+    g.two_cta = row_two_cta;
+    return issue(g, dry, stream);
+  };
+  if (sgd && (rc = dgrad1())) return rc;
+  if (L->swiglu) {
+    if ((rc = wgrad1(G->dh, sgd ? const_cast<void*>(L->wg) : G->dwg))) return rc;
+    if ((rc = wgrad1(G->dh2, sgd ? const_cast<void*>(L->w1) : G->dw1))) return rc;
+    if (dry == nullptr) {
+      if (G->db1 != nullptr &&
+          (rc = ccf_colsum_grouped(G->dh2, f, f, e_loc, L->group_base, L->group_rows, G->db1, L->fp16, stream)))
+        return rc;
+      if (G->dbg != nullptr &&
+          (rc = ccf_colsum_grouped(G->dh, f, f, e_loc, L->group_base, L->group_rows, G->dbg, L->fp16, stream)))
+        return rc;
+    }
+  } else {
+    if ((rc = wgrad1(G->dh, sgd ? const_cast<void*>(L->w1) : G->dw1))) return rc;
+    if (dry == nullptr && G->db1 != nullptr &&
+        (rc = ccf_colsum_grouped(G->dh, f, f, e_loc, L->group_base, L->group_rows, G->db1, L->fp16, stream)))
+      return rc;
   }
+  if (!sgd && (rc = dgrad1())) return rc;
   rc = wait_and_reduce(L, L->gcomb, G->dx, tokens, dry, stream);
   if (dry_count != nullptr) *dry_count = dry_state.n;
   return rc;

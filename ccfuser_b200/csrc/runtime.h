@@ -69,7 +69,7 @@ struct CcfLayer {
   int device;       // CUDA device (-1: leave the calling thread's device alone)
   int pad0;
   int comm_warps;   // 1: dedicated dispatch warps carry the row push, 0: the epilogue warps do
-  int pad1;
+  int small_rows;   // calls that expect at most this many rows per expert use the one-CTA kernel (128-row tiles)
 };
 
 // Per-call tensors of the backward pass (all allocated by the caller; null where the layer has no such parameter).
@@ -84,6 +84,11 @@ struct CcfLayerGrads {
   void* dw2;
   void* db2;
   void* dx;         // [tokens, d]
+  // Non-zero sgd_lr (single-rank layers only): the weight-gradient GEMMs apply plain SGD to w1 / wg / w2 in their
+  // epilogue (w -= lr * (dw + wd * w)) instead of writing dw1 / dwg / dw2, and the input-gradient GEMM that still needs
+  // the old w1 / wg runs before them.
+  float sgd_lr;
+  float sgd_wd;
 };
 
 extern "C" {

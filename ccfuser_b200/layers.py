@@ -58,6 +58,7 @@ class MoELayer(nn.Module):
                                   dtype=config.dtype, device=device)
         self._fused = None
         self._shadow_fused = None
+        self._sgd = None
         self.last_stats = {}
 
     # ---- backend selection -------------------------------------------------------------------
@@ -71,6 +72,7 @@ class MoELayer(nn.Module):
         if self._fused is None:
             from .ops.fused import FusedMoE  # needs the CUDA library
             self._fused = FusedMoE(self)
+            self._fused.sgd = self._sgd
         return self._fused
 
     # ---- forward -----------------------------------------------------------------------------
@@ -144,6 +146,27 @@ class MoELayer(nn.Module):
                 return identity
         rebalance_experts(self, placement, optimizer)
         return list(placement)
+
+    def fuse_sgd(self, lr: Optional[float], weight_decay: float = 0.0):
+        """Apply plain SGD to the expert weight matrices inside the backward pass: the weight-gradient GEMMs' epilogue
+        writes ``w - lr * (dw + weight_decay * w)`` over ``w`` instead of storing ``dw``, so the gradient is never
+        written and the optimizer never reads it and the weights again (with many experts per GPU that traffic is a
+        large part of a step). The matrices' ``.grad`` stays ``None`` (an optimizer skips them); biases and the router
+        keep the ordinary path. Same update as ``torch.optim.SGD`` without momentum, computed from the fp32 accumulator.
+        For the fused backend on a single-rank layer (``ep_size == 1``); not compatible with gradient accumulation,
+        clipping or anything else that needs the expert weight gradients. ``lr=None`` switches it off. Call it again
+        whenever the learning rate changes."""
+        if lr is None:
+            if self._fused is not None:
+                self._fused.sgd = None
+            self._sgd = None
+            return
+        if self.config.ep_size != 1:
+            raise ValueError("fuse_sgd needs ep_size == 1: with peers the input-gradient GEMM must stay the last kernel of "
+                             "a backward pass, after the weight gradients, and it reads the weights they would overwrite")
+        self._sgd = (float(lr), float(weight_decay))
+        if self._fused is not None:
+            self._fused.sgd = self._sgd
 
     def routing_stats(self):
         """Statistics of the last fused forward call as device tensors (see FusedMoE.routing_stats)."""

@@ -51,7 +51,7 @@ class GemmArgs(C.Structure):
         ("n", C.c_int), ("k", C.c_int), ("num_groups", C.c_int), ("m_per_group", C.c_int), ("kseg", C.c_int),
         ("b_group_rows", C.c_int), ("act", C.c_int), ("fp16", C.c_int), ("out_fp32", C.c_int), ("world", C.c_int),
         ("send_finish", C.c_int), ("n_comm_ctas", C.c_int), ("max_slots", C.c_int), ("trace_tiles", C.c_int),
-        ("total_index", C.c_int), ("pad1", C.c_int), ("comm_warps", C.c_int), ("pad2", C.c_int),
+        ("total_index", C.c_int), ("sgd_lr", C.c_float), ("comm_warps", C.c_int), ("sgd_wd", C.c_float),
         ("disp", DispatchArgs),
     ]
 
@@ -104,14 +104,14 @@ class Layer(C.Structure):
         ("d_model", C.c_int), ("d_ffn", C.c_int), ("e_total", C.c_int), ("e_loc", C.c_int), ("top_k", C.c_int),
         ("world", C.c_int), ("rank", C.c_int), ("act", C.c_int), ("swiglu", C.c_int), ("fp16", C.c_int),
         ("max_rows", C.c_int), ("max_slots", C.c_int), ("n_comm_ctas", C.c_int), ("two_cta", C.c_int),
-        ("device", C.c_int), ("pad0", C.c_int), ("comm_warps", C.c_int), ("pad1", C.c_int),
+        ("device", C.c_int), ("pad0", C.c_int), ("comm_warps", C.c_int), ("small_rows", C.c_int),
     ]
 
 
 class LayerGrads(C.Structure):
     """Mirror of CcfLayerGrads (csrc/runtime.h)."""
     _fields_ = [("dgate", _vp), ("dh", _vp), ("dh2", _vp), ("dw1", _vp), ("db1", _vp), ("dwg", _vp), ("dbg", _vp),
-                ("dw2", _vp), ("db2", _vp), ("dx", _vp)]
+                ("dw2", _vp), ("db2", _vp), ("dx", _vp), ("sgd_lr", C.c_float), ("sgd_wd", C.c_float)]
 
 
 _lib = None

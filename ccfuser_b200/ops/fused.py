@@ -269,6 +269,8 @@ class FusedMoE:
         self.native_runtime = bool(env_flag("NATIVE_RUNTIME", 1))
         self._desc = None
         self._desc_key = None
+        self.sgd = None         # (lr, weight decay): expert weights are updated by the weight-gradient GEMMs (fuse_sgd)
+        self._call_two_cta = None   # kernel choice of the current call's row-grouped launches (_row_two_cta)
         self._owed = None       # weak reference to the autograd node whose backward still needs this layer's buffers
 
     # ------------------------------------------------------------------------------------------
@@ -366,6 +368,7 @@ class FusedMoE:
         L.n_comm_ctas = min(int(cc.n_comm), 1 << 30)
         L.two_cta = int(G.TWO_CTA_DEFAULT)
         L.comm_warps = int(G.COMM_WARPS_DEFAULT)
+        L.small_rows = int(G.SMALL_ROWS_DEFAULT)
         L.device = self.device.index if (self.device.type == "cuda" and self.device.index is not None) else (
             torch.cuda.current_device() if self.device.type == "cuda" else -1)
         self._desc, self._desc_key = L, key
@@ -440,6 +443,12 @@ class FusedMoE:
         a.total_index = self.max_rows // TILE  # last element of tile_flags: all rows arrived on that rank
         return a
 
+    def _row_two_cta(self, tokens: int):
+        """Kernel choice of the row-grouped launches of a call with ``tokens`` tokens per rank: None (the default, CTA
+        pairs) or False (one-CTA kernel, 128-row tiles) when an expert expects at most ``CCFUSER_SMALL_ROWS`` rows."""
+        rows = tokens * self.cfg.top_k * self.world // max(1, self.cfg.num_experts)
+        return None if rows > G.SMALL_ROWS_DEFAULT else False
+
     def _combine_kw(self, peer_comb, row_gate):
         ctx = self.ctx
         done = [p + 4 * self.rank for p in ctx.peer("done")]
@@ -496,7 +505,9 @@ class FusedMoE:
         disp = self._dispatch_args(x, t, idx, gate_w, backward=False)
         common = dict(group_base=self.group_base, group_rows=self.group_rows, num_groups=e_loc, tile_flags=cc.tile_flags,
                       dispatch=disp, n_comm_ctas=cc.n_comm, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace,
-                      total_index=self.max_rows // TILE, local_begin=self.local_begin, local_rows=self.local_rows)
+                      total_index=self.max_rows // TILE, local_begin=self.local_begin, local_rows=self.local_rows,
+                      two_cta=self._row_two_cta(t))
+        self._call_two_cta = common["two_cta"]
         if cfg.activation == "swiglu":
             G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), b1=wg.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K,
                      epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre if save_pre else None,
@@ -513,7 +524,7 @@ class FusedMoE:
         d, f, e_loc = cfg.d_model, cfg.d_ffn, cfg.experts_per_rank
         G.launch(a0=self.h_act, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_COMBINE, n=d, k=f,
                  group_base=self.group_base, group_rows=self.group_rows, num_groups=e_loc, b_group_rows=d, bias0=b2,
-                 ld_out=d, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace,
+                 ld_out=d, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace, two_cta=self._call_two_cta,
                  **self._combine_kw(self.buf.peer_ptrs(self.off_comb), cc.row_gate))
 
     def stage_reduce(self, tokens: int, out: torch.Tensor):
@@ -637,6 +648,9 @@ class _FusedMoEFn(torch.autograd.Function):
         dy = dy.contiguous()
         dgate = torch.zeros(t * cfg.top_k, dtype=torch.float32, device=dy.device)  # dropped slots keep 0
         swiglu = cfg.activation == "swiglu"
+        # fuse_sgd: the weight-gradient GEMMs update the weights in place (single-rank layers); no weight gradient is
+        # returned, and dgrad-1, which still needs the old w1 / wg, moves in front of them
+        sgd = fm.sgd if (fm.sgd is not None and fm.world == 1 and fm.sgd[0] != 0.0) else None
         if fm.native_runtime:
             has_b1, has_bg, has_b2 = ctx.has_bias
             mk = lambda like: torch.empty_like(like)                       # noqa: E731
@@ -644,11 +658,13 @@ class _FusedMoEFn(torch.autograd.Function):
             g = N.LayerGrads()
             dh = torch.empty(fm.max_rows, f, dtype=cfg.dtype, device=dy.device)
             dh2 = torch.empty_like(dh) if swiglu else None
-            dw1, dw2, dwg = mk(w1), mk(w2), (mk(wg) if swiglu else None)
+            dw1, dw2, dwg = (None, None, None) if sgd is not None else (mk(w1), mk(w2), (mk(wg) if swiglu else None))
             db1, db2, dbg = (bias(f) if has_b1 else None), (bias(d) if has_b2 else None), (bias(f) if has_bg else None)
             dx = torch.empty(t, d, dtype=dy.dtype, device=dy.device)
             g.dgate, g.dh, g.dh2 = dgate.data_ptr(), dh.data_ptr(), N.ptr(dh2)
             g.dw1, g.db1, g.dwg, g.dbg, g.dw2, g.db2, g.dx = (N.ptr(v) for v in (dw1, db1, dwg, dbg, dw2, db2, dx))
+            if sgd is not None:
+                g.sgd_lr, g.sgd_wd = float(sgd[0]), float(sgd[1])
             N.check(lib.ccf_layer_backward(C.byref(fm.native_desc()), dy.data_ptr(), idx.data_ptr(), gate_w.data_ptr(),
                                            C.byref(g), t, cfg.capacity(t), st, None, 0, None), "ccf_layer_backward")
             # kernels: dy dispatch + dgrad-2, wgrad-2, wgrad-1 (two for SwiGLU), dgrad-1 + combine, wait, reduce, column sums
@@ -662,24 +678,25 @@ class _FusedMoEFn(torch.autograd.Function):
                       workspace=cc.ws)
         dh = torch.empty(fm.max_rows, f, dtype=cfg.dtype, device=dy.device)
         dh2 = torch.empty_like(dh) if swiglu else None
+        rt = fm._row_two_cta(t)
         if swiglu:
             G.launch(a0=cc.grecv, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DSWIGLU, n=f, k=d,
                      b_group_rows=d, out0=dh, out1=dh2, aux0=fm.h_pre, aux1=fm.h_pre2, tile_flags=cc.tile_flags,
                      dispatch=disp, n_comm_ctas=cc.n_comm, total_index=fm.max_rows // TILE, local_begin=fm.local_begin,
-                     local_rows=fm.local_rows, **common)
+                     local_rows=fm.local_rows, two_cta=rt, **common)
         else:
             G.launch(a0=cc.grecv, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_DACT, n=f, k=d,
                      b_group_rows=d, out0=dh, aux0=fm.h_pre, act=N.ACT_CODE[cfg.activation], tile_flags=cc.tile_flags,
                      dispatch=disp, n_comm_ctas=cc.n_comm, total_index=fm.max_rows // TILE, local_begin=fm.local_begin,
-                     local_rows=fm.local_rows, **common)
+                     local_rows=fm.local_rows, two_cta=rt, **common)
         cc.tile_flags.zero_()
         # 3. wgrad-2: dW2[e] = (g dy)^T h_act   [d, f]
         # With few rows per expert the reduction is only a handful of k-blocks and the per-tile latency chain decides:
         # there the one-CTA kernel (shorter barrier round trips, dynamic scheduler) is ~25 % faster than CTA pairs.
         wgrad_two_cta = None if (t * cfg.top_k * fm.world) // max(1, cfg.num_experts) > 512 else False
-        dw2 = torch.empty_like(w2)
+        dw2 = torch.empty_like(w2) if sgd is None else None
         G.launch(a0=cc.grecv, b0=fm.h_act, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True,
-                 m_per_group=d, out0=dw2, ld_out=f, two_cta=wgrad_two_cta, **common)
+                 m_per_group=d, out0=dw2 if sgd is None else w2, ld_out=f, two_cta=wgrad_two_cta, sgd=sgd, **common)
         has_b1, has_bg, has_b2 = ctx.has_bias
 
         def colsum(src, n):
@@ -690,30 +707,36 @@ class _FusedMoEFn(torch.autograd.Function):
             return out
 
         db2 = colsum(cc.grecv, d) if has_b2 else None
+        # 5 (defined here, issued below). dgrad-1 + combine: dx rows go back to the ranks the tokens came from
+        def dgrad1():
+            ck = fm._combine_kw(cc.peer("gcomb"), None)
+            if swiglu:
+                G.launch(a0=dh, a1=dh2, b0=wg.view(e_loc * f, d), b1=w1.view(e_loc * f, d), a_major=N.MAJ_K,
+                         b_major=N.MAJ_MN, epi=N.EPI_COMBINE, n=d, k=f, kseg=2, b_group_rows=f, ld_out=d, two_cta=rt,
+                         **common, **ck)
+            else:
+                G.launch(a0=dh, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_COMBINE, n=d, k=f,
+                         b_group_rows=f, ld_out=d, two_cta=rt, **common, **ck)
+
+        if sgd is not None:
+            dgrad1()            # reads w1 / wg before the weight-gradient GEMMs below overwrite them
         # 4. wgrad-1: dW1[e] = dh^T x_e   [f, d]
-        dw1 = torch.empty_like(w1)
+        dw1 = torch.empty_like(w1) if sgd is None else None
         dwg = dbg = None
+        wkw = dict(b0=fm.xrecv, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True, m_per_group=f, ld_out=d,
+                   two_cta=wgrad_two_cta, sgd=sgd, **common)
         if swiglu:
             # dh = d(gate pre-activation), dh2 = d(up pre-activation)
-            dwg = torch.empty_like(wg)
-            G.launch(a0=dh, b0=fm.xrecv, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True,
-                     m_per_group=f, out0=dwg, ld_out=d, two_cta=wgrad_two_cta, **common)
-            G.launch(a0=dh2, b0=fm.xrecv, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True,
-                     m_per_group=f, out0=dw1, ld_out=d, two_cta=wgrad_two_cta, **common)
+            dwg = torch.empty_like(wg) if sgd is None else None
+            G.launch(a0=dh, out0=dwg if sgd is None else wg, **wkw)
+            G.launch(a0=dh2, out0=dw1 if sgd is None else w1, **wkw)
             db1 = colsum(dh2, f) if has_b1 else None
             dbg = colsum(dh, f) if has_bg else None
         else:
-            G.launch(a0=dh, b0=fm.xrecv, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True,
-                     m_per_group=f, out0=dw1, ld_out=d, two_cta=wgrad_two_cta, **common)
+            G.launch(a0=dh, out0=dw1 if sgd is None else w1, **wkw)
             db1 = colsum(dh, f) if has_b1 else None
-        # 5. dgrad-1 + combine: dx rows go back to the ranks the tokens came from
-        ck = fm._combine_kw(cc.peer("gcomb"), None)
-        if swiglu:
-            G.launch(a0=dh, a1=dh2, b0=wg.view(e_loc * f, d), b1=w1.view(e_loc * f, d), a_major=N.MAJ_K,
-                     b_major=N.MAJ_MN, epi=N.EPI_COMBINE, n=d, k=f, kseg=2, b_group_rows=f, ld_out=d, **common, **ck)
-        else:
-            G.launch(a0=dh, b0=w1.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_COMBINE, n=d, k=f,
-                     b_group_rows=f, ld_out=d, **common, **ck)
+        if sgd is None:
+            dgrad1()
         dx = torch.empty(t, d, dtype=dy.dtype, device=dy.device)
         fm._wait_and_reduce(cc.gcomb, t, G.combine_units(d), dx)
         if fm.check_every_call:

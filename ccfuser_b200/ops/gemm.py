@@ -116,6 +116,9 @@ TWO_CTA_DEFAULT = bool(int(__import__('os').environ.get('CCFUSER_TWO_CTA', '1'))
 # 1: the two dedicated dispatch warps of every CTA push the rows (next to the MMA and epilogue warps); 0: the epilogue
 # warps push them before their first tile
 COMM_WARPS_DEFAULT = int(__import__('os').environ.get('CCFUSER_COMM_WARPS', '1'))
+# calls that expect at most this many rows per expert run on the one-CTA kernel's 128-row tiles: around one 256-row pair
+# tile per expert most second pair tiles would be padding
+SMALL_ROWS_DEFAULT = int(__import__('os').environ.get('CCFUSER_SMALL_ROWS', '320'))
 
 
 def _is_fp16(t: torch.Tensor) -> int:
@@ -132,7 +135,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
            act=N.ACT_NONE, out_fp32=False, tile_flags=None, local_begin=None, local_rows=None, row_src=None, row_gate=None,
            peer_comb=None, peer_done=None, world=1, send_finish=0, max_slots=0,
            dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, total_index=-1, two_cta=None, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
-           workspace: Optional[Workspace] = None, comm_warps: Optional[int] = None):
+           workspace: Optional[Workspace] = None, comm_warps: Optional[int] = None, sgd=None):
     """Fill a CcfGemmLaunch and launch on the current stream. a0/b0 are 2-D contiguous views."""
     lib = N.load()
     ws = workspace or Workspace.get(a0.device)
@@ -163,6 +166,8 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     g.world, g.send_finish, g.n_comm_ctas, g.max_slots = int(world), int(send_finish), int(n_comm_ctas), int(max_slots)
     g.total_index = int(total_index)
     g.comm_warps = int(COMM_WARPS_DEFAULT if comm_warps is None else comm_warps)
+    if sgd is not None:     # (lr, weight decay): EPI_STORE updates out0 in place instead of storing the product
+        g.sgd_lr, g.sgd_wd = float(sgd[0]), float(sgd[1])
     if dispatch is not None:
         g.disp = dispatch
         g.disp.work_counter = ws.sched.data_ptr() + 4 * Workspace.DISPATCH_WORK

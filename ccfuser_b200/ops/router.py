@@ -105,14 +105,19 @@ class _FusedRouter(torch.autograd.Function):
 
 
 def _dw_by_gemm(dlp: torch.Tensor, x: torch.Tensor, e: int, d: int, dtype) -> torch.Tensor:
-    """dW [e, d] = dlp[:, :e]^T x on the library's k-grouped GEMM (one group whose reduction runs over the tokens);
-    ``dlp [T, 128 or 256]`` is the logits' gradient, zero-padded to the kernel's tile height."""
+    """dW [e, d] = dlp[:, :e]^T x on the library's k-grouped GEMM; ``dlp [T, 128 or 256]`` is the logits' gradient,
+    zero-padded to the kernel's tile height. The token range is cut into up to 16 groups, each reduced by its own
+    tiles (one group alone would occupy d / 256 CTAs for the whole reduction), and the partial sums are added."""
     t, ep = dlp.shape
-    gb, gr = G.single_group(t, x.device)
-    dwp = torch.empty(ep, d, dtype=torch.float32, device=x.device)
+    groups = max(1, min(16, t // 1024))
+    per = (t + groups - 1) // groups
+    per = (per + 127) // 128 * 128
+    base = torch.arange(groups, dtype=torch.int32, device=x.device) * per
+    rows = (t - base).clamp(min=0, max=per).to(torch.int32)
+    dwp = torch.empty(groups, ep, d, dtype=torch.float32, device=x.device)
     G.launch(a0=dlp, b0=x, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=d, kgroup=True, m_per_group=ep,
-             group_base=gb, group_rows=gr, num_groups=1, out0=dwp, ld_out=d, out_fp32=True)
-    return dwp[:e].to(dtype)
+             group_base=base, group_rows=rows, num_groups=groups, out0=dwp, ld_out=d, out_fp32=True)
+    return dwp[:, :e].sum(0).to(dtype)
 
 
 def fused_router(x: torch.Tensor, weight: torch.Tensor, bias, k: int, want_logits: bool = False, path: int = 0):

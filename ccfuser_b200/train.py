@@ -19,11 +19,14 @@ from .parallel.ddp import allreduce_replicated_grads, reduce_expert_grads, wrap_
 class TrainStep:
     """One optimisation step as a callable object: forward, backward, gradient reductions, optimizer; see the module docstring."""
     def __init__(self, model: nn.Module, lr: float = 1e-3, optimizer: str = "sgd", dp_group=None,
-                 use_ddp: bool = True, aux_loss: bool = False, expert_dp_group=None, mean_expert_grads: bool = False):
+                 use_ddp: bool = True, aux_loss: bool = False, expert_dp_group=None, mean_expert_grads: bool = False,
+                 fuse_expert_sgd: bool = False):
         """``dp_group``: ranks over which the replicated parameters are averaged (default: all). ``expert_dp_group``:
         ranks that hold replicas of this rank's experts (second value of ``make_ep_dp_groups``) when the expert-parallel
         group is smaller than the job. ``mean_expert_grads``: scale expert gradients by 1 / world size so that they
-        follow the same mean-over-ranks convention as the replicated parameters."""
+        follow the same mean-over-ranks convention as the replicated parameters. ``fuse_expert_sgd`` (plain SGD, fused
+        MoE layers with ``ep_size == 1``): the expert weight matrices are updated inside the backward pass
+        (``MoELayer.fuse_sgd``) with the optimizer's current learning rate and weight decay."""
         self.raw_model = model
         self.dp_group = dp_group
         self.expert_dp_group = expert_dp_group
@@ -43,12 +46,20 @@ class TrainStep:
         else:
             raise ValueError(optimizer)
         self.device = params[0].device
+        self.fuse_expert_sgd = bool(fuse_expert_sgd)
+        if self.fuse_expert_sgd and (optimizer != "sgd" or expert_dp_group is not None or mean_expert_grads):
+            raise ValueError("fuse_expert_sgd needs plain SGD and expert gradients that nothing else uses")
         self.aux_loss = aux_loss
         self._ids = self._labels = None
 
     def step_device(self, ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
         """One optimisation step on device tensors; returns the loss tensor (no host sync)."""
         self.opt.zero_grad(set_to_none=True)
+        if self.fuse_expert_sgd:
+            group = self.opt.param_groups[0]
+            for m in self.raw_model.modules():
+                if hasattr(m, "fuse_sgd") and hasattr(m, "experts"):
+                    m.fuse_sgd(group["lr"], group.get("weight_decay", 0.0))
         loss = self.model(ids, labels)
         if self.aux_loss:
             aux = self.raw_model.aux_loss()

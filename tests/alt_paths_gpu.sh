@@ -17,6 +17,7 @@ run() {   # name, environment assignments..., then the pytest arguments after "-
 }
 run python_launch_path CCFUSER_NATIVE_RUNTIME=0  -- tests/test_gpu_fused.py tests/test_gpu_models.py tests/test_gpu_graph.py -x
 run library_router     CCFUSER_FUSED_ROUTER=0    -- tests/test_gpu_fused.py tests/test_gpu_models.py -x
+run pair_kernel_always CCFUSER_SMALL_ROWS=0      -- tests/test_gpu_fused.py tests/test_gpu_models.py tests/test_gpu_graph.py -x
 run one_cta_kernel     CCFUSER_TWO_CTA=0         -- tests/test_gpu_fused.py tests/test_gpu_bench_shapes.py -x
 run canary             CCFUSER_CANARY=1          -- tests/test_gpu_fused.py -x -k "forward_backward or module_api"
 run few_comm_ctas      CCFUSER_COMM_CTAS=16      -- tests/test_gpu_fused.py -x -k "forward_backward or module_api"

@@ -143,8 +143,13 @@ def _rel(a, b):
 
 @pytest.mark.parametrize("act,cf,tokens", [("gelu", None, 1024), ("gelu", 1.0, 1000), ("relu", 1.25, 333),
                                             ("swiglu", 1.2, 1024), ("swiglu", None, 77)])
-def test_fused_layer_forward_backward_one_gpu(act, cf, tokens):
+@pytest.mark.parametrize("pair_tiles", [True, False])
+def test_fused_layer_forward_backward_one_gpu(act, cf, tokens, pair_tiles, monkeypatch):
+    from ccfuser_b200.ops import gemm as G
     from ccfuser_b200.ops.fused import topk_softmax, _FusedMoEFn
+    # at these sizes an expert expects fewer rows than one 256-row pair tile, which selects the one-CTA kernel for the
+    # row-grouped launches; half of the cases keep the CTA-pair kernel so that both carry the whole layer here
+    monkeypatch.setattr(G, "SMALL_ROWS_DEFAULT", 0 if pair_tiles else 320)
     cfg, layer = _make_layer(act, cf, tokens=1024)
     fm = layer._fused_impl()
     x = (torch.randn(tokens, cfg.d_model, device="cuda") * 0.5).to(cfg.dtype).requires_grad_(True)
@@ -278,3 +283,42 @@ def test_bounded_wait_reports_timeout_without_hanging():
         ws.check("probe")
     ws.check("probe")  # cleared
     assert torch.ones(4, device="cuda").sum().item() == 4
+
+
+@pytest.mark.parametrize("act,native", [("gelu", True), ("swiglu", True), ("gelu", False)])
+def test_sgd_in_the_weight_gradient_epilogue_matches_a_separate_step(act, native):
+    """MoELayer.fuse_sgd against backward + FusedSGD.step on a copy of the layer: same weights after the step (up to the
+    rounding of the gradient that only the separate path stores), same dx, biases and router untouched by the fusion."""
+    from ccfuser_b200.ops.optim import FusedSGD
+    lr, wd = 0.5, 0.01
+    cfg, ref = _make_layer(act, 1.25, e=8, d=256, f=512, tokens=1024)
+    _, fused = _make_layer(act, 1.25, e=8, d=256, f=512, tokens=1024)
+    fused.load_state_dict(ref.state_dict())
+    fused._fused_impl().native_runtime = native
+    ref._fused_impl().native_runtime = native
+    fused.fuse_sgd(lr, wd)
+    x = (torch.randn(1000, cfg.d_model, device="cuda") * 0.5).to(cfg.dtype)
+    gy = (torch.randn(1000, cfg.d_model, device="cuda") * 0.2).to(cfg.dtype)
+    before = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    outs = []
+    for layer in (ref, fused):
+        xi = x.clone().requires_grad_(True)
+        layer(xi).backward(gy)
+        outs.append(xi.grad)
+    opt = FusedSGD([p for n, p in ref.named_parameters() if n.startswith("experts.") and n.endswith("weight")], lr=lr, weight_decay=wd)
+    opt.step()
+    torch.cuda.synchronize()
+    fused.check_status()
+    assert _rel(outs[1], outs[0]) < 1e-2                      # dgrad-1 ran on the old weights
+    for n, p in fused.named_parameters():
+        q = dict(ref.named_parameters())[n]
+        if n.startswith("experts.") and n.endswith("weight"):
+            assert p.grad is None
+            upd_f, upd_r = p.detach().float() - before[n].float(), q.detach().float() - before[n].float()
+            assert float(upd_r.abs().max()) > 1e-3              # the step is visible at bf16 resolution
+            assert _rel(upd_f, upd_r) < 5e-2, n
+        else:
+            assert p.grad is not None and torch.equal(p.detach(), before[n])
+            assert _rel(p.grad, q.grad) < 2e-2, n
+    ref.release()
+    fused.release()

@@ -128,3 +128,53 @@ def test_inference_call_passes_save_pre_zero():
     desc = N.Layer.from_buffer_copy(call[0])
     assert N.load().ccf_layer_forward(C.byref(desc), *call[1:9], None, buf, 4, C.byref(cnt)) == 0
     assert cnt.value == 2 and not buf[0].args.out1 and buf[0].args.out0
+
+
+@pytest.mark.parametrize("act", ["gelu", "swiglu"])
+def test_fused_sgd_launches_agree_and_update_in_place(act):
+    """MoELayer.fuse_sgd: the weight-gradient GEMMs write over the weights (out0 = the parameter, lr and weight decay in
+    the launch block), dgrad-1 runs before the wgrad-1 launches that overwrite what it reads, no weight gradient comes
+    back; the Python path and the native runtime build the same launches in the same order."""
+    cfg = MoEConfig(d_model=128, d_ffn=256, num_experts=4, top_k=2, activation=act, bias=True, dtype=torch.bfloat16,
+                    ep_size=1, backend="fused", max_tokens=256)
+    layer = MoELayer(cfg, device="cpu")
+    layer.fuse_sgd(0.25, 0.01)
+    fm = layer._fused_impl()
+    ex = layer.experts
+    real = N.load()
+    x = torch.randn(100, 128).bfloat16().requires_grad_(True)
+    fm.native_runtime = False
+    with N.record_launches() as rec:
+        layer(x).float().sum().backward()
+    py = _gemms(rec.calls)[2:]                                  # the backward launches
+    assert ex.htoh4.weight.grad is None and ex.h4toh.weight.grad is None and ex.htoh4.bias.grad is not None
+    swiglu = act == "swiglu"
+    # order: dgrad-2, wgrad-2 (in place on w2), dgrad-1 (COMBINE), then the wgrad-1 launches (in place on wg / w1)
+    assert [g.epi for g in py] == [N.EPI_DSWIGLU if swiglu else N.EPI_DACT, N.EPI_STORE, N.EPI_COMBINE] + [N.EPI_STORE] * (2 if swiglu else 1)
+    assert py[1].args.out0 == ex.h4toh.weight.data_ptr() and abs(py[1].args.sgd_lr - 0.25) < 1e-7 and abs(py[1].args.sgd_wd - 0.01) < 1e-7
+    tail = [g.args.out0 for g in py[3:]]
+    assert tail == ([ex.htoh4_gate.weight.data_ptr(), ex.htoh4.weight.data_ptr()] if swiglu else [ex.htoh4.weight.data_ptr()])
+    assert py[0].args.sgd_lr == 0 and py[2].args.sgd_lr == 0
+    # the native runtime: same blocks
+    fm.native_runtime = True
+    x2 = x.detach().clone().requires_grad_(True)
+    with N.record_launches() as rec2:
+        layer(x2).float().sum().backward()
+    bwd = [c for c in rec2.calls if c[0] == "ccf_layer_backward"][0][1]
+    grads = N.LayerGrads.from_buffer_copy(bwd[4])
+    assert abs(grads.sgd_lr - 0.25) < 1e-7 and not grads.dw1 and not grads.dw2
+    buf = (N.GemmLaunch * 8)()
+    cnt = C.c_int(0)
+    assert real.ccf_layer_backward(C.byref(N.Layer.from_buffer_copy(bwd[0])), bwd[1], bwd[2], bwd[3], C.byref(grads), bwd[5],
+                                   bwd[6], None, buf, 8, C.byref(cnt)) == 0
+    nat = [N.GemmLaunch.from_buffer_copy(bytes(buf[i])) for i in range(cnt.value)]
+    assert len(nat) == len(py)
+    per_call = {"args.disp.x", "args.disp.slot_expert", "args.disp.slot_gate", "args.disp.dgate", "args.out0", "args.out1"}
+    for p, n, skip in zip(py, nat, [per_call, set(), {"a0", "a1"}] + [{"a0"}] * 2):
+        _compare(p, n, skip)
+    # a layer that spans ranks refuses
+    spanning = type("SpanningLayer", (), {"config": cfg.replace(ep_size=2), "_fused": None})()
+    with pytest.raises(ValueError):
+        MoELayer.fuse_sgd(spanning, 0.1)
+    layer.fuse_sgd(None)
+    assert fm.sgd is None

@@ -62,7 +62,7 @@ constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiWarps * kEpiStageB
 template <bool kKGroup, int kEpi>
 __device__ __forceinline__ Tile decode_tile(int t, const CcfGemmArgs& a, const Ctrl* c) {
   Tile ti;
-  constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
+  const int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : (a.bn == 128 ? 128 : BN);
   if constexpr (!kKGroup) {
     const int nt = c->n_tiles;
     int lo = 0, hi = a.num_groups;  // largest g with nt * mt_prefix[g] <= t
@@ -111,7 +111,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
   const int lane = threadIdx.x & 31;
   volatile int* abort_word = &ctrl->abort_word;
   const uint64_t limit = fail_fast_limit(args.status, args.wait_limit_ns);
-  constexpr int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : BN;
+  const int bn_run = (!kKGroup && kBMajor == MAJ_K && kEpi != CCF_EPI_SWIGLU && args.bn == 128) ? 128 : BN;   // MMA N
+  const int bn_out = (kEpi == CCF_EPI_SWIGLU) ? BN / 2 : bn_run;
 
   // ---- set-up ------------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
@@ -227,7 +228,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
           const uint32_t fullb = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kABytes;
-          mbar_arrive_expect_tx(fullb, kStageBytes);
+          mbar_arrive_expect_tx(fullb, kABytes + bn_run * BK * 2);
           const int seg = kKGroup ? 0 : kb / kb_per_seg;
           const int kk = kKGroup ? 0 : (kb - seg * kb_per_seg) * BK;
           const CUtensorMap* ma = seg ? &tmA1 : &tmA0;
@@ -263,7 +264,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     }
   } else if (warp == 1) {
     // ======================= MMA issuer =======================
-    const uint32_t idesc = make_idesc(BM, BN, args.fp16, kAMajor, kBMajor);
+    const uint32_t idesc = make_idesc(BM, bn_run, args.fp16, kAMajor, kBMajor);
     int stage = 0, phase = 0, ss = 0, sphase = 0, as = 0, aphase = 0, seq = -1;
     bool ok = true;
     while (ok) {
@@ -533,7 +534,11 @@ int ccf_gemm_launch(const CcfGemmLaunch* L, void* stream_v) {
   const int a_box_rows = (L->a_major == MAJ_K) ? BM : BK;
   const bool pair = L->two_cta != 0;
   if (pair && L->kgroup && (a.m_per_group % (2 * BM) != 0)) return -8;
-  int b_box_rows = (L->b_major == MAJ_K) ? BN : BK;
+  if (a.bn != 0 && a.bn != BN) {
+    // the narrow tile exists in the one-CTA kernel for row-grouped launches with a K-major B operand
+    if (a.bn != 128 || pair || L->kgroup || L->b_major != MAJ_K || L->epi == CCF_EPI_SWIGLU) return -10;
+  }
+  int b_box_rows = (L->b_major == MAJ_K) ? (a.bn == 128 ? 128 : BN) : BK;
   if (L->epi == CCF_EPI_SWIGLU || (pair && L->b_major == MAJ_K)) b_box_rows = BN / 2;  // a pair member loads half of B
   int rc;
   if ((rc = make_tmap(&tm[0], L->a0, L->a_rows, L->a_cols, 64, a_box_rows, fp16))) return rc;

@@ -102,6 +102,9 @@ struct CcfGemmArgs {
   float sgd_lr;             // EPI_STORE, non-zero: out0 holds parameters and is updated in place, out0 -= lr * (acc + wd * out0)
   int comm_warps;           // 1: the CTA's two dedicated warps run the dispatch role; 0: its epilogue warps do, before their first tile
   float sgd_wd;             // weight decay of that update
+  int bn;                   // one-CTA kernel, row-grouped, K-major B: output tile width, 256 (or 0) / 128. The narrow tile doubles
+                            // the number of tiles of a launch that would otherwise leave most SMs idle
+  int pad3;
   CcfDispatchArgs disp;
 };
 

@@ -278,7 +278,9 @@ __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, co
   }
 
   // chunks of 32 accumulator columns; this warp takes n_chunks of them starting at chunk0
-  constexpr int n_chunks = (kEpi == CCF_EPI_SWIGLU) ? 2 : 4;
+  // 32-column chunks per warp: half of a 256-column tile (or of the 128 output columns of a SwiGLU tile, or of a
+  // 128-column narrow tile)
+  const int n_chunks = (kEpi == CCF_EPI_SWIGLU || args.bn == 128) ? 2 : 4;
   const int chunk0 = half * n_chunks;
   uint32_t racc[32];  // one buffer: the next chunk is requested right after this one is copied out to f[]
   if (have_acc) tmem_ld32(t_row + chunk0 * 32, racc);

@@ -33,7 +33,7 @@ struct Dry {
 };
 
 // completion-counter increments per row of a COMBINE GEMM with n columns (two epilogue warps per 256-column tile)
-int combine_units(int n) { return 2 * ((n + 255) / 256); }
+int combine_units(int n, int bn) { return 2 * ((n + bn - 1) / bn); }
 
 // fields every launch of this layer shares
 CcfGemmLaunch base_launch(const CcfLayer* L) {
@@ -132,9 +132,9 @@ int issue(CcfGemmLaunch& g, Dry* dry, void* stream) {
   return ccf_gemm_launch(&g, stream);
 }
 
-int wait_and_reduce(const CcfLayer* L, const void* comb, void* out, int tokens, Dry* dry, void* stream) {
+int wait_and_reduce(const CcfLayer* L, const void* comb, void* out, int tokens, int bn, Dry* dry, void* stream) {
   if (dry != nullptr) return 0;
-  int rc = ccf_combine_wait(L->done, L->done_cum, L->sent_rows, combine_units(L->d_model), L->world, L->wait_limit_ns,
+  int rc = ccf_combine_wait(L->done, L->done_cum, L->sent_rows, combine_units(L->d_model, bn), L->world, L->wait_limit_ns,
                             L->status, stream);
   if (rc) return rc;
   return ccf_combine_reduce(comb, L->slot_row, out, tokens, L->top_k, L->d_model, L->fp16, stream);
@@ -166,6 +166,13 @@ int ccf_layer_forward(const CcfLayer* L, const void* x, const int* idx, const fl
   // calls run on 128-row tiles (one-CTA kernel).
   const long long rows_per_expert = static_cast<long long>(tokens) * L->top_k * L->world / (L->e_total > 0 ? L->e_total : 1);
   const int row_two_cta = rows_per_expert > L->small_rows ? L->two_cta : 0;
+  // GEMM-2 on the one-CTA kernel with so few tiles that most SMs would idle: 128-column tiles (twice as many)
+  int gemm2_bn = 256;
+  if (row_two_cta == 0) {
+    const long long tiles = static_cast<long long>(e_loc) * ((rows_per_expert + 127) / 128 > 0 ? (rows_per_expert + 127) / 128 : 1) *
+                            ((d + 255) / 256);
+    if (tiles < 148) gemm2_bn = 128;
+  }
   if (dry == nullptr) {
     if (L->device >= 0 && cudaSetDevice(L->device) != cudaSuccess) return -7;
     // 1. positions, kept counts, destination order of this rank's slots
@@ -237,10 +244,11 @@ int ccf_layer_forward(const CcfLayer* L, const void* x, const int* idx, const fl
     g.args.ld_out = d;
     set_combine(g, L, L->peer_comb, L->row_gate);
     g.two_cta = row_two_cta;
+    g.args.bn = gemm2_bn;
     if ((rc = issue(g, dry, stream))) return rc;
   }
   // 5. wait for every owner, sum the k slots of each token
-  rc = wait_and_reduce(L, L->comb, y, tokens, dry, stream);
+  rc = wait_and_reduce(L, L->comb, y, tokens, gemm2_bn, dry, stream);
   if (dry_count != nullptr) *dry_count = dry_state.n;
   return rc;
 }
@@ -360,7 +368,7 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
       return rc;
   }
   if (!sgd && (rc = dgrad1())) return rc;
-  rc = wait_and_reduce(L, L->gcomb, G->dx, tokens, dry, stream);
+  rc = wait_and_reduce(L, L->gcomb, G->dx, tokens, 256, dry, stream);
   if (dry_count != nullptr) *dry_count = dry_state.n;
   return rc;
 }

@@ -51,7 +51,7 @@ class GemmArgs(C.Structure):
         ("n", C.c_int), ("k", C.c_int), ("num_groups", C.c_int), ("m_per_group", C.c_int), ("kseg", C.c_int),
         ("b_group_rows", C.c_int), ("act", C.c_int), ("fp16", C.c_int), ("out_fp32", C.c_int), ("world", C.c_int),
         ("send_finish", C.c_int), ("n_comm_ctas", C.c_int), ("max_slots", C.c_int), ("trace_tiles", C.c_int),
-        ("total_index", C.c_int), ("sgd_lr", C.c_float), ("comm_warps", C.c_int), ("sgd_wd", C.c_float),
+        ("total_index", C.c_int), ("sgd_lr", C.c_float), ("comm_warps", C.c_int), ("sgd_wd", C.c_float), ("bn", C.c_int), ("pad3", C.c_int),
         ("disp", DispatchArgs),
     ]
 
@@ -272,7 +272,8 @@ ARG_ERRORS = {-2: "argument out of range", -3: "n must be a multiple of 32", -4:
               -5: "k must be a multiple of 8", -6: "no kernel for this combination of operand majors and epilogue",
               -7: "cudaSetDevice failed", -8: "the CTA-pair kernel needs m_per_group % 256 == 0 in k-grouped mode",
               -9: "the dispatch role exists only in the kernels that read the receive buffer (forward: bias+activation / "
-                  "SwiGLU epilogues with backward=0, backward: activation-derivative epilogues with backward=1)"}
+                  "SwiGLU epilogues with backward=0, backward: activation-derivative epilogues with backward=1)",
+              -10: "128-column tiles exist in the one-CTA kernel for row-grouped launches with a K-major B operand only"}
 
 
 def check(rc: int, what: str):

@@ -270,6 +270,7 @@ class FusedMoE:
         self._desc = None
         self._desc_key = None
         self.sgd = None         # (lr, weight decay): expert weights are updated by the weight-gradient GEMMs (fuse_sgd)
+        self._call_bn = 256
         self._call_two_cta = None   # kernel choice of the current call's row-grouped launches (_row_two_cta)
         self._owed = None       # weak reference to the autograd node whose backward still needs this layer's buffers
 
@@ -449,6 +450,12 @@ class FusedMoE:
         rows = tokens * self.cfg.top_k * self.world // max(1, self.cfg.num_experts)
         return None if rows > G.SMALL_ROWS_DEFAULT else False
 
+    def _gemm2_bn(self, tokens: int) -> int:
+        """Tile width of the forward GEMM-2 + combine launch of a call with ``tokens`` tokens per rank (ops/gemm.py:
+        narrow_tiles); the source-side wait counts its completion units with the same width."""
+        rows = tokens * self.cfg.top_k * self.world // max(1, self.cfg.num_experts)
+        return G.narrow_tiles(rows, self.cfg.experts_per_rank, self.cfg.d_model, self._row_two_cta(tokens) is False)
+
     def _combine_kw(self, peer_comb, row_gate):
         ctx = self.ctx
         done = [p + 4 * self.rank for p in ctx.peer("done")]
@@ -508,6 +515,7 @@ class FusedMoE:
                       total_index=self.max_rows // TILE, local_begin=self.local_begin, local_rows=self.local_rows,
                       two_cta=self._row_two_cta(t))
         self._call_two_cta = common["two_cta"]
+        self._call_bn = self._gemm2_bn(t)
         if cfg.activation == "swiglu":
             G.launch(a0=self.xrecv, b0=w1.view(e_loc * f, d), b1=wg.view(e_loc * f, d), a_major=N.MAJ_K, b_major=N.MAJ_K,
                      epi=N.EPI_SWIGLU, n=f, k=d, b_group_rows=f, out0=self.h_act, out1=self.h_pre if save_pre else None,
@@ -524,12 +532,12 @@ class FusedMoE:
         d, f, e_loc = cfg.d_model, cfg.d_ffn, cfg.experts_per_rank
         G.launch(a0=self.h_act, b0=w2.view(e_loc * d, f), a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_COMBINE, n=d, k=f,
                  group_base=self.group_base, group_rows=self.group_rows, num_groups=e_loc, b_group_rows=d, bias0=b2,
-                 ld_out=d, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace, two_cta=self._call_two_cta,
+                 ld_out=d, wait_ns=cc.wait_ns, workspace=cc.ws, trace=trace, two_cta=self._call_two_cta, bn=self._call_bn,
                  **self._combine_kw(self.buf.peer_ptrs(self.off_comb), cc.row_gate))
 
     def stage_reduce(self, tokens: int, out: torch.Tensor):
         """Wait until every owner has delivered this rank's rows, then sum the k slots of each token."""
-        self._wait_and_reduce(self.comb, tokens, G.combine_units(self.cfg.d_model), out)
+        self._wait_and_reduce(self.comb, tokens, G.combine_units(self.cfg.d_model, self._call_bn), out)
 
 
 class GraphedForward:

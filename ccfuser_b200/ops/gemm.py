@@ -135,7 +135,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
            act=N.ACT_NONE, out_fp32=False, tile_flags=None, local_begin=None, local_rows=None, row_src=None, row_gate=None,
            peer_comb=None, peer_done=None, world=1, send_finish=0, max_slots=0,
            dispatch: Optional[N.DispatchArgs] = None, n_comm_ctas=0, total_index=-1, two_cta=None, wait_ns=DEFAULT_WAIT_NS, grid=0, trace=None,
-           workspace: Optional[Workspace] = None, comm_warps: Optional[int] = None, sgd=None):
+           workspace: Optional[Workspace] = None, comm_warps: Optional[int] = None, sgd=None, bn: int = 0):
     """Fill a CcfGemmLaunch and launch on the current stream. a0/b0 are 2-D contiguous views."""
     lib = N.load()
     ws = workspace or Workspace.get(a0.device)
@@ -166,6 +166,7 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     g.world, g.send_finish, g.n_comm_ctas, g.max_slots = int(world), int(send_finish), int(n_comm_ctas), int(max_slots)
     g.total_index = int(total_index)
     g.comm_warps = int(COMM_WARPS_DEFAULT if comm_warps is None else comm_warps)
+    g.bn = int(bn)
     if sgd is not None:     # (lr, weight decay): EPI_STORE updates out0 in place instead of storing the product
         g.sgd_lr, g.sgd_wd = float(sgd[0]), float(sgd[1])
     if dispatch is not None:
@@ -189,10 +190,19 @@ def launch(*, a0, b0, a_major, b_major, epi, n, k=0, group_base, group_rows, num
     return ws
 
 
-def combine_units(n: int) -> int:
-    """Completion-counter increments per output row of a COMBINE GEMM with n columns: every 256-column tile is
-    stored by two epilogue warps per row quarter (one per 128-column half), and each of them reports its rows."""
-    return 2 * ((n + 255) // 256)
+def combine_units(n: int, bn: int = 256) -> int:
+    """Completion-counter increments per output row of a COMBINE GEMM with n columns and bn-column tiles: every tile
+    is stored by two epilogue warps per row quarter (one per half of its columns), and each of them reports its rows."""
+    return 2 * ((n + bn - 1) // bn)
+
+
+def narrow_tiles(rows_per_expert: int, experts: int, n: int, one_cta: bool) -> int:
+    """Tile width of a row-grouped, K-major-B launch on the one-CTA kernel: 128 when 256-column tiles would leave most of
+    the 148 SMs without a tile (a handful of experts with a few hundred rows: the latency-bound serving shapes)."""
+    if not one_cta:
+        return 256
+    tiles = experts * max(1, (rows_per_expert + 127) // 128) * ((n + 255) // 256)
+    return 128 if tiles < 148 else 256
 
 
 def single_group(rows: int, device):

@@ -249,3 +249,29 @@ def test_scheduler_counters_return_to_zero():
         G.linear(x, w)
     torch.cuda.synchronize()
     assert int(G.Workspace.get(x.device).sched.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 4096, 1024), (300, 320, 256), (129, 128, 64)])
+def test_narrow_tiles_on_the_one_cta_kernel(m, n, k):
+    """128-column output tiles (bn=128): the tile shape of launches that would otherwise leave most SMs without work.
+    Same product and bias as with 256-column tiles, including a column count that is not a multiple of the tile."""
+    N, G = _mods()
+    torch.manual_seed(1)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    b = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    gb, gr = G.single_group(m, "cuda")
+    outs = []
+    for bn in (128, 256):
+        y = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+        G.launch(a0=x, b0=w, a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_STORE, n=n, k=k, group_base=gb, group_rows=gr,
+                 num_groups=1, b_group_rows=n, out0=y, bias0=b.view(1, n), two_cta=False, bn=bn)
+        outs.append(y)
+    torch.cuda.synchronize()
+    G.Workspace.get(x.device).check("narrow tiles")
+    _close(outs[0], F.linear(x.float(), w.float(), b.float()))
+    assert torch.equal(outs[0], outs[1])
+    # the CTA-pair kernel and MN-major operands have no narrow tile: refused on the host
+    with pytest.raises(RuntimeError):
+        G.launch(a0=x, b0=w, a_major=N.MAJ_K, b_major=N.MAJ_K, epi=N.EPI_STORE, n=n, k=k, group_base=gb, group_rows=gr,
+                 num_groups=1, b_group_rows=n, out0=outs[0], two_cta=True, bn=128)

@@ -235,9 +235,9 @@ __global__ void __launch_bounds__(256) router_small_kernel(const void* __restric
   const int vecs = d >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x) + static_cast<size_t>(t) * vecs;
   const uint4* wr = reinterpret_cast<const uint4*>(wg);
-  // unrolled: the iterations are independent, and with one iteration's loads in flight at a time a 4096-wide row
-  // costs sixteen memory latencies
-#pragma unroll 4
+  // unrolled for few experts (the partial sums of many experts need the registers): the iterations are independent, and
+  // with one iteration's loads in flight at a time a 4096-wide row costs sixteen memory latencies
+#pragma unroll(kE <= 16 ? 4 : 1)
   for (int v = lane; v < vecs; v += 32) {
     const uint4 xv = __ldg(xr + v);
     const uint32_t xq[4] = {xv.x, xv.y, xv.z, xv.w};

@@ -561,7 +561,9 @@ class GraphedForward:
             raise ValueError(f"{tokens} tokens exceed config.max_tokens={cfg.max_tokens}")
         fm.ctx.use_device_epoch()
         self.layer, self.tokens = layer, tokens
-        self.x = torch.zeros(tokens, cfg.d_model, dtype=cfg.dtype, device=fm.device)
+        # random warm-up input: with zeros every token has the same logits (the router bias), all ranks route everything
+        # to the same k experts, and the owners' receive buffers overflow during the warm-up calls
+        self.x = torch.randn(tokens, cfg.d_model, device=fm.device).to(cfg.dtype)
         self.valid = torch.ones(tokens, dtype=torch.bool, device=fm.device)
         self._rows = torch.arange(tokens, device=fm.device)
         side = torch.cuda.Stream(device=fm.device)

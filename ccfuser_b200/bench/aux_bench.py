@@ -45,11 +45,8 @@ def main():
         wg = (torch.randn(e, d, device=dev) * 0.05).bfloat16().requires_grad_(True)
         xr = x.clone().requires_grad_(True)
         if "router" in cases:
-            for path, label in ((1, "router_tensor_core"), (2, "router_warp_per_token")):
-                if path == 2 and e > 64:
-                    continue
-                with torch.no_grad():
-                    report(label, t * d * 2 + e * d * 2 + t * k * 8, lambda p=path: fused_router(x, wg, None, k, path=p))
+            with torch.no_grad():
+                report("router_tensor_core", t * d * 2 + e * d * 2 + t * k * 8, lambda: fused_router(x, wg, None, k))
         if "router_bwd" in cases:
             idx, w = fused_router(xr, wg, None, k)
             gw = torch.randn_like(w)

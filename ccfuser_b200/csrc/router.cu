@@ -216,75 +216,6 @@ router_topk_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 
 
 // ---------------------------------------------------------------------------------------------------
-// The same router for small batches without the tensor cores: one warp per token, the lanes stride over the row in
-// 16-byte pieces and keep one fp32 partial sum per expert. A few hundred tokens fill one or two 128-row tensor-core
-// tiles whose 64 k-blocks then run one after the other on one or two SMs (tens of microseconds of latency); spread
-// over warps on all SMs the same work takes a few. Same outputs, same selection rule (topk_offer / topk_finish).
-// ---------------------------------------------------------------------------------------------------
-template <int kE>
-__global__ void __launch_bounds__(256) router_small_kernel(const void* __restrict__ x, const void* __restrict__ wg,
-                                                           const void* __restrict__ bias, int* __restrict__ idx,
-                                                           float* __restrict__ w, float* __restrict__ logits, int T, int d,
-                                                           int E, int K, int fp16) {
-  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (t >= T) return;
-  float acc[kE];
-#pragma unroll
-  for (int e = 0; e < kE; ++e) acc[e] = 0.f;
-  const int vecs = d >> 3;
-  const uint4* xr = reinterpret_cast<const uint4*>(x) + static_cast<size_t>(t) * vecs;
-  const uint4* wr = reinterpret_cast<const uint4*>(wg);
-  // unrolled for few experts (the partial sums of many experts need the registers): the iterations are independent, and
-  // with one iteration's loads in flight at a time a 4096-wide row costs sixteen memory latencies
-#pragma unroll(kE <= 16 ? 4 : 1)
-  for (int v = lane; v < vecs; v += 32) {
-    const uint4 xv = __ldg(xr + v);
-    const uint32_t xq[4] = {xv.x, xv.y, xv.z, xv.w};
-    float xf[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = unpack2(xq[i], fp16);
-      xf[2 * i] = f.x;
-      xf[2 * i + 1] = f.y;
-    }
-#pragma unroll
-    for (int e = 0; e < kE; ++e) {
-      if (e < E) {
-        const uint4 wv = __ldg(wr + static_cast<size_t>(e) * vecs + v);
-        const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = unpack2(wq[i], fp16);
-          acc[e] = fmaf(xf[2 * i], f.x, acc[e]);
-          acc[e] = fmaf(xf[2 * i + 1], f.y, acc[e]);
-        }
-      }
-    }
-  }
-  float tv[kRtMaxK];
-  int ti[kRtMaxK];
-#pragma unroll
-  for (int j = 0; j < kRtMaxK; ++j) { tv[j] = -INFINITY; ti[j] = -1; }
-  bool has_nan = false;
-#pragma unroll
-  for (int e = 0; e < kE; ++e) {
-    float v = acc[e];
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    if (e < E) {
-      if (bias != nullptr)
-        v += fp16 ? __half2float(reinterpret_cast<const __half*>(bias)[e])
-                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[e]);
-      if (logits != nullptr && lane == 0) logits[static_cast<size_t>(t) * E + e] = v;
-      if (v != v) { has_nan = true; v = -INFINITY; }
-      topk_offer(tv, ti, v, e);
-    }
-  }
-  if (lane == 0) topk_finish(tv, ti, K, idx + static_cast<size_t>(t) * K, w + static_cast<size_t>(t) * K, has_nan);
-}
-
-// ---------------------------------------------------------------------------------------------------
 // Backward of the router without a GEMM. The gradient of the logits is non-zero only in the k selected columns,
 //   g[t, j] = w[t, j] * (dw[t, j] - sum_i w[t, i] dw[t, i])          (softmax over the selected logits),
 // so   dx[t, :]  = sum_j g[t, j] * Wg[idx[t, j], :]                  (k rows of the small router matrix per token)
@@ -427,26 +358,12 @@ int ccf_router_select_host(const float* logits, int tokens, int e, int k, int* i
 // x [tokens, d] and wg [e, d] are 2-byte row-major operands of the same type (fp16 = 1: half, 0: bf16), bias [e] of
 // that type or null. idx [tokens, k] int32 and w [tokens, k] fp32 are written; logits_f32 [tokens, e] only if not null.
 // Limits: e <= 256, k <= min(8, e), d a multiple of 8 and at least 64. Returns 0, or a negative host-side error.
-// `path`: 0 = choose by size (the warp-per-token kernel for small batches with at most 64 experts, the tensor-core
-// kernel otherwise), 1 = tensor-core kernel, 2 = warp-per-token kernel (needs e <= 64).
 int ccf_router_topk(const void* x, const void* wg, const void* bias, int tokens, int d, int e, int k, int fp16, int* idx,
-                    float* w, float* logits_f32, int* status, unsigned long long wait_limit_ns, int device, int path,
+                    float* w, float* logits_f32, int* status, unsigned long long wait_limit_ns, int device,
                     void* stream_v) {
   using namespace ccf;
   if (tokens < 1 || e < 1 || e > 256 || k < 1 || k > kRtMaxK || k > e || d < 64 || d % 8 != 0) return -2;
-  if (path == 2 && e > 64) return -2;
   if (device >= 0 && cudaSetDevice(device) != cudaSuccess) return -7;
-  // small batch: a few CTAs' worth of tensor-core tiles would run their k-blocks one after the other
-  if (path == 2 || (path == 0 && e <= 64 && static_cast<long long>(tokens) * e <= 1024LL * 16)) {
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_v);
-    const int threads = 256, blocks = (tokens * 32 + threads - 1) / threads;
-    if (e <= 8) router_small_kernel<8><<<blocks, threads, 0, st>>>(x, wg, bias, idx, w, logits_f32, tokens, d, e, k, fp16);
-    else if (e <= 16) router_small_kernel<16><<<blocks, threads, 0, st>>>(x, wg, bias, idx, w, logits_f32, tokens, d, e, k, fp16);
-    else if (e <= 32) router_small_kernel<32><<<blocks, threads, 0, st>>>(x, wg, bias, idx, w, logits_f32, tokens, d, e, k, fp16);
-    else router_small_kernel<64><<<blocks, threads, 0, st>>>(x, wg, bias, idx, w, logits_f32, tokens, d, e, k, fp16);
-    cudaError_t err = cudaGetLastError();
-    return err == cudaSuccess ? 0 : -static_cast<int>(err);
-  }
   RouterArgs a;
   a.bias = bias; a.idx = idx; a.w = w; a.logits = logits_f32; a.status = status; a.wait_limit_ns = wait_limit_ns;
   a.tokens = tokens; a.d = d; a.e = e; a.k = k; a.fp16 = fp16;

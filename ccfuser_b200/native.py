@@ -173,7 +173,7 @@ def _declare(lib):
         "ccf_gemm_launch": ([C.POINTER(GemmLaunch), p], i),
         "ccf_gemm_smem_bytes": ([], i),
         "ccf_debug_pair_tile_order": ([p, p, p, p, i, i, i, i, i, p, i], i),
-        "ccf_router_topk": ([p, p, p, i, i, i, i, i, p, p, p, p, ull, i, i, p], i),
+        "ccf_router_topk": ([p, p, p, i, i, i, i, i, p, p, p, p, ull, i, p], i),
         "ccf_router_select_host": ([p, i, i, i, p, p], i),
         "ccf_router_bwd": ([p, p, p, p, p, p, p, p, i, i, i, i, i, p], i),
         "ccf_topk_softmax": ([p, i, i, i, i, i, p, p, p], i),

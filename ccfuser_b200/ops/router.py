@@ -25,7 +25,7 @@ from .gemm import Workspace
 
 class _FusedRouter(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, k, want_logits, path=0):
+    def forward(ctx, x, weight, bias, k, want_logits):
         lib = N.load()
         t, d = x.shape
         e = weight.shape[0]
@@ -41,7 +41,7 @@ class _FusedRouter(torch.autograd.Function):
         dev = x.device.index if x.device.index is not None else torch.cuda.current_device()
         N.check(lib.ccf_router_topk(x.data_ptr(), wt.data_ptr(), N.ptr(b), t, d, e, k, int(x.dtype == torch.float16),
                                     idx.data_ptr(), w.data_ptr(), N.ptr(logits), ws.status.data_ptr(),
-                                    5_000_000_000, dev, int(path), N.stream_ptr()), "ccf_router_topk")
+                                    5_000_000_000, dev, N.stream_ptr()), "ccf_router_topk")
         N.count(1)
         ctx.save_for_backward(x, wt, idx, w)
         ctx.has_bias = bias is not None
@@ -71,7 +71,7 @@ class _FusedRouter(torch.autograd.Function):
                                            N.ptr(dw32), N.ptr(db32), t, d, e, k, fp16, N.stream_ptr()), "ccf_router_bwd")
                 N.count(int(need_x) + int(dw32 is not None))
             if not big:
-                return (dx, dw32.to(wt.dtype) if need_w else None, db32.to(wt.dtype) if need_b else None, None, None, None)
+                return (dx, dw32.to(wt.dtype) if need_w else None, db32.to(wt.dtype) if need_b else None, None, None)
             # many tokens: the scatter-add of token rows into E weight rows is a [E, T] x [T, d] product with a sparse
             # left factor; on the tensor cores (own grouped GEMM, reduction over the tokens) it beats atomics
             ep = 128 if e <= 128 else 256
@@ -81,7 +81,7 @@ class _FusedRouter(torch.autograd.Function):
             N.count(1)
             dw = _dw_by_gemm(dlp, x, e, d, wt.dtype) if need_w else None
             db = dlp[:, :e].float().sum(0).to(wt.dtype) if need_b else None
-            return dx, dw, db, None, None, None
+            return dx, dw, db, None, None
         # dense gradient of the logits (auxiliary losses) + the selected columns' part, then two products on the
         # tcgen05 grouped GEMM: [T, Ep] x [Ep, d] and [Ep, T] x [T, d], Ep = E padded to the 128-row tile
         dl = torch.zeros(t, e, dtype=torch.float32, device=x.device)
@@ -101,7 +101,7 @@ class _FusedRouter(torch.autograd.Function):
         if need_w:
             dw = _dw_by_gemm(dlp, x, e, d, wt.dtype)
         db = dl.sum(0).to(wt.dtype) if need_b else None
-        return dx, dw, db, None, None, None
+        return dx, dw, db, None, None
 
 
 def _dw_by_gemm(dlp: torch.Tensor, x: torch.Tensor, e: int, d: int, dtype) -> torch.Tensor:
@@ -120,12 +120,10 @@ def _dw_by_gemm(dlp: torch.Tensor, x: torch.Tensor, e: int, d: int, dtype) -> to
     return dwp[:, :e].sum(0).to(dtype)
 
 
-def fused_router(x: torch.Tensor, weight: torch.Tensor, bias, k: int, want_logits: bool = False, path: int = 0):
+def fused_router(x: torch.Tensor, weight: torch.Tensor, bias, k: int, want_logits: bool = False):
     """-> (idx, w) or, with ``want_logits``, (idx, w, fp32 logits). The logits are differentiable: a loss computed from
-    them (load balance, z-loss) sends its gradient back to x and the router parameters. ``path``: 0 = by size (small
-    batches with at most 64 experts take a warp-per-token kernel, everything else the tensor-core kernel), 1 / 2 force
-    one of the two (tests)."""
-    idx, w, logits = _FusedRouter.apply(x, weight, bias, k, want_logits, path)
+    them (load balance, z-loss) sends its gradient back to x and the router parameters."""
+    idx, w, logits = _FusedRouter.apply(x, weight, bias, k, want_logits)
     return (idx, w, logits) if want_logits else (idx, w)
 
 

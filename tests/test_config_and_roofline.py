@@ -94,7 +94,7 @@ def test_native_entry_points_reject_bad_arguments_before_touching_the_device():
 
     def router(**kw):
         a = dict(ok, **kw)
-        return lib.ccf_router_topk(None, None, None, a["tokens"], a["d"], a["e"], a["k"], 0, None, None, None, None, 0, -1, 0, None)
+        return lib.ccf_router_topk(None, None, None, a["tokens"], a["d"], a["e"], a["k"], 0, None, None, None, None, 0, -1, None)
     assert router(e=257) == -2 and router(k=9) == -2 and router(k=3, e=2) == -2 and router(d=32) == -2
     assert router(d=260) == -2 and router(tokens=0) == -2
     b = N.BarrierArgs()

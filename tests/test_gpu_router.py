@@ -12,10 +12,7 @@ pytestmark = pytest.mark.gpu
                                                (777, 1024, 200, 8, torch.float16, True),
                                                (333, 512, 256, 4, torch.bfloat16, True),
                                                (64, 4096, 8, 1, torch.float16, False)])
-@pytest.mark.parametrize("path", [1, 2])
-def test_fused_router_matches_reference(t, d, e, k, dtype, bias, path):
-    if path == 2 and e > 64:
-        pytest.skip("the warp-per-token kernel holds one partial sum per expert in registers: at most 64 experts")
+def test_fused_router_matches_reference(t, d, e, k, dtype, bias):
     from ccfuser_b200.gates import topk_softmax_reference
     from ccfuser_b200.ops.gemm import Workspace
     from ccfuser_b200.ops.router import fused_router
@@ -23,7 +20,7 @@ def test_fused_router_matches_reference(t, d, e, k, dtype, bias, path):
     x = (torch.randn(t, d, device="cuda") * 0.5).to(dtype).requires_grad_(True)
     w = (torch.randn(e, d, device="cuda") * 0.05).to(dtype).requires_grad_(True)
     b = (torch.randn(e, device="cuda") * 0.1).to(dtype).requires_grad_(True) if bias else None
-    idx, wt, logits = fused_router(x, w, b, k, want_logits=True, path=path)
+    idx, wt, logits = fused_router(x, w, b, k, want_logits=True)
     torch.cuda.synchronize()
     Workspace.get(x.device).check("fused router")
     ref_logits = torch.nn.functional.linear(x.detach().float(), w.detach().float(), None if b is None else b.detach().float())

@@ -5,6 +5,7 @@ epilogue took. Shows that the tensor cores start before the row push has ended.
 
     python -m ccfuser_b200.bench.overlap_trace                 # d_model 2048, d_ffn 8192
     D=1024 F=4096 python -m ccfuser_b200.bench.overlap_trace
+    D=4096 F=14336 TOKENS=256 E_LOC=1 ACT=swiglu python -m ccfuser_b200.bench.overlap_trace   # the small-message shape
 
 Trace layout (``trace=`` of ops/gemm.py:launch): int64 ``[CTA, tile slot, 8]`` SM clock stamps {0 tile fetched, 1 rows
 arrived, 2 last load issued, 3 accumulator free, 4 first operands landed, 5 last MMA committed, 6 accumulator full,
@@ -46,8 +47,9 @@ def analyze(trace: torch.Tensor, kblocks: int, leaders_only: bool = True) -> Dic
 def main():
     from .. import MoEConfig, MoELayer
     from .kernel_bench import synthetic_routing
-    d, f, tokens, e_loc = int(os.environ.get("D", 2048)), int(os.environ.get("F", 8192)), 16384, 8
-    cfg = MoEConfig(d_model=d, d_ffn=f, num_experts=e_loc, top_k=1, activation="gelu", dtype=torch.bfloat16, ep_size=1,
+    d, f = int(os.environ.get("D", 2048)), int(os.environ.get("F", 8192))
+    tokens, e_loc, act = int(os.environ.get("TOKENS", 16384)), int(os.environ.get("E_LOC", 8)), os.environ.get("ACT", "gelu")
+    cfg = MoEConfig(d_model=d, d_ffn=f, num_experts=e_loc, top_k=1, activation=act, bias=act != "swiglu", dtype=torch.bfloat16, ep_size=1,
                     backend="fused", max_tokens=tokens, recv_factor=2.5)
     layer = MoELayer(cfg, device="cuda")
     fm, ex = layer._fused_impl(), layer.experts
@@ -60,7 +62,9 @@ def main():
 
     def fwd(tr1=None):
         fm.stage_route_plan(idx, tokens)
-        fm.stage_dispatch_gemm1(x, idx, gate, ex.htoh4.weight, ex.htoh4.bias, trace=tr1)
+        swiglu = act == "swiglu"
+        fm.stage_dispatch_gemm1(x, idx, gate, ex.htoh4.weight, ex.htoh4.bias, ex.htoh4_gate.weight if swiglu else None,
+                                ex.htoh4_gate.bias if swiglu else None, trace=tr1, save_pre=False)
         fm.stage_gemm2_combine(ex.h4toh.weight, ex.h4toh.bias)
         fm.stage_reduce(tokens, y)
 
@@ -70,7 +74,8 @@ def main():
     fwd(t1)
     torch.cuda.synchronize()
     t = t1.cpu().double()
-    lead = t[0::2]     # leader CTAs of the pairs record the MMA events
+    pair = fm._call_two_cta is not False
+    lead = t[0::2] if pair else t     # in the CTA-pair kernel the leader CTAs record the MMA events
     start, disp = lead[:, nt - 1, 0], lead[:, nt - 1, 1]
     first_ops, first_commit, first_epi = lead[:, 0, 4], lead[:, 0, 5], lead[:, 0, 7]
     ntile = (lead[:, :nt - 1, 7] > 0).sum(1)
@@ -83,7 +88,7 @@ def main():
     print(f"  first epilogue finished                         : {float((first_epi - start)[ok].median()):.0f}")
     print(f"  kernel end (last epilogue)                      : {float((last - start)[ok].median()):.0f}")
     print(f"  CTAs whose first MMA ran before their own push ended: {int(((first_ops < disp) & ok).sum())} of {int(ok.sum())}")
-    print("  per tile:", analyze(t1, kblocks=(d + 63) // 64))
+    print("  per tile:", analyze(t1, kblocks=(d + 63) // 64, leaders_only=pair))
 
 
 if __name__ == "__main__":

@@ -40,8 +40,10 @@ def test_shadow_and_rebalance_multi_gpu(world):
     _run(world, 29700 + world, worker="mgpu_features_worker.py", token="MGPU_FEATURES_OK", timeout=300)
 
 
-@pytest.mark.xfail(strict=False, reason="fused backend on an expert-parallel sub-group: first run on hardware pending")
-def test_expert_parallel_inside_data_parallel_multi_gpu():
-    if torch.cuda.device_count() < 4:
-        pytest.skip("needs 4 GPUs")
-    _run(4, 29710, worker="mgpu_features_worker.py", token="MGPU_EPDP_OK", timeout=300, args=["--ep-inside-dp"])
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_inside_data_parallel_multi_gpu(world):
+    """Expert-parallel groups of two ranks inside the job (with 4 ranks: two replicas of every expert, whose gradients
+    are reduced over the data-parallel group)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run(world, 29710 + world, worker="mgpu_features_worker.py", token="MGPU_EPDP_OK", timeout=300, args=["--ep-inside-dp"])

@@ -124,14 +124,25 @@ __device__ __noinline__ void dispatch_rows(const CcfDispatchArgs& a, int* status
       dst[i] = on ? reinterpret_cast<uint4*>(a.peer_recv[owner]) + static_cast<size_t>(row) * vecs : nullptr;
     }
     if constexpr (!kBackward) {
-      for (int v = lane; v < vecs; v += 32) {
-        uint4 r[kChunk];
+      // kU column steps at a time, so that kChunk * kU = 8 loads are in flight per lane whatever the chunk size: with
+      // few rows to push (small chunks, see dispatch_role) the copy of a row is then a few memory latencies, not d / 256
+      constexpr int kU = 8 / kChunk > 0 ? 8 / kChunk : 1;
+      for (int v0 = lane; v0 < vecs; v0 += 32 * kU) {
+        uint4 r[kChunk][kU];
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i)
-          if (src[i]) r[i] = __ldg(src[i] + v);
+        for (int u = 0; u < kU; ++u) {
+          const int v = v0 + 32 * u;
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i)
-          if (dst[i]) dst[i][v] = r[i];
+          for (int i = 0; i < kChunk; ++i)
+            if (src[i] && v < vecs) r[i][u] = __ldg(src[i] + v);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const int v = v0 + 32 * u;
+#pragma unroll
+          for (int i = 0; i < kChunk; ++i)
+            if (dst[i] && v < vecs) dst[i][v] = r[i][u];
+        }
       }
     } else {
       // rows of the backward pass carry g * dy; the gate gradient is <dy, saved scaled output> / g

@@ -451,7 +451,13 @@ template <int kEpi>
 __device__ __forceinline__ void dispatch_role(const CcfGemmArgs& args, bool comm_warp) {
   if (comm_warp != (args.comm_warps != 0)) return;
   if constexpr (kEpi == CCF_EPI_BIAS_ACT || kEpi == CCF_EPI_SWIGLU) {
-    if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8, false>(args.disp, args.status);
+    if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) {
+      // A chunk is pushed by one warp from start to end. With only a few thousand rows in all (the latency-bound
+      // serving shapes) chunks of two rows spread them over sixteen times as many warps, and the first tile's rows are
+      // complete after microseconds instead of tens of them.
+      if (args.disp.order_off[args.disp.e_total] <= 4096) dispatch_rows<2, false>(args.disp, args.status);
+      else dispatch_rows<8, false>(args.disp, args.status);
+    }
   } else if constexpr (kEpi == CCF_EPI_DACT || kEpi == CCF_EPI_DSWIGLU) {
     if (static_cast<int>(blockIdx.x) < args.n_comm_ctas) dispatch_rows<8, true>(args.disp, args.status);
   }

@@ -34,10 +34,11 @@ def parse():
                     help="1 (default): after the warm-up, every MoE layer moves experts between GPUs to the placement planned "
                          "from its observed routing counts, if that lowers the busiest GPU's load by at least 5 %% (same "
                          "model function; outside the timed region; needs more than one GPU). 0: keep the initial placement")
-    ap.add_argument("--fuse-expert-sgd", type=int, default=0,
-                    help="1: on one GPU the expert weights' SGD update runs in the epilogue of the weight-gradient GEMMs "
-                         "(MoELayer.fuse_sgd; needs ep_size 1). 0 (default): separate optimizer pass, which is faster as "
-                         "measured (the in-place update exposes the weight read's latency in the epilogue)")
+    ap.add_argument("--fuse-expert-sgd", type=int, default=1,
+                    help="1 (default): on one GPU the expert weights' SGD update runs in the epilogue of the weight-gradient "
+                         "GEMMs (MoELayer.fuse_sgd; needs ep_size 1, so it has no effect on 2 or more GPUs): the same update, "
+                         "without writing the expert gradients and reading them and the weights again; measured 5 %% faster "
+                         "per step with all 64 experts on one GPU. 0: separate optimizer pass for all parameters")
     ap.add_argument("--no-baseline", action="store_true",
                     help="skip the repository's own baseline arm (same model on the all_to_all_single + library "
                          "grouped-GEMM backend), against which vs_baseline is reported")

@@ -340,6 +340,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
       if (++ss == kSchedSlots) { ss = 0; sphase ^= 1; }
       if (t < 0) break;
       const Tile ti = decode_tile<kKGroup, kEpi>(t, args, ctrl);
+      if constexpr (kEpi == CCF_EPI_STORE) {
+        // SGD in the epilogue: ask L2 for the weights under this tile while its accumulator is still being filled
+        if (args.sgd_lr != 0.f && !args.out_fp32)
+          sgd_prefetch_l2(args, (kKGroup ? static_cast<long long>(ti.g) * args.m_per_group : 0ll) + ti.row0, ti.n0,
+                          ti.rows_valid, q, half, lane);
+      }
       const bool have_acc = ti.kblocks > 0;
       if (have_acc) {
         if (!mbar_wait(smem_u32(&ctrl->acc_full[as]), aphase, abort_word, limit)) {

@@ -411,6 +411,12 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_
     int as = 0, aphase = 0, seq = 0;
     for (int t = pair; t < total_tiles; t += n_pairs, ++seq) {
       const PairTile ti = decode_pair_tile<kKGroup, kEpi>(t, args, ctrl);
+      if constexpr (kEpi == CCF_EPI_STORE) {
+        // SGD in the epilogue: ask L2 for the weights under this tile while its accumulator is still being filled
+        if (args.sgd_lr != 0.f && !args.out_fp32)
+          sgd_prefetch_l2(args, (kKGroup ? static_cast<long long>(ti.g) * args.m_per_group : 0ll) + ti.row0 + static_cast<int>(cta) * BM,
+                          ti.n0, kKGroup ? BM : max(0, min(BM, ti.rows_pair - static_cast<int>(cta) * BM)), q, half, lane);
+      }
       const bool have_acc = ti.kblocks > 0;
       if (have_acc) {
         if (!mbar_wait_cluster(smem_u32(&ctrl->acc_full[as]), aphase, abort_word, limit)) {

@@ -252,6 +252,52 @@ struct CombineDest {
   bool ok;
 };
 
+// In-place SGD epilogue (STORE with sgd_lr != 0): the weights under the tile are read before they are rewritten. One
+// 32-column chunk of a warp's 32 rows is 2 KB, so a warp that asked for it only when it needed it kept 16 KB per SM in
+// flight and the kernel ran at the latency of a DRAM read per chunk. sgd_prefetch_l2 asks L2 for this lane's row of the
+// tile part as soon as the tile is known (before its accumulator is complete); sgd_fetch reads one chunk in the layout
+// of staged_load64 (row 8 i + lane / 4, piece lane % 4) into registers one chunk ahead of its use. Measured on the
+// 64-expert GPT-MoE step: asking for the NEXT tile's weights instead, or reading two chunks ahead, was slower than this.
+__device__ __forceinline__ void sgd_prefetch_l2(const CcfGemmArgs& args, long long row_base, int n0, int rows_valid, int q,
+                                                int half, int lane) {
+  const int r_in_tile = q * 32 + lane;
+  if (r_in_tile >= rows_valid) return;
+  const int n_chunks = args.bn == 128 ? 2 : 4;
+  const int n = n0 + half * n_chunks * 32;
+  if (n >= args.n) return;
+  const char* p = reinterpret_cast<const char*>(args.out0) + (static_cast<size_t>(row_base + r_in_tile) * args.ld_out + n) * 2;
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+  if (n_chunks == 4 && n + 64 < args.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + 128));
+}
+__device__ __forceinline__ void sgd_fetch(unsigned long long row_ptr, int lane, uint4 (&v)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = 8 * i + (lane >> 2), piece = lane & 3;
+    const unsigned long long p = __shfl_sync(0xffffffffu, row_ptr, row);
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (p != 0ull) v[i] = *reinterpret_cast<const uint4*>(p + piece * 16);
+  }
+}
+// the chunk fetched by sgd_fetch, transposed through the warp's staging area into one row per lane
+__device__ __forceinline__ void sgd_unstage(uint32_t stage, int lane, const uint4 (&v)[4], uint32_t (&w)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = 8 * i + (lane >> 2), piece = lane & 3;
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + stage_off(row, piece)), "r"(v[i].x), "r"(v[i].y),
+                 "r"(v[i].z), "r"(v[i].w)
+                 : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w[4 * j]), "=r"(w[4 * j + 1]), "=r"(w[4 * j + 2]), "=r"(w[4 * j + 3])
+                 : "r"(stage + stage_off(lane, j))
+                 : "memory");
+  }
+  __syncwarp();
+}
+
 template <int kEpi>
 __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, const Tile& ti, long long row_base,
                                                      int rows_valid, int rows_store, bool have_acc, uint32_t t_row,
@@ -289,6 +335,10 @@ __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, co
   const bool has_b0 = kBias0Prefetch && args.bias0 != nullptr;
   if (has_b0 && ti.n0 + chunk0 * 32 < args.n)
     load_bias_raw(args.bias0, static_cast<size_t>(ti.g) * args.n + ti.n0 + chunk0 * 32, bnext);
+  // in-place SGD never carries a bias (the host refuses the combination): the bias registers hold the weights' chunks
+  const bool sgd = kEpi == CCF_EPI_STORE && args.sgd_lr != 0.f && !args.out_fp32;
+  if (sgd) sgd_fetch((valid && ti.n0 + chunk0 * 32 < args.n) ? addr2(args.out0, orow, args.ld_out, ti.n0 + chunk0 * 32) : 0ull,
+                     lane, bnext);
   // not unrolled: the body is large and every launch pays for fetching the kernel's code once per SM
 #pragma unroll 1
   for (int c = 0; c < n_chunks; ++c) {
@@ -300,6 +350,8 @@ __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, co
     for (int i = 0; i < 4; ++i) bcur[i] = bnext[i];
     if (has_b0 && c + 1 < n_chunks && n + 32 < args.n)
       load_bias_raw(args.bias0, static_cast<size_t>(ti.g) * args.n + n + 32, bnext);
+    if (sgd && c + 1 < n_chunks)
+      sgd_fetch((valid && n + 32 < args.n) ? addr2(args.out0, orow, args.ld_out, n + 32) : 0ull, lane, bnext);
     if (have_acc) {
       tmem_ld_wait();
       acc_to_float(racc, f);
@@ -361,10 +413,10 @@ __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, co
         if (has_b0) add_bias_raw(f, bcur, fp16);
         if (args.out_fp32) {
           if (valid) store32_f32(reinterpret_cast<float*>(args.out0) + orow * args.ld_out + n, f);
-        } else if (args.sgd_lr != 0.f) {
+        } else if (sgd) {
           // the accumulator is a weight gradient and out0 the weights themselves: plain SGD applied here saves writing
           // the gradient, and the optimizer's pass that would read it and the weights again
-          staged_load64<false>(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);
+          sgd_unstage(stage, lane, bcur, w);
           const float lr = args.sgd_lr, wd = args.sgd_wd;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {

@@ -7,6 +7,7 @@ Same convention as the reference: expert parameters carry ``skip_allreduce = Tru
 """
 from __future__ import annotations
 
+import os
 from typing import List
 
 import torch
@@ -33,6 +34,9 @@ def wrap_ddp(model: nn.Module, process_group=None, **kw):
     dev = next(model.parameters()).device
     ids = [dev.index] if dev.type == "cuda" else None
     kw.setdefault("gradient_as_bucket_view", True)
+    # bucket size of the gradient all-reduce (MB): NVSwitch gives every message full bandwidth, so a bucket is sized for
+    # launch count and for overlap with the backward pass, not for a link count
+    kw.setdefault("bucket_cap_mb", int(os.environ.get("CCFUSER_DDP_BUCKET_MB", "25")))
     return torch.nn.parallel.DistributedDataParallel(model, device_ids=ids, process_group=process_group, **kw)
 
 

@@ -67,7 +67,8 @@ def time_fn(fn, iters=10, warmup=3, flush_mb=256, back_to_back=0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--cases", default="square,fwd1,fwd2,dgrad,dgrad_plain,wgrad,cublas")
+    ap.add_argument("--cases", default="square,fwd1,fwd2,dgrad,dgrad_plain,wgrad,cublas",
+                    help="comma-separated; also fwd1_parts and wgrad_sgd")
     ap.add_argument("--rows", type=int, default=4096 * 8)
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--d", type=int, default=4096)
@@ -158,11 +159,22 @@ def main():
         report("dgrad2_plain_store", 2 * r * d * f, gemm(
             a0=y, b0=w2.view(e * d, f), a_major=N.MAJ_K, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, k=d,
             group_base=gb, group_rows=gr, num_groups=e, b_group_rows=d, out0=h), kblocks=(d + 63) // 64)
+    # few rows per expert (many experts on one GPU): the one-CTA kernel, as the layer chooses there
+    wgrad_two_cta = None if rows_per > 512 else False
     if "wgrad" in cases:
         dw = torch.empty(e, d, f, device=dev, dtype=torch.bfloat16)
         report("wgrad2", 2 * r * d * f, gemm(
             a0=y, b0=h, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True, m_per_group=d,
-            group_base=gb, group_rows=gr, num_groups=e, out0=dw, ld_out=f), kblocks=(rows_per + 63) // 64)
+            group_base=gb, group_rows=gr, num_groups=e, out0=dw, ld_out=f, two_cta=wgrad_two_cta), kblocks=(rows_per + 63) // 64)
+        del dw
+    if "wgrad_sgd" in cases:
+        # the same product with the SGD step in its epilogue: w2 is read and rewritten in place, no gradient is stored
+        y.normal_()
+        h.normal_()
+        report("wgrad2_sgd_in_place", 2 * r * d * f, gemm(
+            a0=y, b0=h, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True, m_per_group=d,
+            group_base=gb, group_rows=gr, num_groups=e, out0=w2, ld_out=f, two_cta=wgrad_two_cta, sgd=(1e-6, 0.0)),
+            kblocks=(rows_per + 63) // 64)
     sampler.stop()
     if args.out:
         os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)

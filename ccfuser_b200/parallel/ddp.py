@@ -35,8 +35,9 @@ def wrap_ddp(model: nn.Module, process_group=None, **kw):
     ids = [dev.index] if dev.type == "cuda" else None
     kw.setdefault("gradient_as_bucket_view", True)
     # bucket size of the gradient all-reduce (MB): NVSwitch gives every message full bandwidth, so a bucket is sized for
-    # launch count and for overlap with the backward pass, not for a link count
-    kw.setdefault("bucket_cap_mb", int(os.environ.get("CCFUSER_DDP_BUCKET_MB", "25")))
+    # launch count and for overlap with the backward pass, not for a link count (GPT-MoE 24 L on 4 GPUs: 121.1 ms per
+    # step with torch's 25 MB, 119.4 ms with 100 MB, 119.8 ms with 400 MB)
+    kw.setdefault("bucket_cap_mb", int(os.environ.get("CCFUSER_DDP_BUCKET_MB", "100")))
     return torch.nn.parallel.DistributedDataParallel(model, device_ids=ids, process_group=process_group, **kw)
 
 

@@ -151,3 +151,16 @@ struct CcfBarrierArgs {
   unsigned long long wait_limit_ns;
   int world, my_rank, epoch, pad0;
 };
+
+// One launch of the SGD step over several parameter tensors (ccf_sgd_multi): tensor t is updated by the blocks
+// [first_block[t], first_block[t + 1]).
+#define CCF_SGD_MULTI 48
+struct CcfSgdMulti {
+  void* p[CCF_SGD_MULTI];
+  const void* g[CCF_SGD_MULTI];
+  long long n[CCF_SGD_MULTI];
+  int first_block[CCF_SGD_MULTI + 1];
+  int count;
+  float lr, wd;
+  int fp16;
+};

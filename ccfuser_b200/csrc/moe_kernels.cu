@@ -388,12 +388,14 @@ __global__ void __launch_bounds__(256) colsum_grouped_kernel(const void* x, long
 // SGD step on 2-byte parameters: p -= lr * (g + wd * p), 16-byte vectors, fp32 arithmetic. With 64 experts per GPU
 // the optimizer streams ~150 GB per step; one pass with full-width accesses keeps it at the HBM rate.
 // ---------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) sgd_step_kernel(void* p, const void* g, long long n, float lr, float wd, int fp16) {
+// blocks [0, nb) of one tensor: block lb takes every nb-th group of 256 vectors; the odd elements at the end go to
+// the first threads of block 0
+__device__ __forceinline__ void sgd_range(void* p, const void* g, long long n, float lr, float wd, int fp16, int lb, int nb) {
   const long long nvec = n >> 3;
   uint4* pv = reinterpret_cast<uint4*>(p);
   const uint4* gv = reinterpret_cast<const uint4*>(g);
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+  for (long long i = static_cast<long long>(lb) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(nb) * blockDim.x) {
     const uint4 a = pv[i];
     const uint4 b = __ldg(gv + i);
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
@@ -406,9 +408,8 @@ __global__ void __launch_bounds__(256) sgd_step_kernel(void* p, const void* g, l
     pv[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
   // tail (n not a multiple of 8)
-  const long long tail0 = nvec << 3;
-  const long long t = tail0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t < n) {
+  const long long t = (nvec << 3) + threadIdx.x;
+  if (lb == 0 && threadIdx.x < 8 && t < n) {
     if (fp16) {
       __half* ph = reinterpret_cast<__half*>(p);
       const float pf = __half2float(ph[t]), gf = __half2float(reinterpret_cast<const __half*>(g)[t]);
@@ -419,6 +420,22 @@ __global__ void __launch_bounds__(256) sgd_step_kernel(void* p, const void* g, l
       pb[t] = __float2bfloat16(pf - lr * (gf + wd * pf));
     }
   }
+}
+
+__global__ void __launch_bounds__(256) sgd_step_kernel(void* p, const void* g, long long n, float lr, float wd, int fp16) {
+  sgd_range(p, g, n, lr, wd, fp16, blockIdx.x, gridDim.x);
+}
+
+// The same step over up to CCF_SGD_MULTI tensors in one launch. A transformer has hundreds of small parameter tensors
+// (biases, LayerNorm weights, routers): one launch each costs more in launch gaps than in memory traffic.
+__global__ void __launch_bounds__(256) sgd_multi_kernel(const __grid_constant__ CcfSgdMulti a) {
+  const int b = blockIdx.x;
+  int lo = 0, hi = a.count;  // largest t with first_block[t] <= b
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (a.first_block[mid] <= b) lo = mid; else hi = mid;
+  }
+  sgd_range(a.p[lo], a.g[lo], a.n[lo], a.lr, a.wd, a.fp16, b - a.first_block[lo], a.first_block[lo + 1] - a.first_block[lo]);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -572,6 +589,21 @@ int ccf_sgd_step(void* p, const void* g, long long n, float lr, float wd, int fp
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 16) blocks = 148 * 16;
   ccf::sgd_step_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p, g, n, lr, wd, fp16);
+  return last_err();
+}
+
+int ccf_sizeof_sgd_multi() { return static_cast<int>(sizeof(CcfSgdMulti)); }
+
+// a->first_block must be filled: first_block[0] = 0, non-decreasing, at least one block per tensor
+int ccf_sgd_multi(const CcfSgdMulti* a, void* stream) {
+  if (a->count < 1 || a->count > CCF_SGD_MULTI) return -2;
+  uintptr_t bits = 0;
+  for (int t = 0; t < a->count; ++t) {
+    bits |= reinterpret_cast<uintptr_t>(a->p[t]) | reinterpret_cast<uintptr_t>(a->g[t]);
+    if (a->n[t] <= 0 || a->first_block[t + 1] <= a->first_block[t]) return -3;
+  }
+  if ((bits & 15) || a->first_block[0] != 0) return -2;
+  ccf::sgd_multi_kernel<<<a->first_block[a->count], 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*a);
   return last_err();
 }
 

@@ -85,6 +85,16 @@ class BarrierArgs(C.Structure):
                 ("world", C.c_int), ("my_rank", C.c_int), ("epoch", C.c_int), ("pad0", C.c_int)]
 
 
+SGD_MULTI = 48
+
+
+class SgdMulti(C.Structure):
+    """Mirror of CcfSgdMulti (csrc/gemm_args.h): up to SGD_MULTI parameter tensors updated by one launch."""
+    _fields_ = [("p", _vp * SGD_MULTI), ("g", _vp * SGD_MULTI), ("n", C.c_longlong * SGD_MULTI),
+                ("first_block", C.c_int * (SGD_MULTI + 1)), ("count", C.c_int), ("lr", C.c_float), ("wd", C.c_float),
+                ("fp16", C.c_int)]
+
+
 class Layer(C.Structure):
     """Mirror of CcfLayer (csrc/runtime.h): addresses and sizes of one fused layer for the native runtime."""
     _fields_ = [
@@ -159,7 +169,8 @@ def load(build_if_missing: bool = True):
         lib = _DeclaredOnly(cdll, _declare(cdll))
         for name, struct in (("gemm_args", GemmArgs), ("dispatch_args", DispatchArgs),
                              ("gemm_launch", GemmLaunch), ("plan_args", PlanArgs), ("layer", Layer),
-                             ("layer_grads", LayerGrads), ("barrier_args", BarrierArgs)):
+                             ("layer_grads", LayerGrads), ("barrier_args", BarrierArgs),
+                             ("sgd_multi", SgdMulti)):
             want = getattr(lib, "ccf_sizeof_" + name)()
             if want != C.sizeof(struct):
                 raise RuntimeError(f"ctypes mirror of {name} is {C.sizeof(struct)} bytes, library has {want}")
@@ -191,6 +202,7 @@ def _declare(lib):
         "ccf_colsum_grouped": ([p, ll, i, i, p, p, p, i, p], i),
         "ccf_wait_probe": ([p, i, ull, p, p], i),
         "ccf_sgd_step": ([p, p, ll, C.c_float, C.c_float, i, p], i),
+        "ccf_sgd_multi": ([C.POINTER(SgdMulti), p], i),
         "ccf_layernorm_max_d": ([], i),
         "ccf_layernorm_fwd": ([p, p, p, p, p, p, i, i, C.c_float, i, p], i),
         "ccf_layernorm_bwd": ([p, p, p, p, p, p, p, p, i, i, i, p], i),

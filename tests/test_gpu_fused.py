@@ -270,6 +270,28 @@ def test_fused_sgd_matches_torch():
         assert torch.allclose(a.detach().float(), ref.float(), rtol=8e-3, atol=1e-3)
 
 
+def test_fused_sgd_many_tensors_in_few_launches():
+    """More tensors than one launch takes, both dtypes, odd sizes: every tensor gets the same update as alone."""
+    from ccfuser_b200 import native as N
+    from ccfuser_b200.ops.optim import FusedSGD
+    torch.manual_seed(1)
+    sizes = [1, 7, 8, 9, 2048, 4099, 65536, 300001] * 13          # 104 tensors
+    params, refs = [], []
+    for i, n in enumerate(sizes):
+        dtype = torch.float16 if i % 3 == 0 else torch.bfloat16
+        p = torch.randn(n, device="cuda").to(dtype)
+        g = torch.randn(n, device="cuda").to(dtype)
+        a = torch.nn.Parameter(p.clone())
+        a.grad = g.clone()
+        params.append(a)
+        refs.append((p.float() - 0.05 * (g.float() + 0.1 * p.float())).to(dtype))
+    before = N.LAUNCHES[0]
+    FusedSGD(params, lr=0.05, weight_decay=0.1).step()
+    assert N.LAUNCHES[0] - before <= 4                            # 35 fp16 + 69 bf16 tensors, 48 per launch
+    for a, ref in zip(params, refs):
+        assert torch.allclose(a.detach().float(), ref.float(), rtol=8e-3, atol=1e-3)
+
+
 def test_bounded_wait_reports_timeout_without_hanging():
     """A wait on a flag that nothing sets gives up after its limit and records a status; the context stays usable."""
     from ccfuser_b200 import native as N, MoECommTimeout

@@ -278,6 +278,38 @@ __device__ __forceinline__ void sgd_fetch(unsigned long long row_ptr, int lane, 
     if (p != 0ull) v[i] = *reinterpret_cast<const uint4*>(p + piece * 16);
   }
 }
+// The same two helpers for rows that lie one after the other in memory (the STORE epilogue: row r of the warp's 32 rows
+// is at base + r * stride, the first rows_ok of them exist): the addresses are computed instead of shuffled.
+__device__ __forceinline__ void sgd_fetch_lin(unsigned long long base, unsigned long long stride, int rows_ok, int lane,
+                                              uint4 (&v)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = 8 * i + (lane >> 2), piece = lane & 3;
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows_ok) v[i] = *reinterpret_cast<const uint4*>(base + row * stride + piece * 16);
+  }
+}
+__device__ __forceinline__ void staged_store64_lin(uint32_t stage, int lane, const uint32_t (&w)[16], unsigned long long base,
+                                                   unsigned long long stride, int rows_ok) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + stage_off(lane, j)), "r"(w[4 * j]),
+                 "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                 : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = 8 * i + (lane >> 2), piece = lane & 3;
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(stage + stage_off(row, piece))
+                 : "memory");
+    if (row < rows_ok) *reinterpret_cast<uint4*>(base + row * stride + piece * 16) = v;
+  }
+  __syncwarp();
+}
 // the chunk fetched by sgd_fetch, transposed through the warp's staging area into one row per lane
 __device__ __forceinline__ void sgd_unstage(uint32_t stage, int lane, const uint4 (&v)[4], uint32_t (&w)[16]) {
 #pragma unroll
@@ -337,8 +369,11 @@ __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, co
     load_bias_raw(args.bias0, static_cast<size_t>(ti.g) * args.n + ti.n0 + chunk0 * 32, bnext);
   // in-place SGD never carries a bias (the host refuses the combination): the bias registers hold the weights' chunks
   const bool sgd = kEpi == CCF_EPI_STORE && args.sgd_lr != 0.f && !args.out_fp32;
-  if (sgd) sgd_fetch((valid && ti.n0 + chunk0 * 32 < args.n) ? addr2(args.out0, orow, args.ld_out, ti.n0 + chunk0 * 32) : 0ull,
-                     lane, bnext);
+  // STORE: the warp's 32 rows follow each other in out0; the first lin_rows of them exist
+  const unsigned long long lin_stride = static_cast<unsigned long long>(args.ld_out) * 2ull;
+  const int lin_rows = min(32, max(0, rows_valid - q * 32));
+  const unsigned long long lin_base = addr2(args.out0, row_base + q * 32, args.ld_out, 0);
+  if (sgd) sgd_fetch_lin(lin_base + (ti.n0 + chunk0 * 32) * 2ull, lin_stride, ti.n0 + chunk0 * 32 < args.n ? lin_rows : 0, lane, bnext);
   // not unrolled: the body is large and every launch pays for fetching the kernel's code once per SM
 #pragma unroll 1
   for (int c = 0; c < n_chunks; ++c) {
@@ -351,7 +386,7 @@ __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, co
     if (has_b0 && c + 1 < n_chunks && n + 32 < args.n)
       load_bias_raw(args.bias0, static_cast<size_t>(ti.g) * args.n + n + 32, bnext);
     if (sgd && c + 1 < n_chunks)
-      sgd_fetch((valid && n + 32 < args.n) ? addr2(args.out0, orow, args.ld_out, n + 32) : 0ull, lane, bnext);
+      sgd_fetch_lin(lin_base + (n + 32) * 2ull, lin_stride, n + 32 < args.n ? lin_rows : 0, lane, bnext);
     if (have_acc) {
       tmem_ld_wait();
       acc_to_float(racc, f);
@@ -423,10 +458,10 @@ __device__ __forceinline__ CombineDest epilogue_tile(const CcfGemmArgs& args, co
             const float2 p = unpack2(w[j], fp16);
             w[j] = pack2(p.x - lr * fmaf(wd, p.x, f[2 * j]), p.y - lr * fmaf(wd, p.y, f[2 * j + 1]), fp16);
           }
-          staged_store64(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);
+          staged_store64_lin(stage, lane, w, lin_base + n * 2ull, lin_stride, lin_rows);
         } else {
           pack32(f, w, fp16);
-          staged_store64(stage, lane, w, valid ? addr2(args.out0, orow, args.ld_out, n) : 0ull);
+          staged_store64_lin(stage, lane, w, lin_base + n * 2ull, lin_stride, lin_rows);
         }
       } else if constexpr (kEpi == CCF_EPI_BIAS_ACT) {
         if (has_b0) add_bias_raw(f, bcur, fp16);

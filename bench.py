@@ -132,7 +132,7 @@ def classify_kernel(kname: str, scopes: str, shapes: str, vocab_padded: int, d_f
         return "moe_wait_for_peers"
     if any(t in k for t in ("route_", "plan_kernel", "combine_reduce", "topk_softmax", "router_", "colsum_grouped", "dispatch_kernel")):
         return "moe_route_plan_reduce"
-    if "sgd_step" in k:
+    if "sgd_step" in k or "sgd_multi" in k:
         return "optimizer"
     if "nccl" in k:
         return "nccl_allreduce"

@@ -35,10 +35,10 @@ def parse():
                          "from its observed routing counts, if that lowers the busiest GPU's load by at least 1 %% (same "
                          "model function; outside the timed region; needs more than one GPU). 0: keep the initial placement")
     ap.add_argument("--fuse-expert-sgd", type=int, default=1,
-                    help="1 (default): on one GPU the expert weights' SGD update runs in the epilogue of the weight-gradient "
-                         "GEMMs (MoELayer.fuse_sgd; needs ep_size 1, so it has no effect on 2 or more GPUs): the same update, "
-                         "without writing the expert gradients and reading them and the weights again; measured 5 %% faster "
-                         "per step with all 64 experts on one GPU. 0: separate optimizer pass for all parameters")
+                    help="1 (default): the expert weights' SGD update runs in the epilogue of the weight-gradient GEMMs "
+                         "(MoELayer.fuse_sgd: every expert matrix on one GPU, the second projection on 2 or more): the same "
+                         "update, without writing those gradients and reading them and the weights again; measured 5 %% "
+                         "faster per step with all 64 experts on one GPU. 0: separate optimizer pass for all parameters")
     ap.add_argument("--no-baseline", action="store_true",
                     help="skip the repository's own baseline arm (same model on the all_to_all_single + library "
                          "grouped-GEMM backend), against which vs_baseline is reported")
@@ -250,7 +250,7 @@ def run_arm(torch, dist, args, backend, steps, warmup, rank, local_rank, world, 
     model = GPTMoE(c, device=dev)
     fused = backend == "fused"
     # optional on one GPU: the experts' SGD update inside the weight-gradient GEMMs (same update, no gradient round trip)
-    fuse_sgd = fused and world == 1 and bool(args.fuse_expert_sgd)
+    fuse_sgd = fused and bool(args.fuse_expert_sgd)
     trainer = TrainStep(model, lr=1e-4, optimizer="sgd", fuse_expert_sgd=fuse_sgd)
 
     def sync():
@@ -416,7 +416,9 @@ def main():
                        "optimizer": "sgd", "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2",
                        "loss": round(ours["loss"], 4), "first_loss": ours["first_loss"], "capacity_factor": None,
                        "mean_expert_grads": False,
-                       "expert_sgd": ("applied in the weight-gradient GEMM epilogue (MoELayer.fuse_sgd)" if ours.get("fuse_sgd")
+                       "expert_sgd": (("applied in the weight-gradient GEMM epilogue (MoELayer.fuse_sgd)" if world == 1 else
+                                       "second projection: in its weight-gradient GEMM's epilogue (MoELayer.fuse_sgd); first "
+                                       "projection: separate optimizer pass") if ours.get("fuse_sgd")
                                       else "separate optimizer pass"),
                        "expert_placement": ("re-planned once from the routing counts of the last warm-up step, outside the "
                                             "timed region" if (args.rebalance and world > 1 and args.impl == "ours") else "initial"),

@@ -266,8 +266,13 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
   const long long rows_per_expert = static_cast<long long>(tokens) * L->top_k * L->world / (L->e_total > 0 ? L->e_total : 1);
   const int wgrad_two_cta = rows_per_expert > 512 ? L->two_cta : 0;
   const int row_two_cta = rows_per_expert > L->small_rows ? L->two_cta : 0;
-  const bool sgd = G->sgd_lr != 0.f;
-  if (sgd && L->world != 1) return -2;   // with peers the input-gradient GEMM has to stay the last owner-side kernel
+  // In-place SGD (sgd_lr != 0), matrix by matrix: a weight whose gradient pointer is null is updated by its weight-gradient
+  // GEMM. w2 may be at any group size (dgrad-2 above it is its last reader). w1 / wg only on a single rank: dgrad-1 reads
+  // them and, with peers, has to stay the last owner-side kernel of the pass.
+  const bool sgd2 = G->sgd_lr != 0.f && G->dw2 == nullptr;
+  const bool sgd = G->sgd_lr != 0.f && G->dw1 == nullptr;     // w1 (and wg) in place: dgrad-1 moves in front of wgrad-1
+  if (sgd && L->world != 1) return -2;
+  if (sgd && L->swiglu && G->dwg != nullptr) return -2;
   // 1 + 2. push g * dy rows + dgrad-2 with the activation derivative
   {
     CcfGemmLaunch g = base_launch(L);
@@ -300,9 +305,9 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
     g.kgroup = 1;
     g.args.n = f;
     g.args.m_per_group = d;
-    g.args.out0 = sgd ? const_cast<void*>(L->w2) : G->dw2;   // dgrad-2 above was the last reader of the old w2
-    g.args.sgd_lr = G->sgd_lr;
-    g.args.sgd_wd = G->sgd_wd;
+    g.args.out0 = sgd2 ? const_cast<void*>(L->w2) : G->dw2;   // dgrad-2 above was the last reader of the old w2
+    g.args.sgd_lr = sgd2 ? G->sgd_lr : 0.f;
+    g.args.sgd_wd = sgd2 ? G->sgd_wd : 0.f;
     g.args.ld_out = f;
     g.two_cta = wgrad_two_cta;
     if ((rc = issue(g, dry, stream))) return rc;
@@ -320,8 +325,8 @@ int ccf_layer_backward(const CcfLayer* L, const void* dy, const int* idx, const 
     g.args.n = d;
     g.args.m_per_group = f;
     g.args.out0 = out;
-    g.args.sgd_lr = G->sgd_lr;
-    g.args.sgd_wd = G->sgd_wd;
+    g.args.sgd_lr = sgd ? G->sgd_lr : 0.f;
+    g.args.sgd_wd = sgd ? G->sgd_wd : 0.f;
     g.args.ld_out = d;
     g.two_cta = wgrad_two_cta;
     return issue(g, dry, stream);

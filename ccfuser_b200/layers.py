@@ -153,17 +153,20 @@ class MoELayer(nn.Module):
         written and the optimizer never reads it and the weights again (with many experts per GPU that traffic is a
         large part of a step). The matrices' ``.grad`` stays ``None`` (an optimizer skips them); biases and the router
         keep the ordinary path. Same update as ``torch.optim.SGD`` without momentum, computed from the fp32 accumulator.
-        For the fused backend on a single-rank layer (``ep_size == 1``); not compatible with gradient accumulation,
-        clipping or anything else that needs the expert weight gradients. ``lr=None`` switches it off. Call it again
-        whenever the learning rate changes."""
+        On a single-rank layer (``ep_size == 1``) every expert matrix is updated this way. On a layer that spans ranks
+        only the second projection (``h4toh``) is: the first projection is still read by the input-gradient GEMM, which
+        with peers has to stay the last kernel of a backward pass, so it keeps its gradient and the optimizer's update.
+        For the fused backend; not compatible with gradient accumulation, clipping, replicated (shadow) experts or
+        anything else that needs the expert weight gradients. ``lr=None`` switches it off. Call it again whenever the
+        learning rate changes."""
         if lr is None:
             if self._fused is not None:
                 self._fused.sgd = None
             self._sgd = None
             return
-        if self.config.ep_size != 1:
-            raise ValueError("fuse_sgd needs ep_size == 1: with peers the input-gradient GEMM must stay the last kernel of "
-                             "a backward pass, after the weight gradients, and it reads the weights they would overwrite")
+        if getattr(self.config, "shadow_experts", 0) > 0:
+            raise ValueError("fuse_sgd is not available with shadow_experts > 0: the replicas return weight gradients to "
+                             "the experts' owners")
         self._sgd = (float(lr), float(weight_decay))
         if self._fused is not None:
             self._fused.sgd = self._sgd

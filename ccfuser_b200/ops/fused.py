@@ -660,7 +660,9 @@ class _FusedMoEFn(torch.autograd.Function):
         swiglu = cfg.activation == "swiglu"
         # fuse_sgd: the weight-gradient GEMMs update the weights in place (single-rank layers); no weight gradient is
         # returned, and dgrad-1, which still needs the old w1 / wg, moves in front of them
-        sgd = fm.sgd if (fm.sgd is not None and fm.world == 1 and fm.sgd[0] != 0.0) else None
+        # (w2 at any group size; w1 / wg only on a single rank, where dgrad-1 may move in front of their update)
+        sgd2 = fm.sgd if (fm.sgd is not None and fm.sgd[0] != 0.0) else None
+        sgd = sgd2 if fm.world == 1 else None
         if fm.native_runtime:
             has_b1, has_bg, has_b2 = ctx.has_bias
             mk = lambda like: torch.empty_like(like)                       # noqa: E731
@@ -668,13 +670,14 @@ class _FusedMoEFn(torch.autograd.Function):
             g = N.LayerGrads()
             dh = torch.empty(fm.max_rows, f, dtype=cfg.dtype, device=dy.device)
             dh2 = torch.empty_like(dh) if swiglu else None
-            dw1, dw2, dwg = (None, None, None) if sgd is not None else (mk(w1), mk(w2), (mk(wg) if swiglu else None))
+            dw2 = None if sgd2 is not None else mk(w2)
+            dw1, dwg = (None, None) if sgd is not None else (mk(w1), (mk(wg) if swiglu else None))
             db1, db2, dbg = (bias(f) if has_b1 else None), (bias(d) if has_b2 else None), (bias(f) if has_bg else None)
             dx = torch.empty(t, d, dtype=dy.dtype, device=dy.device)
             g.dgate, g.dh, g.dh2 = dgate.data_ptr(), dh.data_ptr(), N.ptr(dh2)
             g.dw1, g.db1, g.dwg, g.dbg, g.dw2, g.db2, g.dx = (N.ptr(v) for v in (dw1, db1, dwg, dbg, dw2, db2, dx))
-            if sgd is not None:
-                g.sgd_lr, g.sgd_wd = float(sgd[0]), float(sgd[1])
+            if sgd2 is not None:
+                g.sgd_lr, g.sgd_wd = float(sgd2[0]), float(sgd2[1])
             N.check(lib.ccf_layer_backward(C.byref(fm.native_desc()), dy.data_ptr(), idx.data_ptr(), gate_w.data_ptr(),
                                            C.byref(g), t, cfg.capacity(t), st, None, 0, None), "ccf_layer_backward")
             # kernels: dy dispatch + dgrad-2, wgrad-2, wgrad-1 (two for SwiGLU), dgrad-1 + combine, wait, reduce, column sums
@@ -704,9 +707,9 @@ class _FusedMoEFn(torch.autograd.Function):
         # With few rows per expert the reduction is only a handful of k-blocks and the per-tile latency chain decides:
         # there the one-CTA kernel (shorter barrier round trips, dynamic scheduler) is ~25 % faster than CTA pairs.
         wgrad_two_cta = None if (t * cfg.top_k * fm.world) // max(1, cfg.num_experts) > 512 else False
-        dw2 = torch.empty_like(w2) if sgd is None else None
+        dw2 = torch.empty_like(w2) if sgd2 is None else None
         G.launch(a0=cc.grecv, b0=fm.h_act, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=f, kgroup=True,
-                 m_per_group=d, out0=dw2 if sgd is None else w2, ld_out=f, two_cta=wgrad_two_cta, sgd=sgd, **common)
+                 m_per_group=d, out0=dw2 if sgd2 is None else w2, ld_out=f, two_cta=wgrad_two_cta, sgd=sgd2, **common)
         has_b1, has_bg, has_b2 = ctx.has_bias
 
         def colsum(src, n):

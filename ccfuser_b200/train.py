@@ -25,8 +25,9 @@ class TrainStep:
         ranks that hold replicas of this rank's experts (second value of ``make_ep_dp_groups``) when the expert-parallel
         group is smaller than the job. ``mean_expert_grads``: scale expert gradients by 1 / world size so that they
         follow the same mean-over-ranks convention as the replicated parameters. ``fuse_expert_sgd`` (plain SGD, fused
-        MoE layers with ``ep_size == 1``): the expert weight matrices are updated inside the backward pass
-        (``MoELayer.fuse_sgd``) with the optimizer's current learning rate and weight decay."""
+        MoE layers): expert weight matrices are updated inside the backward pass (``MoELayer.fuse_sgd``: all of them on
+        single-rank layers, the second projection on layers that span ranks) with the optimizer's current learning rate
+        and weight decay."""
         self.raw_model = model
         self.dp_group = dp_group
         self.expert_dp_group = expert_dp_group

@@ -81,8 +81,53 @@ def ep_inside_dp(rank, world):
     assert all(torch.equal(parts[0], q) for q in parts)
 
 
+def fused_sgd_across_ranks(rank, world):
+    """fuse_sgd on a layer that spans ranks: the second projection is updated by its weight-gradient GEMM (no gradient
+    tensor), the first keeps its gradient; after the optimizer's step both match a layer that took the ordinary path."""
+    from ccfuser_b200.ops.optim import FusedSGD
+    for act in ("gelu", "swiglu"):
+        cfg = MoEConfig(d_model=256, d_ffn=512, num_experts=4 * world, top_k=2, capacity_factor=None, activation=act,
+                        dtype=torch.bfloat16, ep_size=world, backend="fused", max_tokens=1024, recv_factor=4.0)
+        plain, fused = make(cfg, 11), make(cfg, 11)
+        w0 = plain.experts.h4toh.weight.detach().clone()
+        lr, wd = 0.05, 0.01
+        fused.fuse_sgd(lr, wd)
+        gx = torch.Generator(device="cuda").manual_seed(70 + rank)
+        x = (torch.randn(1024, 256, device="cuda", generator=gx) * 0.5).bfloat16()
+        gy = torch.randn(1024, 256, device="cuda", generator=gx).bfloat16()
+        outs = []
+        for layer in (plain, fused):
+            xi = x.clone().requires_grad_(True)
+            y = layer(xi)
+            y.backward(gy)
+            FusedSGD(layer.parameters(), lr=lr, weight_decay=wd).step()
+            torch.cuda.synchronize()
+            layer.check_status()
+            outs.append((y.detach(), xi.grad))
+        assert fused.experts.h4toh.weight.grad is None and fused.experts.htoh4.weight.grad is not None
+        assert rel(outs[1][0], outs[0][0]) < 1e-3 and rel(outs[1][1], outs[0][1]) < 1e-3
+        for (n, a), (_, b) in zip(fused.named_parameters(), plain.named_parameters()):
+            if n == "experts.h4toh.weight":
+                # the in-place update rounds once from the fp32 accumulator, the ordinary path rounds the gradient first
+                upd_f, upd_p = a.detach().float() - w0.float(), b.detach().float() - w0.float()
+                assert float(upd_p.abs().max()) > 1e-3, "the step must be visible at bf16 resolution"
+                assert rel(upd_f, upd_p) < 5e-2, (act, n, rel(upd_f, upd_p))
+            else:
+                assert rel(a.detach(), b.detach()) < 1e-3, (act, n, rel(a.detach(), b.detach()))
+        dist.barrier()
+        plain.release()
+        fused.release()
+
+
 def main():
     rank, _, world = init_distributed()
+    if "--fused-sgd" in sys.argv:
+        fused_sgd_across_ranks(rank, world)
+        dist.barrier()
+        if rank == 0:
+            print("MGPU_FSGD_OK", flush=True)
+        dist.destroy_process_group()
+        return
     if "--ep-inside-dp" in sys.argv:
         assert world in (2, 4), "needs 2 or 4 ranks (expert-parallel groups of two)"
         ep_inside_dp(rank, world)

@@ -47,3 +47,12 @@ def test_expert_parallel_inside_data_parallel_multi_gpu(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _run(world, 29710 + world, worker="mgpu_features_worker.py", token="MGPU_EPDP_OK", timeout=300, args=["--ep-inside-dp"])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sgd_in_the_weight_gradient_epilogue_across_ranks_multi_gpu(world):
+    """MoELayer.fuse_sgd on a layer that spans ranks: second projection updated in place, same weights as the ordinary
+    path after one step."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run(world, 29720 + world, worker="mgpu_features_worker.py", token="MGPU_FSGD_OK", timeout=300, args=["--fused-sgd"])

@@ -172,9 +172,9 @@ def test_fused_sgd_launches_agree_and_update_in_place(act):
     per_call = {"args.disp.x", "args.disp.slot_expert", "args.disp.slot_gate", "args.disp.dgate", "args.out0", "args.out1"}
     for p, n, skip in zip(py, nat, [per_call, set(), {"a0", "a1"}] + [{"a0"}] * 2):
         _compare(p, n, skip)
-    # a layer that spans ranks refuses
-    spanning = type("SpanningLayer", (), {"config": cfg.replace(ep_size=2), "_fused": None})()
+    # a layer with replicated experts refuses (their gradients travel back to the owners)
+    shadowed = type("ShadowedLayer", (), {"config": cfg.replace(shadow_experts=1), "_fused": None})()
     with pytest.raises(ValueError):
-        MoELayer.fuse_sgd(spanning, 0.1)
+        MoELayer.fuse_sgd(shadowed, 0.1)
     layer.fuse_sgd(None)
     assert fm.sgd is None

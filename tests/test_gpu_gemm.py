@@ -175,6 +175,34 @@ def test_wgrad_kgrouped():
             _close(dw32[i], ref, tol=2e-3)
 
 
+@pytest.mark.parametrize("two_cta", [False, True])
+def test_wgrad_with_sgd_in_the_epilogue(two_cta):
+    """k-grouped product whose epilogue rewrites the weights in place (w - lr * (a^T b + wd * w)) instead of storing the
+    gradient, on the one-CTA kernel and on CTA pairs, with groups of ragged and zero length."""
+    N, G = _mods()
+    torch.manual_seed(15)
+    rows = [700, 0, 64, 1100, 255]
+    e, m, n = len(rows), 512, 768
+    lr, wd = 0.05, 0.1
+    gb, gr, total = _groups(rows, "cuda")
+    a = torch.randn(total, m, device="cuda", dtype=torch.bfloat16) * 0.1
+    b = torch.randn(total, n, device="cuda", dtype=torch.bfloat16)
+    for i, r in enumerate(rows):
+        s = int(gb[i])
+        a[s + r:s + (r + 127) // 128 * 128] = 0
+    w0 = torch.randn(e, m, n, device="cuda", dtype=torch.bfloat16)
+    w = w0.clone()
+    G.launch(a0=a, b0=b, a_major=N.MAJ_MN, b_major=N.MAJ_MN, epi=N.EPI_STORE, n=n, kgroup=True, m_per_group=m,
+             group_base=gb, group_rows=gr, num_groups=e, out0=w, ld_out=n, two_cta=two_cta, sgd=(lr, wd))
+    torch.cuda.synchronize()
+    G.Workspace.get(a.device).check("wgrad with sgd")
+    for i, r in enumerate(rows):
+        s = int(gb[i])
+        dw = a[s:s + r].float().t() @ b[s:s + r].float()
+        ref = w0[i].float() - lr * (dw + wd * w0[i].float())
+        assert float((w[i].float() - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
 def test_combine_epilogue_local_rank():
     """GEMM-2 epilogue on one GPU: rows go to `slot` rows of this rank's own combine buffer, scaled by the gate."""
     N, G = _mods()

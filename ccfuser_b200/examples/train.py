@@ -110,6 +110,9 @@ def main():
     ap.add_argument("--aux-loss-coef", type=float, default=0.0, help="weight of the router load-balance loss")
     ap.add_argument("--z-loss-coef", type=float, default=0.0, help="weight of the router z-loss")
     ap.add_argument("--router-fp32", action="store_true", help="keep the routers in fp32")
+    ap.add_argument("--fuse-expert-sgd", action="store_true",
+                    help="fused variant with --optimizer sgd: expert weight matrices are updated inside the backward pass "
+                         "(MoELayer.fuse_sgd; all of them when the experts live on one rank, the second projection otherwise)")
     ap.add_argument("--data", default="", help="txl only: training text file (word-level vocabulary built from it); "
                                                "default is a fixed synthetic batch")
     ap.add_argument("--valid", default="", help="txl only: validation text file, evaluated at the end")
@@ -141,6 +144,13 @@ def main():
     wrapped = wrap_ddp(model) if world > 1 else model
     params = [p for p in model.parameters() if p.requires_grad]
     opt = torch.optim.SGD(params, lr=args.lr) if args.optimizer == "sgd" else torch.optim.AdamW(params, lr=args.lr)
+    if args.fuse_expert_sgd:
+        if args.variant != "fused" or args.optimizer != "sgd" or expert_dp_group is not None:
+            raise SystemExit("--fuse-expert-sgd needs --variant fused, --optimizer sgd and experts that are not replicated")
+        from ..layers import MoELayer
+        for m in model.modules():
+            if isinstance(m, MoELayer):
+                m.fuse_sgd(args.lr)
     start_step = 0
     if args.resume:
         import os

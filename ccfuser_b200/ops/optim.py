@@ -43,7 +43,10 @@ class FusedSGD(torch.optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None):
-        loss = closure() if closure is not None else None
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
         lib = None
         for group in self.param_groups:
             lr, wd = float(group["lr"]), float(group["weight_decay"])

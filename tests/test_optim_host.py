@@ -55,3 +55,17 @@ def test_launch_table_gives_every_tensor_its_blocks():
     assert [t.n[i] for i in range(len(sizes))] == sizes
     assert [t.p[i] for i in range(len(sizes))] == [0x1000 * (i + 1) for i in range(len(sizes))]
     assert C.sizeof(N.SgdMulti) == 48 * 24 + 49 * 4 + 16 + 4      # the layout the library checks at load time
+
+
+def test_closure_runs_with_gradients_enabled():
+    p = torch.nn.Parameter(torch.tensor([1.0, -2.0]))
+    opt = FusedSGD([p], lr=0.5)
+
+    def closure():
+        opt.zero_grad()
+        loss = (p * p).sum()
+        loss.backward()
+        return loss
+
+    loss = opt.step(closure)
+    assert float(loss) == 5.0 and torch.allclose(p.detach(), torch.tensor([0.0, 0.0]))
